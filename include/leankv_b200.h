@@ -1,0 +1,206 @@
+/*
+ * leankv_b200 — C ABI of the B200 (sm_100a) kernels behind the leankv hot paths.
+ *
+ * The reference project (asmit383/leankv) is pure Python and has no FFI of its own;
+ * each entry point below names the reference function whose arithmetic it replaces
+ * (paths are relative to the reference project root).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless its comment says "host";
+ *  - the caller owns all buffers; no entry point allocates, frees or synchronises;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream); work is
+ *    stream-ordered, entry points may be captured into a CUDA graph;
+ *  - return value: 0 on success, a negative LEANKV_E* code otherwise
+ *    (leankv_strerror gives the text). Arguments are validated before any launch;
+ *  - "workspace" buffers hold split-K partial sums and arrival counters. A workspace
+ *    must be zero-filled once after allocation; kernels leave the counters zeroed
+ *    on exit. One workspace must not be shared by launches that can overlap in time.
+ */
+#ifndef LEANKV_B200_H
+#define LEANKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LEANKV_OK 0
+#define LEANKV_EINVAL (-1)      /* bad shape / size / null pointer            */
+#define LEANKV_EALIGN (-2)      /* pointer or leading dimension misaligned    */
+#define LEANKV_EWORKSPACE (-3)  /* workspace too small                        */
+#define LEANKV_ECUDA (-4)       /* a CUDA runtime call failed                 */
+#define LEANKV_EUNSUPPORTED (-5)/* valid request the kernels do not implement */
+#define LEANKV_ELIMIT (-6)      /* size beyond a compiled-in maximum          */
+
+const char* leankv_strerror(int code);
+/* ABI version: bumped when a signature changes. */
+int leankv_abi_version(void);
+/* Text of the last CUDA error seen by this library on the calling thread. */
+const char* leankv_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------- *
+ * TEAL activation-sparse GEMV (batch 1).
+ * Replaces leankv/teal/kernels/sparse_gemv.py:143-181 (sparse_gemv) and the Triton
+ * kernel at :61-87; mask semantics follow leankv/teal/sparse_fns.py:32-39:
+ *     y[n] = sum over z with |x[z]| > fp16(threshold) of Wt[z][n] * x[z]
+ * Wt is the layout produced by prepare_weight_for_sparse_gemv (:229-234):
+ * row z holds the N weights that multiply input channel z, rows contiguous.
+ * Accumulation is fp32 in a fixed order (results are bit-reproducible run to run);
+ * y is rounded to fp16 once.
+ * ------------------------------------------------------------------------- */
+
+/* Segments let one launch serve several projections that share x but carry their
+ * own thresholds (q/k/v): segment s covers output columns [seg_end[s-1], seg_end[s]).
+ * Every seg_end must be a multiple of 256 except the last, which must equal N. */
+#define LEANKV_MAX_SEGMENTS 4
+typedef struct {
+    int   n_segments;                       /* 1..LEANKV_MAX_SEGMENTS */
+    int   seg_end[LEANKV_MAX_SEGMENTS];
+    float threshold[LEANKV_MAX_SEGMENTS];
+} leankv_segments_t;
+
+size_t leankv_sparse_gemv_workspace_bytes(int N, int Z);
+
+/* N % 8 == 0; Wt and y 16-byte aligned. bias / residual may be NULL; when given they are
+ * fp16 [N] and are added in fp16 after y has been rounded (bias first, as
+ * patching.py:174-175 does, then residual + y as the decoder block does).
+ * active_elems (may be NULL) is a uint64 counter that receives += the number of weight
+ * elements streamed (channels that passed the threshold x columns); 2 bytes each. */
+int leankv_sparse_gemv_f16(const void* Wt, const void* x, void* y, int N, int Z,
+                           float threshold, const void* bias, const void* residual,
+                           void* workspace, size_t workspace_bytes,
+                           unsigned long long* active_elems, void* stream);
+
+int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y, int N, int Z,
+                               const leankv_segments_t* segs /* host */,
+                               const void* bias, const void* residual,
+                               void* workspace, size_t workspace_bytes,
+                               unsigned long long* active_elems, void* stream);
+
+/* Fused gate/up SwiGLU: y[n] = silu(Wg.x_g)[n] * (Wu.x_u)[n], where x_g / x_u are x
+ * masked with t_gate / t_up (the reference installs separate thresholds on gate_proj
+ * and up_proj, leankv/teal/patching.py:101-125). Replaces two sparse_gemv calls plus
+ * the act_fn(gate)*up elementwise of the HF MLP. Rounding follows that path: gate and
+ * up are rounded to fp16, silu is evaluated in fp32 and rounded to fp16, the product
+ * is rounded to fp16. */
+size_t leankv_sparse_swiglu_workspace_bytes(int N, int Z);
+int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, const void* x,
+                             void* y, int N, int Z, float t_gate, float t_up,
+                             void* workspace, size_t workspace_bytes,
+                             unsigned long long* active_elems, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * TurboQuant (MSE variant, Algorithm 1), reference-format tensors.
+ * Replaces leankv/turboquant/quantizer.py:119-129 (quantize) and :131-137
+ * (dequantize) with _pack_indices/_unpack_indices (:38-85).
+ *   norm = ||x||_2 ; u = x / (norm + 1e-10) ; y = Pi u (fp32 FMA, ascending index) ;
+ *   code = number of decision boundaries strictly below y ; codes bit-packed
+ * indices: uint8 [n_vec][packed_len(dim,bits)], bits 1 -> 8 per byte, 2 -> 4 per
+ * byte, 3..4 -> two nibbles per byte (low nibble = even coordinate). norms fp32.
+ * Pi is row-major [dim][dim] fp32 (y = Pi u, i.e. rotate_forward of rotation.py:45-47).
+ * dim must be 128, bits 1..4. x_dtype: 0 = fp16, 1 = fp32; rows of x contiguous.
+ * ------------------------------------------------------------------------- */
+int leankv_tq_packed_len(int dim, int bits);
+int leankv_tq_quantize(const void* x, int x_dtype, long long n_vec, int dim, int bits,
+                       const float* Pi, const float* decision_boundaries /* 2^bits-1 */,
+                       uint8_t* indices, float* norms, void* stream);
+/* x_hat[v] = norms[v] * (centroids[codes[v]] @ Pi)   (rotate_backward, rotation.py:50-52) */
+int leankv_tq_dequantize(const uint8_t* indices, const float* norms, long long n_vec,
+                         int dim, int bits, const float* Pi, const float* centroids,
+                         void* x_hat, int out_dtype /* 0 = fp16, 1 = fp32 */, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Paged 3-bit TurboQuant KV pool (dim 128, 3 bits, 16 tokens per page).
+ * The pool replaces the cold store of leankv/turboquant/cache.py:73-76 and borrows
+ * the page-table conventions of leankv/turboquant/paged_cache.py:215-233
+ * (kv_indptr / kv_page_indices / kv_last_page_len, int32).
+ *
+ * One layer's pool is [n_pages][2 (K,V)][n_kv_heads][LEANKV_TQ_CHUNK_BYTES] bytes.
+ * A chunk holds the 16 tokens of one page for one head: 768 bytes of 3-bit codes
+ * (192 words, kernel-native order, see leankv_tq_pool_unpack) followed by 16 fp16 norms.
+ * ------------------------------------------------------------------------- */
+#define LEANKV_TQ_PAGE_TOKENS 16
+#define LEANKV_TQ_DIM 128
+#define LEANKV_TQ_CHUNK_BYTES 800
+
+size_t leankv_tq_pool_bytes(int n_pages, int n_kv_heads);
+
+/* Fused rotate + Lloyd-Max quantize + 3-bit pack on append (cache.py:136-142 followed
+ * by the torch.cat of :145-159). k, v: fp16 [B][n_kv_heads][T_new][128] contiguous.
+ * Token t of sequence b lands at position start_pos[b] + t of that sequence; its page
+ * is kv_page_indices[kv_indptr[b] + pos / 16]. Pages must already be assigned.
+ * start_pos: int32 [B] device. */
+int leankv_tq_pool_append(const void* k, const void* v, int B, int n_kv_heads, int T_new,
+                          const float* Pi_k, const float* Pi_v,
+                          const float* decision_boundaries /* 7 */,
+                          void* pool, int n_pages,
+                          const int32_t* kv_indptr, const int32_t* kv_page_indices,
+                          const int32_t* start_pos, void* stream);
+
+/* Pool -> reference format for pages of one sequence: codes as nibble-packed uint8
+ * [n_kv_heads][n_tokens][64] and norms fp32 [n_kv_heads][n_tokens] (the fp16 pool
+ * norm widened), for K (which = 0) or V (which = 1). */
+int leankv_tq_pool_unpack(const void* pool, int n_pages, int n_kv_heads,
+                          const int32_t* page_indices /* device, ceil(n_tokens/16) */,
+                          int n_tokens, int which, uint8_t* indices, float* norms,
+                          void* stream);
+
+/* Decode attention straight from the packed pool: for each sequence b and query head h
+ *   out[b][h] = softmax_t( scale * q[b][h] . k_hat[b][kvh][t] ) . v_hat[b][kvh][t]
+ * with k_hat / v_hat the TurboQuant reconstructions (quantizer.py:131-137) that
+ * cache.py:169-189 would materialise; they are never formed: the query is rotated once,
+ * scores and the value sum are taken in rotated space on tensor cores, and the output is
+ * rotated back once. q, out: fp16 [B][n_q_heads][128]. n_q_heads / n_kv_heads must be 4
+ * (GQA-4) in this version. kv_last_page_len[b] in 1..16; a sequence with
+ * kv_indptr[b+1] == kv_indptr[b] yields zeros. max_pages_per_seq bounds the split-KV
+ * grid (host value, >= the longest sequence's page count). centroids is read on the
+ * host (the codebook is a compile-time-like constant of the cache): it is turned into
+ * register look-up tables that travel as kernel arguments. The first 4 bytes of the
+ * workspace are a status word (see leankv_tq_decode_attn_status). */
+size_t leankv_tq_decode_attn_workspace_bytes(int B, int n_q_heads, int n_kv_heads,
+                                             int max_pages_per_seq);
+int leankv_tq_decode_attn(const void* q, void* out, int B, int n_q_heads, int n_kv_heads,
+                          const void* pool, int n_pages,
+                          const int32_t* kv_indptr, const int32_t* kv_page_indices,
+                          const int32_t* kv_last_page_len, int max_pages_per_seq,
+                          const float* Pi_k, const float* Pi_v,
+                          const float* centroids /* host, 8 */, float scale,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device status word of the bounded waits inside the attention kernel (0 = no wait
+ * ever gave up). Copied to *status with a synchronous 4-byte copy from `workspace`. */
+int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
+
+/* ------------------------------------------------------------------------- *
+ * Glue kernels of a batch-1 decode step (no reference counterpart: the reference leaves
+ * these steps to the HF modules around its hooks — MistralRMSNorm, apply_rotary_pos_emb,
+ * embed_tokens, argmax of generate()). They exist so that a whole decode step, including
+ * the position / page-table bookkeeping, can be replayed as one CUDA graph.
+ *
+ * state: int32[8] on the device:
+ *   [0] pos        tokens already cached = position of the token being decoded
+ *   [1] step       tokens generated so far (index into history)
+ *   [2],[3]        kv_indptr of the single sequence {0, pages in use after this append}
+ *   [4]            kv_last_page_len after this append
+ *   [5]            start_pos of this append
+ * ------------------------------------------------------------------------- */
+/* y = weight * fp16(x * rsqrt(mean(x^2) + eps)); fp16 [n], one vector. */
+int leankv_rmsnorm_f16(const void* x, const void* weight, void* y, int n, float eps, void* stream);
+/* h = embed_table[*token]; state[2..5] derived from state[0]. hidden % 8 == 0. */
+int leankv_decode_begin(const void* embed_table, const long long* token, void* h, int hidden,
+                        int vocab, int32_t* state, void* stream);
+/* Rotary embedding (rotate_half form, position state[0]) of the first n_q_heads + n_kv_heads
+ * 128-wide heads of a fused qkv row; inv_freq fp32 [64]. */
+int leankv_rope_f16(const void* qkv, const float* inv_freq, const int32_t* state, void* q_out,
+                    void* k_out, int n_q_heads, int n_kv_heads, int head_dim, void* stream);
+/* *token = argmax(logits) (lowest index on ties); history[state[1]] = *token;
+ * state[1] += 1; state[0] += 1. */
+int leankv_decode_end(const void* logits, int vocab, long long* token, long long* history,
+                      int history_cap, int32_t* state, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEANKV_B200_H */

@@ -1,0 +1,51 @@
+// Error reporting and device queries shared by the C ABI entry points.
+
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace leankv {
+
+namespace {
+thread_local char g_last_cuda_error[256] = "";
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices] = {0};
+}  // namespace
+
+int note_cuda_error(cudaError_t e, const char* what) {
+    std::snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s (%s)", what,
+                  cudaGetErrorName(e), cudaGetErrorString(e));
+    return LEANKV_ECUDA;
+}
+
+int sm_count() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int n = g_sm_count[dev];
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;   // B200; also the value used when planning without a device present
+        g_sm_count[dev] = n;
+    }
+    return n;
+}
+
+}  // namespace leankv
+
+extern "C" const char* leankv_strerror(int code) {
+    switch (code) {
+        case LEANKV_OK: return "success";
+        case LEANKV_EINVAL: return "invalid argument (shape, size or null pointer)";
+        case LEANKV_EALIGN: return "pointer, size or segment boundary not suitably aligned";
+        case LEANKV_EWORKSPACE: return "workspace missing or too small";
+        case LEANKV_ECUDA: return "CUDA runtime error (see leankv_last_cuda_error)";
+        case LEANKV_EUNSUPPORTED: return "configuration not implemented by the sm_100a kernels";
+        case LEANKV_ELIMIT: return "size exceeds a compiled-in maximum";
+        default: return "unknown leankv error code";
+    }
+}
+
+extern "C" int leankv_abi_version(void) { return 1; }
+
+extern "C" const char* leankv_last_cuda_error(void) { return leankv::g_last_cuda_error; }

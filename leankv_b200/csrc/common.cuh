@@ -1,0 +1,58 @@
+// Shared helpers for the leankv_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "leankv_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "leankv_b200 kernels are written for sm_100a"
+#endif
+
+namespace leankv {
+
+// Records a failing CUDA call for leankv_last_cuda_error() and maps it to LEANKV_ECUDA.
+int note_cuda_error(cudaError_t e, const char* what);
+
+#define LEANKV_CUDA_TRY(expr)                                              \
+    do {                                                                   \
+        cudaError_t _e = (expr);                                           \
+        if (_e != cudaSuccess) return ::leankv::note_cuda_error(_e, #expr); \
+    } while (0)
+
+// Number of SMs of the current device (cached per device id).
+int sm_count();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// 16-byte streaming load that does not allocate in L1 (weights are read exactly once).
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// L2-coherent 4-byte load for data written by other CTAs of the same grid.
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float2 h2_to_f2(uint32_t packed) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&packed));
+}
+
+}  // namespace leankv

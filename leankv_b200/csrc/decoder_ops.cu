@@ -1,0 +1,156 @@
+// Small kernels that sit between the two hot paths in a batch-1 decode step of a
+// Llama/Mistral-style block: embedding fetch, RMSNorm, rotary embedding, greedy argmax and
+// the on-device bookkeeping of the sequence position / page table, so that a whole decode
+// step can be replayed as one CUDA graph without the host touching per-step values.
+// Rounding points follow the HF eager modules the reference runs around its kernels
+// (transformers modeling_mistral.py: MistralRMSNorm, apply_rotary_pos_emb).
+
+#include "common.cuh"
+
+namespace leankv {
+namespace {
+
+// Decode state words (int32, device): see leankv_decode_state_t in the header.
+enum { kPos = 0, kStep = 1, kIndptr0 = 2, kIndptr1 = 3, kLastLen = 4, kStartPos = 5 };
+
+__device__ __forceinline__ float block_sum(float v, float* s_tmp) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) s_tmp[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = 0.f;
+    for (int w = 0; w < nw; ++w) t += s_tmp[w];   // fixed order: bit-reproducible
+    __syncthreads();
+    return t;
+}
+
+// y = w * fp16( x * rsqrt(mean(x^2) + eps) ), statistics in fp32.
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const __half* x, const __half* w, __half* y,
+                                                       int n, float eps) {
+    __shared__ float s_tmp[32];
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = __half2float(x[i]);
+        ss = fmaf(v, v, ss);
+    }
+    const float tot = block_sum(ss, s_tmp);
+    const float r = rsqrtf(tot / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        y[i] = __hmul(w[i], __float2half_rn(__half2float(x[i]) * r));
+}
+
+// Fetch the embedding row of the current token and derive this step's page-table words.
+__global__ void __launch_bounds__(256) decode_begin_kernel(const __half* table, const long long* token,
+                                                           __half* h, int hidden, int vocab,
+                                                           int* state) {
+    long long tok = *token;
+    if (tok < 0 || tok >= vocab) tok = 0;
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(h);
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+    if (threadIdx.x == 0) {
+        const int pos = state[kPos];
+        state[kStartPos] = pos;
+        state[kIndptr0] = 0;
+        state[kIndptr1] = pos / 16 + 1;
+        state[kLastLen] = pos % 16 + 1;
+    }
+}
+
+// Rotary embedding (rotate_half form) on the q and k parts of a fused qkv row.
+// cos/sin are rounded to fp16 and the products/sum are fp16, as in the HF module.
+__global__ void __launch_bounds__(64) rope_kernel(const __half* qkv, const float* inv_freq,
+                                                  const int* state, __half* q_out, __half* k_out,
+                                                  int n_q_heads, int n_kv_heads) {
+    const int head = blockIdx.x;                 // q heads first, then k heads
+    const int i = threadIdx.x;                   // 0..63
+    const float ang = (float)state[kPos] * inv_freq[i];
+    const __half c = __float2half_rn(cosf(ang)), s = __float2half_rn(sinf(ang));
+    const __half* src = qkv + (size_t)head * 128;
+    __half* dst = head < n_q_heads ? q_out + (size_t)head * 128
+                                   : k_out + (size_t)(head - n_q_heads) * 128;
+    const __half a = src[i], b = src[i + 64];
+    dst[i] = __hadd(__hmul(a, c), __hmul(__hneg(b), s));
+    dst[i + 64] = __hadd(__hmul(b, c), __hmul(a, s));
+}
+
+// Greedy next token (lowest index wins ties), appended to the history; advances the position.
+__global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, int vocab,
+                                                          long long* token, long long* history,
+                                                          int history_cap, int* state) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = __half2float(logits[i]);
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (s_v[w] > best || (s_v[w] == best && s_i[w] < best_i)) { best = s_v[w]; best_i = s_i[w]; }
+        if (best_i == 0x7fffffff) best_i = 0;   // all-NaN row
+        *token = best_i;
+        const int step = state[kStep];
+        if (step < history_cap) history[step] = best_i;
+        state[kStep] = step + 1;
+        state[kPos] = state[kPos] + 1;
+    }
+}
+
+}  // namespace
+}  // namespace leankv
+
+using namespace leankv;
+
+extern "C" int leankv_rmsnorm_f16(const void* x, const void* weight, void* y, int n, float eps,
+                                  void* stream) {
+    if (!x || !weight || !y || n <= 0) return LEANKV_EINVAL;
+    rmsnorm_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(weight), static_cast<__half*>(y), n, eps);
+    LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_decode_begin(const void* embed_table, const long long* token, void* h,
+                                   int hidden, int vocab, int32_t* state, void* stream) {
+    if (!embed_table || !token || !h || !state || hidden <= 0 || vocab <= 0) return LEANKV_EINVAL;
+    if (hidden % 8 != 0 || !aligned16(embed_table) || !aligned16(h)) return LEANKV_EALIGN;
+    decode_begin_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(embed_table), token, static_cast<__half*>(h), hidden, vocab, state);
+    LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_rope_f16(const void* qkv, const float* inv_freq, const int32_t* state,
+                               void* q_out, void* k_out, int n_q_heads, int n_kv_heads,
+                               int head_dim, void* stream) {
+    if (!qkv || !inv_freq || !state || !q_out || !k_out || n_q_heads <= 0 || n_kv_heads <= 0)
+        return LEANKV_EINVAL;
+    if (head_dim != 128) return LEANKV_EUNSUPPORTED;
+    rope_kernel<<<n_q_heads + n_kv_heads, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(qkv), inv_freq, state, static_cast<__half*>(q_out),
+        static_cast<__half*>(k_out), n_q_heads, n_kv_heads);
+    LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_decode_end(const void* logits, int vocab, long long* token, long long* history,
+                                 int history_cap, int32_t* state, void* stream) {
+    if (!logits || !token || !history || !state || vocab <= 0 || history_cap < 0) return LEANKV_EINVAL;
+    decode_end_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(logits), vocab, token, history, history_cap, state);
+    LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}

@@ -1,0 +1,407 @@
+// TEAL activation-sparse GEMV for batch-1 decode on B200.
+//
+// y[n] = sum_{z : |x[z]| > t} Wt[z][n] * x[z]        (Wt is [Z][N], rows contiguous)
+//
+// Work decomposition: a CTA owns 256 output columns (one 16-byte load per lane per row)
+// and a contiguous range of input channels. It tests the threshold on its range,
+// compacts the surviving channels with warp ballot/popc into an ordered list in shared
+// memory, and its 8 warps stream the listed weight rows round-robin, 8 independent
+// 16-byte loads in flight per lane. Split-K partials go to a workspace; the last CTA to
+// arrive for a column slice sums them in split order, so the result does not depend on
+// arrival order and no floating-point atomics are used.
+//
+// Arithmetic follows the reference's B=1 path (leankv/teal/kernels/sparse_gemv.py:71-87:
+// fp16 operands widened to fp32, fp32 sums) and the mask of leankv/teal/sparse_fns.py:36
+// (strict '>' against the threshold rounded to fp16).
+
+#include "common.cuh"
+
+namespace leankv {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kColsPerCta = 256;       // 32 lanes x 8 fp16
+constexpr int kLaneSlots = 4;          // threshold tests per lane during compaction
+constexpr int kMaxRowsPerSplit = kWarps * 32 * kLaneSlots;  // 1024
+constexpr int kMaxSplits = 128;
+constexpr int kCtasPerSm = 4;
+
+struct GemvParams {
+    const __half* Wt;
+    const __half* Wt2;   // up_proj weights (SwiGLU only)
+    const __half* x;
+    __half* y;
+    const __half* bias;
+    const __half* residual;
+    float* partials;
+    int* counters;
+    unsigned long long* active_elems;
+    int N, Z;
+    int n_slices, k_splits, rows_per_split;
+    int n_segments;
+    int seg_end[LEANKV_MAX_SEGMENTS];
+    float thr[LEANKV_MAX_SEGMENTS];
+    float thr_up;        // SwiGLU: thr[0] masks gate, thr_up masks up
+};
+
+struct GemvPlan {
+    int n_slices, k_splits, rows_per_split;
+    size_t counter_bytes, partial_bytes;
+};
+
+GemvPlan make_plan(int N, int Z, int arrays) {
+    GemvPlan pl;
+    pl.n_slices = (N + kColsPerCta - 1) / kColsPerCta;
+    int target = sm_count() * kCtasPerSm;
+    int ks = target / pl.n_slices;
+    if (ks < 1) ks = 1;
+    int by_rows = Z / 32;            // keep at least ~32 input channels per split
+    if (by_rows < 1) by_rows = 1;
+    if (ks > by_rows) ks = by_rows;
+    if (ks > kMaxSplits) ks = kMaxSplits;
+    int rows = (Z + ks - 1) / ks;
+    if (rows > kMaxRowsPerSplit) rows = kMaxRowsPerSplit;
+    pl.rows_per_split = rows;
+    pl.k_splits = (Z + rows - 1) / rows;
+    pl.counter_bytes = round_up(sizeof(int) * (size_t)pl.n_slices, 256);
+    pl.partial_bytes =
+        pl.k_splits > 1 ? sizeof(float) * (size_t)pl.k_splits * arrays * pl.n_slices * kColsPerCta : 0;
+    return pl;
+}
+
+__device__ __forceinline__ void fma8(float (&acc)[8], const uint4& w, float xv) {
+    float2 a = h2_to_f2(w.x), b = h2_to_f2(w.y), c = h2_to_f2(w.z), d = h2_to_f2(w.w);
+    acc[0] = fmaf(a.x, xv, acc[0]);
+    acc[1] = fmaf(a.y, xv, acc[1]);
+    acc[2] = fmaf(b.x, xv, acc[2]);
+    acc[3] = fmaf(b.y, xv, acc[3]);
+    acc[4] = fmaf(c.x, xv, acc[4]);
+    acc[5] = fmaf(c.y, xv, acc[5]);
+    acc[6] = fmaf(d.x, xv, acc[6]);
+    acc[7] = fmaf(d.y, xv, acc[7]);
+}
+
+template <bool kSwiglu>
+__global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(const GemvParams p) {
+    constexpr int kArrays = kSwiglu ? 2 : 1;
+    constexpr int kUnroll = kSwiglu ? 4 : 8;
+
+    __shared__ uint16_t s_row[kMaxRowsPerSplit];
+    __shared__ float s_x[kMaxRowsPerSplit];
+    __shared__ float s_x2[kSwiglu ? kMaxRowsPerSplit : 1];
+    __shared__ __align__(16) float s_red[kWarps][kArrays][kColsPerCta];
+    __shared__ int s_wcount[kWarps];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int slice = blockIdx.x;
+    const int z0 = blockIdx.y * p.rows_per_split;
+    const int nrows = min(p.rows_per_split, p.Z - z0);
+
+    // Threshold of the projection this column slice belongs to.
+    float thr = p.thr[0];
+    if (!kSwiglu) {
+        const int c = slice * kColsPerCta;
+        int s = 0;
+        while (s + 1 < p.n_segments && c >= p.seg_end[s]) ++s;
+        thr = p.thr[s];
+    }
+    const __half thr_h = __float2half_rn(thr);
+    const __half thr2_h = __float2half_rn(kSwiglu ? p.thr_up : thr);
+
+    // ---- threshold test + ordered compaction of this CTA's input channels ----
+    const int per_warp = (nrows + kWarps - 1) / kWarps;
+    const int w0 = warp * per_warp;
+    const int w1 = min(nrows, w0 + per_warp);
+    float xv[kLaneSlots], xv2[kLaneSlots];
+    int pos[kLaneSlots];
+    bool act[kLaneSlots];
+    int wtotal = 0;
+#pragma unroll
+    for (int s = 0; s < kLaneSlots; ++s) {
+        const int r = w0 + s * 32 + lane;
+        bool a = false;
+        float v = 0.f, v2 = 0.f;
+        if (r < w1) {
+            const __half h = p.x[z0 + r];
+            const __half m = __habs(h);
+            const bool a1 = __hgt(m, thr_h);
+            const bool a2 = kSwiglu ? __hgt(m, thr2_h) : a1;
+            a = a1 || a2;
+            const float f = __half2float(h);
+            v = a1 ? f : 0.f;
+            v2 = a2 ? f : 0.f;
+        }
+        const unsigned b = __ballot_sync(0xffffffffu, a);
+        pos[s] = wtotal + __popc(b & ((1u << lane) - 1u));
+        act[s] = a;
+        xv[s] = v;
+        xv2[s] = v2;
+        wtotal += __popc(b);
+    }
+    if (lane == 0) s_wcount[warp] = wtotal;
+    __syncthreads();
+    int base = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const int c = s_wcount[w];
+        if (w < warp) base += c;
+        total += c;
+    }
+#pragma unroll
+    for (int s = 0; s < kLaneSlots; ++s) {
+        if (act[s]) {
+            const int e = base + pos[s];
+            s_row[e] = (uint16_t)(w0 + s * 32 + lane);
+            s_x[e] = xv[s];
+            if (kSwiglu) s_x2[e] = xv2[s];
+        }
+    }
+    __syncthreads();
+
+    // ---- stream the active weight rows ----
+    const int col0 = slice * kColsPerCta + lane * 8;
+    const bool col_ok = col0 < p.N;   // N % 8 == 0: a lane's 8 columns are all in or all out
+    const size_t ldw = (size_t)p.N;
+    const __half* wbase = p.Wt + (size_t)z0 * ldw + col0;
+    const __half* wbase2 = kSwiglu ? p.Wt2 + (size_t)z0 * ldw + col0 : nullptr;
+
+    float acc[8], acc2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = acc2[j] = 0.f;
+
+    if (col_ok) {
+        for (int e0 = warp; e0 < total; e0 += kWarps * kUnroll) {
+            uint4 w[kUnroll], w2[kSwiglu ? kUnroll : 1];
+            float xs[kUnroll], xs2[kSwiglu ? kUnroll : 1];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int e = e0 + u * kWarps;
+                if (e < total) {
+                    const size_t off = (size_t)s_row[e] * ldw;
+                    w[u] = ld_stream_16(wbase + off);
+                    xs[u] = s_x[e];
+                    if (kSwiglu) {
+                        w2[u] = ld_stream_16(wbase2 + off);
+                        xs2[u] = s_x2[e];
+                    }
+                } else {
+                    w[u] = make_uint4(0, 0, 0, 0);
+                    xs[u] = 0.f;
+                    if (kSwiglu) {
+                        w2[u] = make_uint4(0, 0, 0, 0);
+                        xs2[u] = 0.f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                fma8(acc, w[u], xs[u]);
+                if (kSwiglu) fma8(acc2, w2[u], xs2[u]);
+            }
+        }
+    }
+
+    // ---- CTA reduction over the 8 warps (fixed order) ----
+    {
+        float4* d = reinterpret_cast<float4*>(&s_red[warp][0][lane * 8]);
+        d[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        d[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        if (kSwiglu) {
+            float4* d2 = reinterpret_cast<float4*>(&s_red[warp][kArrays - 1][lane * 8]);
+            d2[0] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
+            d2[1] = make_float4(acc2[4], acc2[5], acc2[6], acc2[7]);
+        }
+    }
+    __syncthreads();
+    float sum = 0.f, sum2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        sum += s_red[w][0][tid];
+        if (kSwiglu) sum2 += s_red[w][kArrays - 1][tid];
+    }
+
+    const int col = slice * kColsPerCta + tid;
+    const int npad = p.n_slices * kColsPerCta;
+
+    if (p.active_elems != nullptr && tid == 0) {
+        const int cols_here = min(kColsPerCta, p.N - slice * kColsPerCta);
+        atomicAdd(p.active_elems, (unsigned long long)total * cols_here * kArrays);
+    }
+
+    if (p.k_splits > 1) {
+        float* mine = p.partials + ((size_t)blockIdx.y * kArrays) * npad + col;
+        mine[0] = sum;
+        if (kSwiglu) mine[npad] = sum2;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int prev = atomicAdd(&p.counters[slice], 1);
+            s_last = (prev == p.k_splits - 1);
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        sum = 0.f;
+        sum2 = 0.f;
+        for (int k = 0; k < p.k_splits; ++k) {
+            const float* src = p.partials + ((size_t)k * kArrays) * npad + col;
+            sum += ld_cg_f32(src);
+            if (kSwiglu) sum2 += ld_cg_f32(src + npad);
+        }
+        if (tid == 0) p.counters[slice] = 0;   // leave the workspace ready for the next launch
+    }
+
+    if (col >= p.N) return;
+    if (kSwiglu) {
+        // Rounding points of the two-GEMV + act_fn(gate)*up path: fp16 gate, fp16 up,
+        // silu evaluated in fp32 and rounded, fp16 product.
+        const __half g16 = __float2half_rn(sum);
+        const __half u16 = __float2half_rn(sum2);
+        const float gf = __half2float(g16);
+        const __half s16 = __float2half_rn(gf / (1.0f + expf(-gf)));
+        p.y[col] = __hmul(s16, u16);
+    } else {
+        __half r = __float2half_rn(sum);
+        if (p.bias != nullptr) r = __hadd(r, p.bias[col]);
+        if (p.residual != nullptr) r = __hadd(p.residual[col], r);
+        p.y[col] = r;
+    }
+}
+
+int check_common(const void* Wt, const void* x, const void* y, int N, int Z) {
+    if (Wt == nullptr || x == nullptr || y == nullptr) return LEANKV_EINVAL;
+    if (N <= 0 || Z <= 0) return LEANKV_EINVAL;
+    if (N % 8 != 0) return LEANKV_EALIGN;
+    if (!aligned16(Wt) || !aligned16(y)) return LEANKV_EALIGN;
+    if ((reinterpret_cast<uintptr_t>(x) & 1u) != 0) return LEANKV_EALIGN;
+    return LEANKV_OK;
+}
+
+int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const leankv_segments_t* segs,
+                const void* bias, const void* residual, void* workspace, size_t workspace_bytes,
+                unsigned long long* active, void* stream) {
+    int rc = check_common(Wt, x, y, N, Z);
+    if (rc != LEANKV_OK) return rc;
+    if (segs == nullptr || segs->n_segments < 1 || segs->n_segments > LEANKV_MAX_SEGMENTS)
+        return LEANKV_EINVAL;
+    int prev = 0;
+    for (int s = 0; s < segs->n_segments; ++s) {
+        const int e = segs->seg_end[s];
+        if (e <= prev) return LEANKV_EINVAL;
+        if (s + 1 < segs->n_segments && e % kColsPerCta != 0) return LEANKV_EALIGN;
+        prev = e;
+    }
+    if (prev != N) return LEANKV_EINVAL;
+
+    const GemvPlan pl = make_plan(N, Z, 1);
+    if (pl.k_splits > 1) {
+        if (workspace == nullptr || workspace_bytes < pl.counter_bytes + pl.partial_bytes)
+            return LEANKV_EWORKSPACE;
+        if (!aligned16(workspace)) return LEANKV_EALIGN;
+    }
+    GemvParams p{};
+    p.Wt = static_cast<const __half*>(Wt);
+    p.Wt2 = nullptr;
+    p.x = static_cast<const __half*>(x);
+    p.y = static_cast<__half*>(y);
+    p.bias = static_cast<const __half*>(bias);
+    p.residual = static_cast<const __half*>(residual);
+    p.counters = static_cast<int*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.counter_bytes);
+    p.active_elems = active;
+    p.N = N;
+    p.Z = Z;
+    p.n_slices = pl.n_slices;
+    p.k_splits = pl.k_splits;
+    p.rows_per_split = pl.rows_per_split;
+    p.n_segments = segs->n_segments;
+    for (int s = 0; s < LEANKV_MAX_SEGMENTS; ++s) {
+        p.seg_end[s] = s < segs->n_segments ? segs->seg_end[s] : N;
+        p.thr[s] = s < segs->n_segments ? segs->threshold[s] : 0.f;
+    }
+    p.thr_up = 0.f;
+    dim3 grid(pl.n_slices, pl.k_splits);
+    sparse_gemv_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}
+
+}  // namespace
+}  // namespace leankv
+
+using namespace leankv;
+
+extern "C" size_t leankv_sparse_gemv_workspace_bytes(int N, int Z) {
+    if (N <= 0 || Z <= 0) return 0;
+    const GemvPlan pl = make_plan(N, Z, 1);
+    return pl.counter_bytes + pl.partial_bytes;
+}
+
+extern "C" size_t leankv_sparse_swiglu_workspace_bytes(int N, int Z) {
+    if (N <= 0 || Z <= 0) return 0;
+    const GemvPlan pl = make_plan(N, Z, 2);
+    return pl.counter_bytes + pl.partial_bytes;
+}
+
+extern "C" int leankv_sparse_gemv_f16(const void* Wt, const void* x, void* y, int N, int Z,
+                                      float threshold, const void* bias, const void* residual,
+                                      void* workspace, size_t workspace_bytes,
+                                      unsigned long long* active_elems, void* stream) {
+    leankv_segments_t segs{};
+    segs.n_segments = 1;
+    segs.seg_end[0] = N;
+    segs.threshold[0] = threshold;
+    return launch_gemv(Wt, x, y, N, Z, &segs, bias, residual, workspace, workspace_bytes,
+                       active_elems, stream);
+}
+
+extern "C" int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y, int N, int Z,
+                                          const leankv_segments_t* segs, const void* bias,
+                                          const void* residual, void* workspace,
+                                          size_t workspace_bytes, unsigned long long* active_elems,
+                                          void* stream) {
+    return launch_gemv(Wt, x, y, N, Z, segs, bias, residual, workspace, workspace_bytes,
+                       active_elems, stream);
+}
+
+extern "C" int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, const void* x,
+                                        void* y, int N, int Z, float t_gate, float t_up,
+                                        void* workspace, size_t workspace_bytes,
+                                        unsigned long long* active_elems, void* stream) {
+    int rc = check_common(Wt_gate, x, y, N, Z);
+    if (rc != LEANKV_OK) return rc;
+    if (Wt_up == nullptr) return LEANKV_EINVAL;
+    if (!aligned16(Wt_up)) return LEANKV_EALIGN;
+    const GemvPlan pl = make_plan(N, Z, 2);
+    if (pl.k_splits > 1) {
+        if (workspace == nullptr || workspace_bytes < pl.counter_bytes + pl.partial_bytes)
+            return LEANKV_EWORKSPACE;
+        if (!aligned16(workspace)) return LEANKV_EALIGN;
+    }
+    GemvParams p{};
+    p.Wt = static_cast<const __half*>(Wt_gate);
+    p.Wt2 = static_cast<const __half*>(Wt_up);
+    p.x = static_cast<const __half*>(x);
+    p.y = static_cast<__half*>(y);
+    p.counters = static_cast<int*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.counter_bytes);
+    p.active_elems = active_elems;
+    p.N = N;
+    p.Z = Z;
+    p.n_slices = pl.n_slices;
+    p.k_splits = pl.k_splits;
+    p.rows_per_split = pl.rows_per_split;
+    p.n_segments = 1;
+    for (int s = 0; s < LEANKV_MAX_SEGMENTS; ++s) {
+        p.seg_end[s] = N;
+        p.thr[s] = t_gate;
+    }
+    p.thr_up = t_up;
+    dim3 grid(pl.n_slices, pl.k_splits);
+    sparse_gemv_kernel<true><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}

@@ -1,0 +1,307 @@
+"""Paged TurboQuant KV cache with fused decode attention (API of ``leankv/turboquant/paged_cache.py``).
+
+The reference class of this name keeps fp16 pages and hands them to FlashInfer. This one
+keeps **3-bit TurboQuant pages** (48 bytes of codes + an fp16 norm per 128-d vector, 16
+tokens per page) and runs decode attention directly on the packed pages with the sm_100a
+kernel behind ``leankv_tq_decode_attn``; FlashInfer is not needed. Page-table conventions
+(``kv_indptr`` / ``kv_page_indices`` / ``kv_last_page_len`` int32, LIFO free list, one
+page table shared by all layers) are the reference's (``paged_cache.py:78,96-115,215-233``).
+
+``update`` appends through the fused rotate+quantize+pack kernel and, for HF
+compatibility, returns dense K/V de-quantized from the pages; ``decode_attention`` is the
+fast path.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native
+from .quantizer import TurboQuantMSE
+
+PAGE = _native.TQ_PAGE_TOKENS
+
+
+class PagedKVCache:
+    """Page pool of 3-bit TurboQuant KV + fused paged decode attention."""
+
+    is_compileable = False
+    layer_type = None
+
+    def __init__(self, num_layers: int = 32, num_kv_heads: int = 8, num_q_heads: int = 32,
+                 head_dim: int = 128, page_size: int = 16, max_pages: int = 2048,
+                 dtype: torch.dtype = torch.float16, device=None, bits: int = 3, seed: int = 42):
+        if head_dim != _native.TQ_DIM or page_size != PAGE or bits != 3:
+            raise RuntimeError("PagedKVCache kernels need head_dim=128, page_size=16, bits=3")
+        self.num_layers = num_layers
+        self.num_kv_heads = num_kv_heads
+        self.num_q_heads = num_q_heads
+        self.head_dim = head_dim
+        self.page_size = page_size
+        self.max_pages = max_pages
+        self.bits = bits
+        self._dtype = dtype
+        self._device = torch.device(device) if device is not None else torch.device("cuda")
+        self._seen_tokens = 0
+
+        # [layer][page][K|V][kv head][800 bytes]; zero pages decode to finite values
+        self.kv_data = torch.zeros(num_layers, max_pages, 2, num_kv_heads, _native.TQ_CHUNK_BYTES,
+                                   dtype=torch.uint8, device=self._device)
+        # same per-layer rotations as TurboQuantCache (seed + 2i for K, seed + 2i + 1 for V)
+        self.key_quantizers = [TurboQuantMSE(head_dim, bits, self._device, torch.float32, seed + 2 * i)
+                               for i in range(num_layers)]
+        self.val_quantizers = [TurboQuantMSE(head_dim, bits, self._device, torch.float32,
+                                             seed + 2 * i + 1) for i in range(num_layers)]
+        self._centroids_host = self.key_quantizers[0].centroids.float().cpu().contiguous()
+        self._bounds = self.key_quantizers[0].decision_boundaries.float().contiguous()
+
+        self._free_pages = list(range(max_pages))
+        self._seq_page_indices: list[list[int]] = []
+        self._seq_lengths: list[int] = []
+        self._batch_size = 0
+        self._pending_start: list[int] = []   # start positions of the append in flight (per layer pass)
+        self._meta = None                     # device copies of the page table, rebuilt when stale
+        self._workspace = None
+
+    # ── page management ────────────────────────────────────────────────
+
+    def _allocate_page(self) -> int:
+        if not self._free_pages:
+            raise RuntimeError(
+                f"PagedKVCache: out of pages ({self.max_pages} used). "
+                f"Increase max_pages or reduce batch/sequence length.")
+        return self._free_pages.pop()
+
+    def _free_sequence_pages(self, batch_idx: int):
+        self._free_pages.extend(self._seq_page_indices[batch_idx])
+        self._seq_page_indices[batch_idx] = []
+        self._seq_lengths[batch_idx] = 0
+        self._meta = None
+
+    def _ensure_batch_size(self, batch_size: int):
+        while len(self._seq_page_indices) < batch_size:
+            self._seq_page_indices.append([])
+            self._seq_lengths.append(0)
+        self._batch_size = max(self._batch_size, batch_size)
+
+    def _device_meta(self, batch_size: int):
+        """(kv_indptr, kv_page_indices, kv_last_page_len) int32 on the device."""
+        if self._meta is None or self._meta[3] != batch_size:
+            indptr, flat, last = [0], [], []
+            for b in range(batch_size):
+                pages = self._seq_page_indices[b]
+                flat.extend(pages)
+                indptr.append(len(flat))
+                rem = self._seq_lengths[b] % PAGE
+                last.append(rem if rem > 0 else PAGE)
+            mk = lambda v: torch.tensor(v if v else [0], dtype=torch.int32, device=self._device)
+            self._meta = (mk(indptr), mk(flat), mk(last), batch_size)
+        return self._meta[:3]
+
+    # ── appends ────────────────────────────────────────────────────────
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
+               cache_kwargs=None):
+        """Quantize-append ``[B, Hkv, T_new, D]`` K/V of one layer; return dense ``(K, V)``."""
+        self.append(layer_idx, key_states, value_states)
+        return self._gather_kv(layer_idx, key_states.shape[0])
+
+    def append(self, layer_idx: int, key_states: torch.Tensor, value_states: torch.Tensor):
+        """Quantize-append without building dense tensors (use with ``decode_attention``)."""
+        _native.require_cuda(key_states, "key_states")
+        batch, _, t_new, _ = key_states.shape
+        if layer_idx == 0:
+            # the page table is shared by all layers: pages are assigned once per step
+            self._seen_tokens += t_new
+            self._ensure_batch_size(batch)
+            self._pending_start = list(self._seq_lengths[:batch])
+            for b in range(batch):
+                need = math.ceil((self._seq_lengths[b] + t_new) / PAGE)
+                while len(self._seq_page_indices[b]) < need:
+                    self._seq_page_indices[b].append(self._allocate_page())
+                self._seq_lengths[b] += t_new
+            self._meta = None
+        indptr, flat, _ = self._device_meta(batch)
+        start = torch.tensor(self._pending_start[:batch], dtype=torch.int32, device=self._device)
+        k = key_states.to(torch.float16).contiguous()
+        v = value_states.to(torch.float16).contiguous()
+        kq, vq = self.key_quantizers[layer_idx], self.val_quantizers[layer_idx]
+        with torch.cuda.device(self._device):
+            rc = _native.lib().leankv_tq_pool_append(
+                k.data_ptr(), v.data_ptr(), batch, self.num_kv_heads, t_new, kq._consts()[0].data_ptr(),
+                vq._consts()[0].data_ptr(), self._bounds.data_ptr(), self.kv_data[layer_idx].data_ptr(),
+                self.max_pages, indptr.data_ptr(), flat.data_ptr(), start.data_ptr(),
+                _native.current_stream())
+        _native.check(rc, "leankv_tq_pool_append")
+
+    def unpack_sequence(self, layer_idx: int, batch_idx: int, which: int):
+        """Codes (uint8 [Hkv, T, 64], reference nibble format) and norms (fp32 [Hkv, T]) of one sequence."""
+        t = self._seq_lengths[batch_idx]
+        pages = torch.tensor(self._seq_page_indices[batch_idx] or [0], dtype=torch.int32,
+                             device=self._device)
+        idx = torch.empty(self.num_kv_heads, t, 64, dtype=torch.uint8, device=self._device)
+        norms = torch.empty(self.num_kv_heads, t, dtype=torch.float32, device=self._device)
+        with torch.cuda.device(self._device):
+            rc = _native.lib().leankv_tq_pool_unpack(
+                self.kv_data[layer_idx].data_ptr(), self.max_pages, self.num_kv_heads,
+                pages.data_ptr(), t, which, idx.data_ptr(), norms.data_ptr(), _native.current_stream())
+        _native.check(rc, "leankv_tq_pool_unpack")
+        return idx, norms
+
+    def _gather_kv(self, layer_idx: int, batch_size: int):
+        """Dense ``[B, Hkv, max_seq, D]`` K and V de-quantized from the pages (zero padded)."""
+        from .quantizer import MSEQuantized
+
+        max_seq = max(self._seq_lengths[:batch_size])
+        keys = torch.zeros(batch_size, self.num_kv_heads, max_seq, self.head_dim, dtype=self._dtype,
+                           device=self._device)
+        values = torch.zeros_like(keys)
+        for b in range(batch_size):
+            t = self._seq_lengths[b]
+            if t == 0:
+                continue
+            for which, quant, dst in ((0, self.key_quantizers[layer_idx], keys),
+                                      (1, self.val_quantizers[layer_idx], values)):
+                idx, norms = self.unpack_sequence(layer_idx, b, which)
+                dst[b, :, :t] = quant.dequantize(MSEQuantized(idx, norms, self.bits)).to(self._dtype)
+        return keys, values
+
+    # ── fused decode attention ─────────────────────────────────────────
+
+    def decode_attention(self, layer_idx: int, query: torch.Tensor) -> torch.Tensor:
+        """``softmax(q K_hat^T / sqrt(d)) V_hat`` over the packed pages; query/out ``[B, Hq, D]``."""
+        _native.require_cuda(query, "query")
+        batch = query.shape[0]
+        indptr, flat, last = self._device_meta(batch)
+        max_pages_seq = max(len(p) for p in self._seq_page_indices[:batch])
+        q = query.to(torch.float16).contiguous()
+        out = torch.empty_like(q)
+        lib = _native.lib()
+        with torch.cuda.device(self._device):
+            need = lib.leankv_tq_decode_attn_workspace_bytes(batch, self.num_q_heads, self.num_kv_heads,
+                                                             max_pages_seq)
+            if self._workspace is None or self._workspace.numel() < need:
+                self._workspace = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=self._device)
+            kq, vq = self.key_quantizers[layer_idx], self.val_quantizers[layer_idx]
+            rc = lib.leankv_tq_decode_attn(
+                q.data_ptr(), out.data_ptr(), batch, self.num_q_heads, self.num_kv_heads,
+                self.kv_data[layer_idx].data_ptr(), self.max_pages, indptr.data_ptr(), flat.data_ptr(),
+                last.data_ptr(), max_pages_seq, kq._consts()[0].data_ptr(), vq._consts()[0].data_ptr(),
+                self._centroids_host.data_ptr(), 1.0 / math.sqrt(self.head_dim),
+                self._workspace.data_ptr(), self._workspace.numel(), _native.current_stream())
+        _native.check(rc, "leankv_tq_decode_attn")
+        return out if query.dtype == torch.float16 else out.to(query.dtype)
+
+    def kernel_status(self) -> int:
+        """Status word of the attention kernel's bounded waits (0 = clean)."""
+        if self._workspace is None:
+            return 0
+        import ctypes
+
+        val = ctypes.c_int(0)
+        _native.check(_native.lib().leankv_tq_decode_attn_status(self._workspace.data_ptr(),
+                                                                 ctypes.byref(val)),
+                      "leankv_tq_decode_attn_status")
+        return val.value
+
+    # ── HF cache surface ───────────────────────────────────────────────
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return max(self._seq_lengths[:self._batch_size]) if self._batch_size > 0 else 0
+
+    def get_mask_sizes(self, query_length: int, layer_idx: int = 0):
+        return self.get_seq_length(layer_idx) + query_length, 0
+
+    def get_max_cache_shape(self, *args, **kwargs):
+        return None
+
+    def get_max_length(self):
+        return self.max_pages * self.page_size
+
+    def has_previous_state(self, layer_idx=None):
+        return any(s > 0 for s in self._seq_lengths)
+
+    def crop(self, max_length):
+        pass
+
+    def batch_repeat_interleave(self, repeats):
+        pass
+
+    def batch_select_indices(self, indices):
+        pass
+
+    def reorder_cache(self, beam_idx):
+        pass
+
+    def reset(self):
+        self._free_pages = list(range(self.max_pages))
+        self._seq_page_indices = []
+        self._seq_lengths = []
+        self._batch_size = 0
+        self._seen_tokens = 0
+        self._meta = None
+        self.kv_data.zero_()
+
+    @property
+    def seen_tokens(self):
+        return self._seen_tokens
+
+    @property
+    def key_cache(self):
+        return [torch.empty(0, device=self._device)] * self.num_layers
+
+    @property
+    def value_cache(self):
+        return [torch.empty(0, device=self._device)] * self.num_layers
+
+    @property
+    def is_initialized(self):
+        return any(s > 0 for s in self._seq_lengths)
+
+    @property
+    def is_sliding(self):
+        return [False] * self.num_layers
+
+    @property
+    def max_batch_size(self):
+        return self._batch_size
+
+    @property
+    def max_cache_len(self):
+        return max(self._seq_lengths) if self._seq_lengths else 0
+
+    def __len__(self):
+        return self.num_layers if any(s > 0 for s in self._seq_lengths) else 0
+
+    def __getitem__(self, layer_idx):
+        return self._gather_kv(layer_idx, self._batch_size)
+
+    def __iter__(self):
+        for i in range(self.num_layers):
+            yield self._gather_kv(i, self._batch_size)
+
+    def __bool__(self):
+        return True
+
+    # ── diagnostics ────────────────────────────────────────────────────
+
+    def get_pages_used(self) -> int:
+        return self.max_pages - len(self._free_pages)
+
+    def bytes_per_page(self) -> int:
+        """Bytes one page occupies in one layer (K and V, all kv heads)."""
+        return 2 * self.num_kv_heads * _native.TQ_CHUNK_BYTES
+
+    def get_memory_usage_mb(self) -> float:
+        return self.get_pages_used() * self.bytes_per_page() * self.num_layers / 1e6
+
+    def get_total_pool_mb(self) -> float:
+        return self.kv_data.numel() * self.kv_data.element_size() / 1e6
+
+    def print_memory_report(self):
+        seq_len = max(self._seq_lengths) if self._seq_lengths else 0
+        print(f"[PagedKVCache] pages={self.get_pages_used()}/{self.max_pages}, "
+              f"pool={self.get_total_pool_mb():.1f} MB, used={self.get_memory_usage_mb():.1f} MB, "
+              f"batch={self._batch_size}, seq_len={seq_len}")
