@@ -1,0 +1,428 @@
+"""Benchmark of the leankv hot paths on B200: batch-1 decode of a Mistral-7B-shaped model with TEAL
+40 % activation sparsity and 3-bit TurboQuant KV, plus per-kernel HBM roofline figures.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step (one token through all layers). ``value`` is tok/s with the token fed
+back on the device (CUDA-graph replays, CUDA-event timing); ``e2e`` is the same loop with the token
+copied host->device before and device->host after every step. With N > 1 (torchrun) the model is
+tensor-parallel over N ranks (fixed total work: strong scaling). ``--impl reference`` times the CPU
+restatement of the reference's PyTorch path (``oracle/``) on the host cores instead.
+Prints exactly one JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "B=1 decode tok/s (Mistral-7B shape)"
+PROMPT_LEN = 512
+SPARSITY = 0.4
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+                 "hw_thermal_slowdown": 0x40, "hw_power_brake": 0x80, "sync_boost": 0x10}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.reasons.update(n for n, b in names.items() if bits & b)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ── CPU baseline: the reference's PyTorch path restated in oracle/, on the host cores ──────────
+
+def cpu_decode_sample(n_steps: int, warmup: int, threads: int, ctx: int = PROMPT_LEN + 128):
+    """Times decode steps of ONE Mistral-7B-shaped layer on the CPU the way the reference runs it:
+    TEAL hook (mask, dense fp16 F.linear) on the seven projections, TurboQuant cache update
+    (quantize the new token, de-quantize the whole cold cache) and attention. A token costs 32 such
+    layers plus the lm_head GEMV; tok/s is extrapolated from the per-layer time."""
+    import torch
+    import torch.nn.functional as F
+
+    from oracle import teal as oteal, turboquant as otq
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(0)
+    H, I, nq, nkv, V = 4096, 14336, 32, 8, 32768
+    w = {n: (torch.randn(o, i, generator=gen) * 0.02).half()
+         for n, (o, i) in dict(q=(nq * 128, H), k=(nkv * 128, H), v=(nkv * 128, H), o=(H, nq * 128),
+                               gate=(I, H), up=(I, H), down=(H, I)).items()}
+    lm_head = (torch.randn(V, H, generator=gen) * 0.02).half()
+    x0 = torch.distributions.Laplace(0.0, 1.0).sample((1, H)).half()
+    cb = otq.lloyd_max(128, 3)
+    bounds = torch.tensor(cb["boundaries"][1:-1])
+    cents = torch.tensor(cb["centroids"])
+    Pi_k, Pi_v = otq.rotation_matrix(128, 42), otq.rotation_matrix(128, 43)
+    kv = torch.randn(2, 1, nkv, ctx, 128, generator=gen)
+    cold = [otq.quantize(kv[i], Pi, bounds, 3)[:2] for i, Pi in ((0, Pi_k), (1, Pi_v))]
+
+    def layer_step(x):
+        t = oteal.threshold_for_sparsity(x, SPARSITY)
+        q = oteal.sparse_linear(x, w["q"], t).reshape(1, nq, 128)
+        k = oteal.sparse_linear(x, w["k"], t).reshape(1, nkv, 1, 128)
+        v = oteal.sparse_linear(x, w["v"], t).reshape(1, nkv, 1, 128)
+        otq.quantize(k.float(), Pi_k, bounds, 3)
+        otq.quantize(v.float(), Pi_v, bounds, 3)
+        k_hat = otq.dequantize(cold[0][0], cold[0][1], Pi_k, cents, 3, 128).half()
+        v_hat = otq.dequantize(cold[1][0], cold[1][1], Pi_v, cents, 3, 128).half()
+        a = otq.kv_attention(q, k_hat, v_hat, 128 ** -0.5).half().reshape(1, nq * 128)
+        h = x + oteal.sparse_linear(a, w["o"], oteal.threshold_for_sparsity(a, SPARSITY))
+        m = oteal.swiglu(h, w["gate"], w["up"], t, t)
+        return h + oteal.sparse_linear(m, w["down"], oteal.threshold_for_sparsity(m, SPARSITY))
+
+    with torch.no_grad():
+        for _ in range(max(warmup, 1)):
+            layer_step(x0)
+        t0 = time.perf_counter()
+        for _ in range(n_steps):
+            layer_step(x0)
+        t_layer = (time.perf_counter() - t0) / n_steps
+        t1 = time.perf_counter()
+        for _ in range(3):
+            F.linear(x0, lm_head)
+        t_head = (time.perf_counter() - t1) / 3
+    tok_s = 1.0 / (32 * t_layer + t_head)
+    sample = (f"{n_steps} decode steps of 1 of 32 layers at {ctx}-token context (7 masked fp16 F.linear, "
+              f"quantize 1 + de-quantize {ctx} tokens x 8 kv heads, attention) + lm_head GEMV; "
+              f"tok/s = 1 / (32 x {t_layer * 1e3:.2f} ms + {t_head * 1e3:.2f} ms)")
+    return tok_s, sample, t_layer
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    steps = max(1, min(args.steps, 64))
+    tok_s, sample, t_layer = cpu_decode_sample(steps, max(args.warmup, 1), threads)
+    line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / tok_s,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": _config(args.gpus),
+            "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def _config(n_gpus):
+    return {"workload": "Mistral-7B-v0.3 shape (32 layers, hidden 4096, inter 14336, 32/8 heads, vocab 32768), "
+                        "random-init fp16, B=1, 512-token prompt then greedy decode, TEAL 40 % thresholds from the "
+                        "prompt's activations, 3-bit TurboQuant paged KV",
+            "parallelism": f"tp{n_gpus}", "prompt_len": PROMPT_LEN, "sparsity": SPARSITY, "kv_bits": 3,
+            "l2": "weights streamed per step (8.7 GB) exceed L2 (126 MB); kernel legs rotate 5 weight copies"}
+
+
+# ── kernel legs: each hot kernel alone on its BASELINE configuration ─────────────────────────
+
+def time_kernel(fn, n_variants: int, iters: int, warmup: int = 5):
+    """Average device time of fn(i % n_variants) over ``iters`` launches (CUDA events, current stream)."""
+    import torch
+
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i % n_variants)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / iters
+
+
+def kernel_legs(dev, peak_gbs):
+    import math
+
+    import torch
+
+    from leankv_b200 import _native, workloads
+
+    lib = _native.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+    copies = 5     # 5 x 117 MB (GEMV) / 5 x 235 MB (SwiGLU) > 126 MB L2
+    # config 1: sparse GEMV 4096 x 14336
+    c = workloads.sparse_gemv_case(device=dev)
+    wts = [c.weight.t().contiguous() for _ in range(copies)]
+    x = c.x.reshape(-1).contiguous()
+    y = torch.empty(4096, dtype=torch.float16, device=dev)
+    ws = torch.zeros(lib.leankv_sparse_gemv_workspace_bytes(4096, 14336) + 256, dtype=torch.uint8, device=dev)
+    fn = lambda i: lib.leankv_sparse_gemv_f16(wts[i].data_ptr(), x.data_ptr(), y.data_ptr(), 4096, 14336,
+                                              c.threshold, None, None, ws.data_ptr(), ws.numel(), None, st)
+    t = time_kernel(fn, copies, 200)
+    alg = c.n_active * 4096 * 2 + 14336 * 2 + 4096 * 2
+    out["sparse_gemv_4096x14336"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
+                                     "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 200}
+    # dense cuBLAS GEMV on the same matrix, for scale (library kernel, not part of the product path)
+    wd = c.weight
+    xd = c.x.reshape(-1, 1).contiguous()
+    t_dense = time_kernel(lambda i: torch.matmul(wd, xd), 1, 50)
+    out["cublas_dense_gemv_4096x14336_us"] = t_dense * 1e6
+    del wts, wd
+    # config 2: fused gate/up SwiGLU 14336 x 4096
+    s = workloads.swiglu_case(device=dev)
+    g = [s.w_gate.t().contiguous() for _ in range(copies)]
+    u = [s.w_up.t().contiguous() for _ in range(copies)]
+    xs = s.x.reshape(-1).contiguous()
+    ys = torch.empty(14336, dtype=torch.float16, device=dev)
+    ws2 = torch.zeros(lib.leankv_sparse_swiglu_workspace_bytes(14336, 4096) + 256, dtype=torch.uint8, device=dev)
+    fn2 = lambda i: lib.leankv_sparse_swiglu_f16(g[i].data_ptr(), u[i].data_ptr(), xs.data_ptr(), ys.data_ptr(),
+                                                 14336, 4096, s.threshold, s.threshold, ws2.data_ptr(),
+                                                 ws2.numel(), None, st)
+    t = time_kernel(fn2, copies, 200)
+    alg = 2 * s.n_active * 14336 * 2 + 4096 * 2 + 14336 * 2
+    out["sparse_swiglu_14336x4096"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
+                                       "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 200}
+    del g, u
+    # config 3: decode attention on packed pages, B=16, 8 kv heads, 4096 tokens; 4 pools rotate
+    from leankv_b200.turboquant import codebook, rotation
+
+    kv = workloads.kv_case(device=dev)
+    B, H, T = 16, 8, 4096
+    Pk = rotation.generate_rotation_matrix(128, dev, torch.float32, 42).contiguous()
+    Pv = rotation.generate_rotation_matrix(128, dev, torch.float32, 43).contiguous()
+    cents, bounds = codebook.get_codebook_tensors(128, 3, "cpu")
+    cents_h = cents.float().contiguous()
+    bounds_d = bounds[1:-1].float().contiguous().to(dev)
+    indptr = torch.arange(0, (B + 1) * 256, 256, dtype=torch.int32, device=dev)
+    flat = kv.page_ids.reshape(-1).contiguous()
+    last = torch.full((B,), 16, dtype=torch.int32, device=dev)
+    start = torch.zeros(B, dtype=torch.int32, device=dev)
+    pools = [torch.zeros(kv.n_pages, 2, H, 800, dtype=torch.uint8, device=dev) for _ in range(4)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for p in pools:
+        lib.leankv_tq_pool_append(kv.k.data_ptr(), kv.v.data_ptr(), B, H, T, Pk.data_ptr(), Pv.data_ptr(),
+                                  bounds_d.data_ptr(), p.data_ptr(), kv.n_pages, indptr.data_ptr(),
+                                  flat.data_ptr(), start.data_ptr(), st)
+    e1.record()
+    torch.cuda.synchronize()
+    t_q = e0.elapsed_time(e1) * 1e-3 / len(pools)
+    alg_q = 2 * B * H * T * (256 + 50)
+    out["tq_bulk_quantize_append_b16_t4096"] = {"us": t_q * 1e6, "algorithmic_bytes": alg_q,
+                                                "gbs": alg_q / t_q / 1e9, "fp32_gflops": 2 * B * H * T * 2 * 128 * 128 / t_q / 1e9,
+                                                "bound": "fp32 FMA"}
+    wsa = torch.zeros(lib.leankv_tq_decode_attn_workspace_bytes(B, 32, H, 256) + 256, dtype=torch.uint8, device=dev)
+    o = torch.empty_like(kv.q)
+    fn3 = lambda i: lib.leankv_tq_decode_attn(kv.q.data_ptr(), o.data_ptr(), B, 32, H, pools[i].data_ptr(),
+                                              kv.n_pages, indptr.data_ptr(), flat.data_ptr(), last.data_ptr(),
+                                              256, Pk.data_ptr(), Pv.data_ptr(), cents_h.data_ptr(),
+                                              1.0 / math.sqrt(128.0), wsa.data_ptr(), wsa.numel(), st)
+    t = time_kernel(fn3, len(pools), 200)
+    alg = 2 * B * H * T * 50 + 2 * B * 32 * 128 * 2 + 4 * (B * 256 + 2 * B + 1)
+    out["tq_decode_attn_b16_t4096"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
+                                       "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 400,
+                                       "note": "two launches per call: query rotation + attention"}
+    return out
+
+
+# ── main leg: the decode loop ─────────────────────────────────────────────────────────────
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from leankv_b200 import _native
+    from leankv_b200.engine import DecodeEngine, DecoderConfig
+
+    _native.lib()   # fail loudly if the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    K, W = args.steps, args.warmup
+    cfg = DecoderConfig.mistral_7b() if not args.small else DecoderConfig(
+        vocab_size=4096, hidden_size=1024, intermediate_size=2048, num_layers=4, num_q_heads=8 * world,
+        num_kv_heads=2 * world)
+    max_seq = PROMPT_LEN + W + K + 32
+    eng = DecodeEngine.random_init(cfg, dev, seed=0, tp_rank=rank, tp_size=world, group=group,
+                                   max_seq_len=max_seq)
+    gen = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=gen).tolist()
+    eng.calibrate_thresholds(prompt, SPARSITY)
+    peak_gbs, peak_src = _peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_steps(host_io: bool):
+        """W warm-up + K timed decode steps after a fresh prefill; returns (seconds, clocks)."""
+        eng.prefill(prompt)
+        if eng.graph is None:
+            eng.capture()
+        pinned_in = torch.zeros(1, dtype=torch.int64).pin_memory()
+        pinned_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+        pinned_in.copy_(eng.token.cpu())
+        for _ in range(W):
+            eng.graph.replay()
+        torch.cuda.synchronize()
+        pinned_in.copy_(eng.token.cpu())
+        eng.active_elems.zero_()
+        sampler = ClockSampler(local)
+        barrier()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(K):
+            if host_io:
+                eng.token.copy_(pinned_in, non_blocking=True)       # H2D: this step's input token
+            eng.graph.replay()
+            if host_io:
+                pinned_out.copy_(eng.token, non_blocking=True)      # D2H: this step's result
+                torch.cuda.current_stream().synchronize()
+                pinned_in[0] = pinned_out[0]
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        sampler.stop()
+        barrier()
+        sec = wall if host_io else e0.elapsed_time(e1) * 1e-3
+        if world > 1:
+            tsec = torch.tensor([sec], dtype=torch.float64, device=dev)
+            dist.all_reduce(tsec, op=dist.ReduceOp.MAX)
+            sec = float(tsec.item())
+        return sec, sampler.summary()
+
+    sec, clocks = timed_steps(host_io=False)
+    streamed = eng.bytes_streamed()
+    launches = eng.launches_per_step * K
+    sec_e2e, _ = timed_steps(host_io=True)
+
+    # the same engine with TEAL off (every weight column streamed): the dense-fp16 comparison point
+    sparse_thresholds = [dict(t) for t in eng.thresholds]
+    eng.set_thresholds(None)
+    sec_dense, _ = timed_steps(host_io=False)
+    dense_streamed = eng.bytes_streamed()
+    eng.set_thresholds({l: t for l, t in enumerate(sparse_thresholds)})
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ctx_mid = PROMPT_LEN + W + K // 2
+    kv_bytes = eng.kv_bytes_per_token() * ctx_mid                       # read per step, this rank
+    step_bytes = streamed / K + kv_bytes
+    line = {
+        "metric": METRIC, "value": K / sec, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": sec / K * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic", "config": _config(world), "clocks": clocks,
+        "e2e": {"value": K / sec_e2e, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+        "gpu_launches": launches,
+        "step": {"weight_bytes_streamed_per_step_per_gpu": streamed / K, "kv_bytes_per_step_per_gpu": kv_bytes,
+                 "gbs_per_gpu": step_bytes / (sec / K) / 1e9, "frac_of_peak": step_bytes / (sec / K) / 1e9 / peak_gbs,
+                 "launches_per_step": eng.launches_per_step,
+                 "dense_same_engine_tok_s": K / sec_dense,
+                 "dense_weight_bytes_per_step_per_gpu": dense_streamed / K,
+                 "speedup_vs_dense_same_engine": sec_dense / sec},
+    }
+    if world == 1 and not args.small:
+        del eng
+        torch.cuda.empty_cache()
+        legs = kernel_legs(dev, peak_gbs)
+        g = legs["sparse_gemv_4096x14336"]
+        line["roofline"] = {"bound": "hbm", "kernel": "sparse_gemv_kernel<false> (config 1: 4096 x 14336, 40 % sparse)",
+                            "achieved": g["gbs"], "peak": peak_gbs, "unit": "GB/s", "frac": g["frac"],
+                            "traffic": None, "peak_source": peak_src,
+                            "algorithmic_bytes_per_launch": g["algorithmic_bytes"], "us_per_launch": g["us"]}
+        line["kernels"] = legs
+        if not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tok_s, sample, _ = cpu_decode_sample(8, 2, threads)
+            line["cpu_baseline"] = {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": sample}
+    else:
+        line["roofline"] = {"bound": "hbm", "kernel": "whole decode step (all kernels)", "achieved": line["step"]["gbs_per_gpu"],
+                            "peak": peak_gbs, "unit": "GB/s", "frac": line["step"]["frac_of_peak"], "traffic": None,
+                            "peak_source": peak_src}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--small", action="store_true", help="tiny model (functional check, not a benchmark)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -186,8 +186,10 @@ int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
  *   [4]            kv_last_page_len after this append
  *   [5]            start_pos of this append
  * ------------------------------------------------------------------------- */
-/* y = weight * fp16(x * rsqrt(mean(x^2) + eps)); fp16 [n], one vector. */
-int leankv_rmsnorm_f16(const void* x, const void* weight, void* y, int n, float eps, void* stream);
+/* If delta != NULL: x += delta first (fp16 add, written back: the residual stream).
+ * Then y = weight * fp16(x * rsqrt(mean(x^2) + eps)); fp16 [n], one vector. */
+int leankv_rmsnorm_f16(void* x, const void* delta, const void* weight, void* y, int n, float eps,
+                       void* stream);
 /* h = embed_table[*token]; state[2..5] derived from state[0]. hidden % 8 == 0. */
 int leankv_decode_begin(const void* embed_table, const long long* token, void* h, int hidden,
                         int vocab, int32_t* state, void* stream);

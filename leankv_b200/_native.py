@@ -60,7 +60,7 @@ SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_float, c_void_p, c_size_t, c_void_p]),
     "leankv_tq_decode_attn_status": (c_int, [c_void_p, POINTER(c_int)]),
-    "leankv_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "leankv_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "leankv_decode_begin": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "leankv_rope_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                 c_void_p]),

@@ -26,13 +26,19 @@ __device__ __forceinline__ float block_sum(float v, float* s_tmp) {
     return t;
 }
 
-// y = w * fp16( x * rsqrt(mean(x^2) + eps) ), statistics in fp32.
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(const __half* x, const __half* w, __half* y,
-                                                       int n, float eps) {
+// Optional residual update h += delta (fp16 add, as the decoder block does), then
+// y = w * fp16( h * rsqrt(mean(h^2) + eps) ), statistics in fp32.
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(__half* x, const __half* delta, const __half* w,
+                                                       __half* y, int n, float eps) {
     __shared__ float s_tmp[32];
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = __half2float(x[i]);
+        __half hv = x[i];
+        if (delta != nullptr) {
+            hv = __hadd(hv, delta[i]);
+            x[i] = hv;
+        }
+        const float v = __half2float(hv);
         ss = fmaf(v, v, ss);
     }
     const float tot = block_sum(ss, s_tmp);
@@ -114,11 +120,12 @@ __global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, 
 
 using namespace leankv;
 
-extern "C" int leankv_rmsnorm_f16(const void* x, const void* weight, void* y, int n, float eps,
-                                  void* stream) {
+extern "C" int leankv_rmsnorm_f16(void* x, const void* delta, const void* weight, void* y, int n,
+                                  float eps, void* stream) {
     if (!x || !weight || !y || n <= 0) return LEANKV_EINVAL;
     rmsnorm_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(x), static_cast<const __half*>(weight), static_cast<__half*>(y), n, eps);
+        static_cast<__half*>(x), static_cast<const __half*>(delta), static_cast<const __half*>(weight),
+        static_cast<__half*>(y), n, eps);
     LEANKV_CUDA_TRY(cudaGetLastError());
     return LEANKV_OK;
 }

@@ -38,7 +38,7 @@ constexpr int kStages = 4;
 constexpr int kGroup = 4;                     // query heads per kv head
 constexpr int kPartialFloats = kGroup * kDim + 2 * kGroup;
 constexpr int kMaxChunks = 64;
-constexpr int kSpinLimit = 1 << 22;
+constexpr int kSpinLimit = 1 << 20;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // status bits written to the workspace status word

@@ -1,0 +1,154 @@
+"""The CUDA-graph decode loop against HuggingFace + the oracle's TEAL hooks and TurboQuant cache on the same weights."""
+
+import pytest
+import torch
+
+from conftest import rel_l2
+from leankv_b200.engine import DecodeEngine, DecoderConfig, PROJ_NAMES
+from leankv_b200.turboquant.cache import TurboQuantCache
+from oracle import teal as oteal, turboquant as otq
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _hf_model(layers=2):
+    from transformers import MistralConfig, MistralForCausalLM
+
+    torch.manual_seed(0)
+    cfg = MistralConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
+                        num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                        max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-5,
+                        tie_word_embeddings=False)
+    model = MistralForCausalLM(cfg)
+    for p in model.parameters():            # larger weights: logits far from uniform
+        if p.dim() == 2:
+            p.data.mul_(3.0)
+    return model.half().to(_dev()).eval()
+
+
+class OracleCache(TurboQuantCache):
+    """Quantize-on-append cache built from the oracle's torch restatement (fp16 norms, like the pool)."""
+
+    def __init__(self, num_layers, device):
+        super().__init__(bits=3, head_dim=128, num_layers=num_layers, hot_buffer_size=0, device=device)
+        self.store = [None] * num_layers
+
+    def update(self, key_states, value_states, layer_idx, cache_kwargs=None):
+        if layer_idx == 0:
+            self._seen_tokens += key_states.shape[2]
+        self._seq_lengths[layer_idx] += key_states.shape[2]
+        outs = []
+        for which, x, quant in ((0, key_states, self.key_quantizers[layer_idx]),
+                                (1, value_states, self.val_quantizers[layer_idx])):
+            packed, norms, _, _ = otq.quantize(x.float(), quant.Pi, quant.decision_boundaries, 3)
+            deq = otq.dequantize(packed, norms.half().float(), quant.Pi, quant.centroids, 3, 128).half()
+            prev = self.store[layer_idx][which] if self.store[layer_idx] is not None else None
+            outs.append(deq if prev is None else torch.cat([prev, deq], dim=2))
+        self.store[layer_idx] = outs
+        return outs[0], outs[1]
+
+
+def _reference_run(model, prompt, n_new, thresholds):
+    """HF forward with the oracle cache; oracle TEAL hooks are active on decode steps only
+    (the reference's kernel mode is dense at prefill, patching.py:178-180)."""
+    cache = OracleCache(model.config.num_hidden_layers, _dev())
+    ids = torch.tensor([prompt], device=_dev())
+    logits, tokens = [], []
+    with torch.no_grad():
+        out = model(ids, past_key_values=cache, use_cache=True)
+        logits.append(out.logits[0, -1].float().cpu())
+        tokens.append(int(out.logits[0, -1].float().argmax()))
+        hooks = []
+        if thresholds is not None:
+            for l, layer in enumerate(model.model.layers):
+                for p in PROJ_NAMES:
+                    mod = getattr(layer.self_attn if p in ("q_proj", "k_proj", "v_proj", "o_proj") else layer.mlp, p)
+                    t = thresholds[l][p]
+                    hooks.append(mod.register_forward_pre_hook(
+                        lambda m, a, t=t: (oteal.sparsify(a[0], t),) + a[1:]))
+        for _ in range(n_new - 1):
+            out = model(torch.tensor([[tokens[-1]]], device=_dev()), past_key_values=cache, use_cache=True)
+            logits.append(out.logits[0, -1].float().cpu())
+            tokens.append(int(out.logits[0, -1].float().argmax()))
+        for h in hooks:
+            h.remove()
+    return tokens, logits
+
+
+def _engine_run(engine, prompt, n_new, follow_tokens=None, use_graph=True):
+    """Step the engine; when ``follow_tokens`` is given, feed those tokens (teacher forcing) so that
+    logits stay comparable even if an argmax near-tie picks another token."""
+    logits, tokens = [], []
+    tokens.append(engine.prefill(prompt))
+    logits.append(engine.prefill_logits.float().cpu())
+    for i in range(n_new - 1):
+        if follow_tokens is not None:
+            engine.token.fill_(follow_tokens[i])
+        engine.step(use_graph=use_graph)
+        torch.cuda.synchronize()
+        logits.append(engine.logits.float().cpu())
+        tokens.append(int(engine.token.item()))
+    return tokens, logits
+
+
+@pytest.mark.parametrize("sparse", [False, True])
+def test_engine_matches_hf_with_oracle_hooks_and_cache(sparse):
+    model = _hf_model()
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 512, (37,), generator=gen).tolist()
+    engine = DecodeEngine.from_hf(model, max_seq_len=128)
+    thresholds = engine.calibrate_thresholds(prompt, 0.4) if sparse else None
+    if sparse:
+        assert set(thresholds[0]) == set(PROJ_NAMES) and all(v > 0 for v in thresholds[1].values())
+    n_new = 24
+    ref_tokens, ref_logits = _reference_run(model, prompt, n_new, thresholds)
+    eng_tokens, eng_logits = _engine_run(engine, prompt, n_new, follow_tokens=ref_tokens)
+    errs = [rel_l2(e, r) for e, r in zip(eng_logits, ref_logits)]
+    print("per-step logits rel-L2:", [f"{e:.1e}" for e in errs])
+    assert max(errs) < 3e-2 and sum(errs) / len(errs) < 1.5e-2
+    agree = sum(int(a == b) for a, b in zip(eng_tokens, ref_tokens)) / n_new
+    assert agree >= 0.75
+    if sparse:
+        # the counter says ~60 % of the projection weights were streamed on the decode steps
+        streamed = engine.bytes_streamed()
+        cfg = engine.cfg
+        per_layer = 2 * (cfg.hidden_size * engine.n_qkv + engine.nq * 128 * cfg.hidden_size
+                         + 3 * cfg.hidden_size * cfg.intermediate_size)
+        dense = (n_new - 1) * (cfg.num_layers * per_layer + 2 * cfg.hidden_size * cfg.vocab_size)
+        assert 0.45 < streamed / dense < 0.85
+
+
+def test_graph_replay_equals_eager_and_generate():
+    model = _hf_model()
+    prompt = list(range(3, 50))
+    a = DecodeEngine.from_hf(model, max_seq_len=128)
+    th = a.calibrate_thresholds(prompt, 0.4)
+    b = DecodeEngine.from_hf(model, max_seq_len=128, thresholds=th)
+    ta, la = _engine_run(a, prompt, 20, use_graph=True)
+    tb, lb = _engine_run(b, prompt, 20, use_graph=False)
+    assert ta == tb
+    assert all(torch.equal(x, y) for x, y in zip(la, lb))
+    assert a.generate(prompt, 20, stream_to_host=True) == ta
+    assert a.generate(prompt, 20, stream_to_host=False) == ta
+    assert a.launches_per_step == 2 + 10 * a.cfg.num_layers + 2
+    # the pool holds prompt + generated tokens at 50 bytes per vector
+    assert a.kv_bytes_per_token() == 2 * 2 * 2 * 50
+    with pytest.raises(ValueError):
+        a.prefill(list(range(128)))
+
+
+def test_random_init_engine_runs_and_is_dense_without_thresholds():
+    cfg = DecoderConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_layers=2,
+                        num_q_heads=8, num_kv_heads=2)
+    eng = DecodeEngine.random_init(cfg, _dev(), seed=3, max_seq_len=96)
+    toks = eng.generate(list(range(40)), 16)
+    assert len(toks) == 16 and all(0 <= t < 1024 for t in toks)
+    eng.active_elems.zero_()
+    eng.step()
+    torch.cuda.synchronize()
+    per_layer = 512 * eng.n_qkv + eng.nq * 128 * 512 + 3 * 512 * 1024
+    assert eng.bytes_streamed() == 2 * (2 * per_layer + 512 * 1024)

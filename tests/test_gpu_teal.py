@@ -1,0 +1,197 @@
+"""TEAL sparse GEMV / SwiGLU kernels (through the C ABI) against the oracle and the reference goldens."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+from leankv_b200 import _native, workloads
+from leankv_b200.teal.kernels.sparse_gemv import (batched_sparse_gemm, prepare_weight_for_sparse_gemv,
+                                                  sparse_gemv, sparse_swiglu)
+from oracle import teal as oteal
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3   # rel-L2 bound for fp16 GEMV outputs
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _raw_gemv(wt, x, t, bias=None, residual=None, segs=None):
+    """Direct C-ABI call; returns (y, active_elems)."""
+    lib = _native.lib()
+    z, n = wt.shape
+    y = torch.empty(n, dtype=torch.float16, device=wt.device)
+    ws = torch.zeros(max(lib.leankv_sparse_gemv_workspace_bytes(n, z), 256), dtype=torch.uint8, device=wt.device)
+    cnt = torch.zeros(1, dtype=torch.int64, device=wt.device)
+    st = torch.cuda.current_stream().cuda_stream
+    if segs is None:
+        rc = lib.leankv_sparse_gemv_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), n, z, float(t),
+                                        _native.ptr(bias), _native.ptr(residual), ws.data_ptr(), ws.numel(),
+                                        cnt.data_ptr(), st)
+    else:
+        rc = lib.leankv_sparse_gemv_seg_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), n, z,
+                                            ctypes.byref(segs), _native.ptr(bias), _native.ptr(residual),
+                                            ws.data_ptr(), ws.numel(), cnt.data_ptr(), st)
+    _native.check(rc, "sparse gemv")
+    torch.cuda.synchronize()
+    assert int(ws[:4 * ((n + 255) // 256)].sum()) == 0, "arrival counters must be left zeroed"
+    return y, int(cnt.item())
+
+
+def test_small_and_ragged_cases_vs_reference(golden_teal):
+    for i, (n, z, s, seed) in enumerate(golden_teal["small_cases"]):
+        n, z = int(n), int(z)
+        c = workloads.sparse_gemv_case(n, z, float(s), int(seed), device=_dev())
+        t = float(golden_teal[f"small{i}_threshold"])
+        assert c.threshold == t
+        wt = c.weight.t().contiguous()
+        y, active = _raw_gemv(wt, c.x.reshape(-1).contiguous(), t)
+        mask = golden_teal[f"small{i}_mask"]
+        n_act = int(mask.sum()) if t > 0 else int((c.x != 0).sum())   # t == 0 still skips exact zeros
+        assert active == n_act * n, f"case {i}: mask differs from the reference's"
+        want32 = torch.from_numpy(golden_teal[f"small{i}_y_fp32"]).reshape(-1)
+        if n_act == 0:
+            assert torch.count_nonzero(y) == 0
+            continue
+        assert rel_l2(y.cpu(), want32) < TOL, f"case {i}"
+        # fp16 rounding of an fp32-accumulated sum: at most one fp16 ulp from the fp32 reference
+        ulp = torch.from_numpy(np.spacing(np.abs(want32.numpy()).astype(np.float16)).astype(np.float32))
+        assert torch.all((y.cpu().float() - want32).abs() <= ulp + 1e-7)
+        # the API wrapper gives the same bits
+        y2 = sparse_gemv(c.x.reshape(1, 1, z), prepare_weight_for_sparse_gemv(c.weight), t)
+        assert y2.shape == (1, 1, n) and torch.equal(y2.reshape(-1), y)
+
+
+def test_config1_full_size(golden_teal):
+    c = workloads.sparse_gemv_case(device=_dev())
+    wt = c.weight.t().contiguous()
+    y, active = _raw_gemv(wt, c.x.reshape(-1).contiguous(), c.threshold)
+    assert active == int(golden_teal["c1_n_active"]) * 4096
+    assert rel_l2(y.cpu(), golden_teal["c1_y_fp32"]) < TOL
+    assert rel_l2(y.cpu(), golden_teal["c1_y_fp16"]) < TOL
+    y_again, _ = _raw_gemv(wt, c.x.reshape(-1).contiguous(), c.threshold)
+    assert torch.equal(y, y_again), "fixed-order split-K must be bit-reproducible"
+    # mask monotonicity in the threshold
+    counts = [_raw_gemv(wt, c.x.reshape(-1).contiguous(), t)[1] for t in (0.1, 0.5, 1.0, 3.0, 1e9)]
+    assert counts == sorted(counts, reverse=True) and counts[-1] == 0
+    # linearity in x over a fixed mask: doubling x (and t) doubles y exactly in fp16
+    y2, _ = _raw_gemv(wt, (c.x.reshape(-1) * 2).contiguous(), c.threshold * 2)
+    assert torch.equal(y2, y * 2)
+
+
+def test_config2_fused_swiglu_full_size(golden_teal):
+    c = workloads.swiglu_case(device=_dev())
+    wg, wu = prepare_weight_for_sparse_gemv(c.w_gate), prepare_weight_for_sparse_gemv(c.w_up)
+    y = sparse_swiglu(c.x.reshape(1, 1, -1), wg, wu, c.threshold, c.threshold).reshape(-1)
+    assert rel_l2(y.cpu(), golden_teal["c2_y_fp32"].reshape(-1)) < TOL
+    assert rel_l2(y.cpu(), golden_teal["c2_y_fp16"].reshape(-1)) < TOL
+    # equals two sparse GEMVs + act_fn(gate) * up, the way the reference composes it
+    g = sparse_gemv(c.x.reshape(1, 1, -1), wg, c.threshold)
+    u = sparse_gemv(c.x.reshape(1, 1, -1), wu, c.threshold)
+    assert torch.equal(y, (torch.nn.functional.silu(g) * u).reshape(-1))
+    assert torch.equal(y, sparse_swiglu(c.x.reshape(1, 1, -1), wg, wu, c.threshold, c.threshold).reshape(-1))
+
+
+def test_swiglu_distinct_thresholds_and_ragged():
+    for (n, z, tg, tu, seed) in ((264, 100, 0.2, 0.9, 1), (512, 37, 1.5, 0.1, 2), (8, 3, 0.0, 0.0, 3)):
+        c = workloads.swiglu_case(n, z, 0.4, seed, device=_dev())
+        wg, wu = prepare_weight_for_sparse_gemv(c.w_gate), prepare_weight_for_sparse_gemv(c.w_up)
+        y = sparse_swiglu(c.x.reshape(1, 1, -1), wg, wu, tg, tu).reshape(-1)
+        want = oteal.swiglu(c.x.cpu(), c.w_gate.cpu(), c.w_up.cpu(), tg, tu, accumulate="fp32").reshape(-1)
+        assert rel_l2(y.cpu(), want) < 2 * TOL   # three fp16 roundings on the reference path
+
+
+def test_threshold_is_strict_and_rounded_to_fp16():
+    dev = _dev()
+    z, n = 64, 256
+    w = torch.ones(n, z, dtype=torch.float16, device=dev)
+    wt = w.t().contiguous()
+    x = torch.zeros(z, dtype=torch.float16, device=dev)
+    edge = 1.0 + 2.0 ** -10
+    x[3], x[10], x[20] = edge, -edge, 1.0 + 2.0 ** -9
+    # |x| == t is dropped (strict >)
+    y, active = _raw_gemv(wt, x, edge)
+    assert active == 1 * n and float(y[0]) == pytest.approx(1.0 + 2.0 ** -9, abs=1e-3)
+    # a threshold just below the fp16 value rounds up to it: torch compares in fp16, so do we
+    y, active = _raw_gemv(wt, x, edge - 1e-5)
+    assert active == 1 * n
+    ref = oteal.sparsify(x.cpu(), edge - 1e-5)
+    assert int((ref != 0).sum()) == 1
+    # negative threshold keeps everything non-NaN, including zeros
+    y, active = _raw_gemv(wt, x, -1.0)
+    assert active == z * n
+
+
+def test_segments_bias_residual():
+    dev = _dev()
+    gen = torch.Generator(device="cpu").manual_seed(4)
+    z, n = 300, 1024 + 256 + 512
+    w = (torch.randn(n, z, generator=gen) * 0.05).half().to(dev)
+    x = torch.randn(z, generator=gen).half().to(dev)
+    bias = torch.randn(n, generator=gen).half().to(dev)
+    res = torch.randn(n, generator=gen).half().to(dev)
+    wt = w.t().contiguous()
+    segs = _native.Segments()
+    segs.n_segments = 3
+    ends, thr = (1024, 1280, n), (0.2, 0.8, 1.4)
+    for i in range(3):
+        segs.seg_end[i], segs.threshold[i] = ends[i], thr[i]
+    y, active = _raw_gemv(wt, x, 0.0, segs=segs)
+    start, want_active = 0, 0
+    for e, t in zip(ends, thr):
+        part, a = _raw_gemv(wt[:, start:e].contiguous(), x, t)
+        assert torch.equal(y[start:e], part)
+        want_active += a
+        start = e
+    assert active == want_active
+    yb, _ = _raw_gemv(wt, x, 0.5, bias=bias, residual=res)
+    y0, _ = _raw_gemv(wt, x, 0.5)
+    assert torch.equal(yb, res + (y0 + bias))
+
+
+def test_batched_wrapper_and_dtype():
+    dev = _dev()
+    c = workloads.sparse_gemv_case(520, 264, 0.5, 8, device=dev)
+    w = prepare_weight_for_sparse_gemv(c.weight)
+    xb = torch.stack([c.x.reshape(-1), c.x.reshape(-1) * 0.5, -c.x.reshape(-1)])
+    yb = batched_sparse_gemm(xb, w, c.threshold)
+    assert yb.shape == (3, 520)
+    for i in range(3):
+        want = oteal.sparse_linear(xb[i].cpu().reshape(1, -1), c.weight.cpu(), c.threshold, "fp32")
+        assert rel_l2(yb[i].cpu(), want.reshape(-1)) < TOL
+    y32 = sparse_gemv(c.x.float().reshape(1, 1, -1), w, c.threshold)
+    assert y32.dtype == torch.float32
+    with pytest.raises(ValueError, match="column-major"):
+        sparse_gemv(c.x.reshape(1, 1, -1), c.weight, c.threshold)
+
+
+def test_apply_teal_kernel_mode_matches_hook_mode():
+    from transformers import MistralConfig, MistralForCausalLM
+
+    from leankv_b200.teal import patching
+
+    dev = _dev()
+    torch.manual_seed(0)
+    cfg = MistralConfig(vocab_size=512, hidden_size=256, intermediate_size=768, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                        max_position_embeddings=128)
+    thresholds = {l: {p: 0.25 if p != "down_proj" else 0.02 for p in patching.PROJ_NAMES} for l in range(2)}
+    ids = torch.randint(0, 512, (1, 9), device=dev)
+    logits = {}
+    for mode in ("hook", "kernel", "fused"):
+        torch.manual_seed(0)
+        model = MistralForCausalLM(cfg).half().to(dev).eval()
+        patching.apply_teal(model, thresholds=thresholds, use_triton=(mode != "hook"),
+                            fuse_mlp=(mode == "fused"))
+        with torch.no_grad():
+            out = model(ids[:, :8], use_cache=True)
+            step = model(ids[:, 8:], past_key_values=out.past_key_values, use_cache=True)
+        logits[mode] = step.logits.float().cpu()
+        if mode != "hook":
+            assert model.model.layers[0].mlp.down_proj._teal_patched
+    assert rel_l2(logits["kernel"], logits["hook"]) < 5e-3
+    assert rel_l2(logits["fused"], logits["kernel"]) < 5e-3

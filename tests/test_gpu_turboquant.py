@@ -1,0 +1,259 @@
+"""TurboQuant kernels (through the C ABI) against the exact-order oracle and the reference goldens."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+from gpu_util import RawPool, oracle_attention_from_pool
+from leankv_b200 import workloads
+from leankv_b200.turboquant.cache import TurboQuantCache
+from leankv_b200.turboquant.paged_cache import PagedKVCache
+from leankv_b200.turboquant.quantizer import MSEQuantized, TurboQuantMSE, TurboQuantProd
+from oracle import pool_layout, tq_exact, turboquant as otq
+
+pytestmark = pytest.mark.gpu
+ATTN_TOL = 1e-3   # rel-L2 bound for fp16 attention outputs
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _small_kv(dev="cpu"):
+    return workloads.kv_case(batch=2, n_q_heads=8, n_kv_heads=2, context=70, seed=3, device=dev)
+
+
+def _near_tie_ok(codes, ref_codes, y, margin):
+    """Codes may differ from the reference only where |y - boundary| <= 4 ulp(y)."""
+    diff = codes != ref_codes
+    assert np.all(margin[diff] <= 4 * np.spacing(np.abs(y[diff]).astype(np.float32)))
+    return int(diff.sum())
+
+
+def test_quantize_bit_exact_vs_exact_oracle_and_reference(golden_tq):
+    kv = _small_kv()
+    ties = total = 0
+    for name, seed, x in (("k", 42, kv.k), ("v", 43, kv.v)):
+        quant = TurboQuantMSE(128, 3, _dev(), torch.float32, seed=seed)
+        for xin in (x.to(_dev()), x.float().to(_dev())):          # fp16 and fp32 inputs: same codes
+            q = quant.quantize(xin)
+            assert q.indices.shape == (2, 2, 70, 64) and q.indices.dtype == torch.uint8 and q.bits == 3
+            assert q.norms.dtype == xin.dtype
+            codes = pool_layout.nibbles_to_codes(q.indices.cpu().numpy()).reshape(-1, 128)
+            ex_codes, ex_norms, y, margin = tq_exact.quantize(
+                x.float().numpy().reshape(-1, 128), quant.Pi.cpu().numpy(), golden_tq["decision_boundaries"])
+            assert np.array_equal(codes, ex_codes), "kernel and fixed-order oracle must agree bit for bit"
+            if xin.dtype == torch.float32:
+                assert np.array_equal(q.norms.cpu().numpy().reshape(-1), ex_norms)
+        ref_codes = pool_layout.nibbles_to_codes(golden_tq[f"{name}_indices"]).reshape(-1, 128)
+        ties += _near_tie_ok(codes, ref_codes, y, margin)
+        total += codes.size
+        ref_norms = golden_tq[f"{name}_norms"].reshape(-1)
+        assert np.all(np.abs(ex_norms - ref_norms) <= 2 * np.spacing(ref_norms))
+    print(f"near-tie code differences vs reference: {ties} of {total}")
+    assert ties <= 1
+
+
+def test_dequantize_vs_reference(golden_tq):
+    for name, seed in (("k", 42), ("v", 43)):
+        quant = TurboQuantMSE(128, 3, _dev(), torch.float32, seed=seed)
+        q = MSEQuantized(torch.from_numpy(golden_tq[f"{name}_indices"]).to(_dev()),
+                         torch.from_numpy(golden_tq[f"{name}_norms"]).to(_dev()), 3)
+        out = quant.dequantize(q)
+        assert out.dtype == torch.float32 and out.shape == (2, 2, 70, 128)
+        want = golden_tq[f"{name}_dequant"]
+        assert rel_l2(out.cpu(), want) < 1e-6
+        assert np.max(np.abs(out.cpu().numpy() - want)) < 1e-5
+        exact = tq_exact.dequantize(pool_layout.nibbles_to_codes(golden_tq[f"{name}_indices"]),
+                                    golden_tq[f"{name}_norms"], quant.Pi.cpu().numpy(), golden_tq["centroids"])
+        assert np.array_equal(out.cpu().numpy().reshape(-1, 128), exact)
+        # forward() = quantize then dequantize; ~0.18 relative reconstruction error at 3 bits
+        x = _small_kv().k.float().to(_dev())
+        assert 0.1 < rel_l2(quant(x).cpu(), x.cpu()) < 0.3
+
+
+def test_other_bit_widths_vs_reference(golden_tq):
+    xs = _small_kv().k[0, 0, :9].float().to(_dev())
+    for bits in (1, 2, 4):
+        quant = TurboQuantMSE(128, bits, _dev(), torch.float32, seed=7)
+        q = quant.quantize(xs)
+        assert np.array_equal(q.indices.cpu().numpy(), golden_tq[f"b{bits}_indices"])
+        assert rel_l2(quant.dequantize(q).cpu(), golden_tq[f"b{bits}_dequant"]) < 1e-6
+    prod = TurboQuantProd(128, 3, _dev(), seed=42)       # 2-bit MSE + QJL, smoke only
+    assert rel_l2(prod(xs).cpu(), xs.cpu()) < 0.6
+    # empty and single-vector inputs
+    quant = TurboQuantMSE(128, 3, _dev())
+    q0 = quant.quantize(torch.empty(0, 128, device=_dev()))
+    assert q0.indices.shape == (0, 64) and quant.dequantize(q0).shape == (0, 128)
+    q1 = quant.quantize(torch.zeros(128, device=_dev()))            # zero vector: norm 0, no NaN
+    assert q1.norms.item() == 0.0 and torch.isfinite(quant.dequantize(q1)).all()
+
+
+def _exact_codes(x, Pi, bounds):
+    codes, norms, _, _ = tq_exact.quantize(x.float().cpu().numpy().reshape(-1, 128), Pi.cpu().numpy(),
+                                           bounds.cpu().numpy())
+    return codes, norms
+
+
+def test_pool_append_unpack_chunk_independent():
+    dev = _dev()
+    kv = workloads.kv_case(batch=2, n_q_heads=8, n_kv_heads=2, context=70, seed=5, device=dev)
+    pages_a = [[9, 2, 7, 0, 5], [1, 8, 3, 6, 4]]                    # 5 pages per sequence, shuffled
+    rp = RawPool(10, 2, dev)
+    rp.append(kv.k, kv.v, [0, 5, 10], pages_a[0] + pages_a[1], [0, 0])
+    # the same tokens appended in ragged pieces (prefill 7, then 1, 1, 20, 9, 31, 1) into another pool
+    rq = RawPool(10, 2, dev)
+    pos = 0
+    for piece in (7, 1, 1, 20, 9, 31, 1):
+        rq.append(kv.k[:, :, pos:pos + piece], kv.v[:, :, pos:pos + piece], [0, 5, 10],
+                  pages_a[0] + pages_a[1], [pos, pos])
+        pos += piece
+    assert pos == 70
+    for b in range(2):
+        for which, x, Pi in ((0, kv.k, rp.Pi_k), (1, kv.v, rp.Pi_v)):
+            idx, norms = rp.unpack(pages_a[b], 70, which)
+            idx2, norms2 = rq.unpack(pages_a[b], 70, which)
+            assert np.array_equal(idx, idx2) and np.array_equal(norms, norms2)
+            want_codes, want_norms = _exact_codes(x[b], Pi, rp.bounds)
+            assert np.array_equal(pool_layout.nibbles_to_codes(idx).reshape(-1, 128), want_codes)
+            assert np.array_equal(norms.reshape(-1),
+                                  want_norms.astype(np.float16).astype(np.float32))
+    # the numpy codec reads the raw pool bytes the same way the unpack kernel does
+    raw = rp.pool.cpu().numpy()
+    for which, x, Pi in ((0, kv.k, rp.Pi_k), (1, kv.v, rp.Pi_v)):
+        want_codes, _ = _exact_codes(x[1, 1], Pi, rp.bounds)        # sequence 1, head 1
+        for ordinal, page in enumerate(pages_a[1]):
+            codes, _ = pool_layout.decode_chunk(raw[page, which, 1], which)
+            n = min(16, 70 - 16 * ordinal)
+            assert np.array_equal(codes[:n], want_codes[16 * ordinal:16 * ordinal + n])
+    # pages of sequence 0 were not touched by writes for sequence 1 and vice versa; unused tail is zero
+    last = raw[pages_a[0][4], 0, 0]
+    codes, _ = pool_layout.decode_chunk(last, 0)
+    assert np.all(codes[6:] == 0)
+
+
+def test_decode_attention_small_vs_reference(golden_tq):
+    dev = _dev()
+    kv = _small_kv(dev)
+    lengths = golden_tq["attn_lengths"].tolist()                    # [70, 37]
+    pages = [[3, 0, 6, 2, 7], [5, 1, 4]]
+    rp = RawPool(8, 2, dev)
+    for b in range(2):
+        n = lengths[b]
+        rp.append(kv.k[b:b + 1, :, :n], kv.v[b:b + 1, :, :n], [0, len(pages[b])], pages[b], [0])
+    indptr = [0, 5, 8]
+    flat = pages[0] + pages[1]
+    last = [70 - 64, 37 - 32]
+    out = rp.attention(kv.q, indptr, flat, last)
+    assert rp.status() == 0
+    assert rel_l2(out.cpu(), golden_tq["attn_out"]) < ATTN_TOL
+    want = oracle_attention_from_pool(rp, kv.q, pages, lengths)
+    assert rel_l2(out.cpu(), want) < ATTN_TOL
+    # same answer whatever split-KV partition the grid heuristics pick
+    for max_pages in (5, 8, 64, 300):
+        again = rp.attention(kv.q, indptr, flat, last, max_pages=max_pages)
+        assert rel_l2(again.cpu(), out.cpu()) < 2e-3
+    # an empty sequence yields zeros; a one-token sequence returns that token's value reconstruction
+    out2 = rp.attention(kv.q, [0, 0, 3], pages[1], [16, 37 - 32])
+    assert torch.count_nonzero(out2[0]) == 0
+    assert rel_l2(out2[1].cpu(), out[1].cpu()) < 1e-6
+    one = RawPool(2, 2, dev)
+    one.append(kv.k[:1, :, :1], kv.v[:1, :, :1], [0, 1], [1], [0])
+    o1 = one.attention(kv.q[:1], [0, 1], [1], [1])
+    v_hat = torch.from_numpy(golden_tq["v_dequant_fp16norm_half"])[0, :, 0].float()   # [Hkv, 128]
+    assert rel_l2(o1[0].cpu(), v_hat.repeat_interleave(4, dim=0)) < ATTN_TOL
+
+
+def test_decode_attention_config3_shape():
+    """Batch 16 x 8 kv heads x 4096 tokens, shuffled pages: the benchmark configuration itself."""
+    dev = _dev()
+    kv = workloads.kv_case(device=dev)
+    B, H, T = 16, 8, 4096
+    rp = RawPool(kv.n_pages, H, dev)
+    page_lists = kv.page_ids.cpu().tolist()
+    indptr = [256 * b for b in range(B + 1)]
+    flat = [p for row in page_lists for p in row]
+    rp.append(kv.k, kv.v, indptr, flat, [0] * B)
+    out = rp.attention(kv.q, indptr, flat, [16] * B)
+    assert rp.status() == 0
+    # (a) against the CPU reference path on two of the sequences (codes read back from the pool)
+    for b in (0, 11):
+        want = oracle_attention_from_pool(rp, kv.q[b:b + 1], [page_lists[b]], [T])
+        assert rel_l2(out[b].cpu(), want[0]) < ATTN_TOL
+    # (b) the quantizer the API exposes wrote the same codes into the pool
+    quant = TurboQuantMSE(128, 3, dev, torch.float32, seed=42)
+    q = quant.quantize(kv.k[3])
+    idx, norms = rp.unpack(page_lists[3], T, 0)
+    assert np.array_equal(idx, q.indices.cpu().numpy())
+    assert np.array_equal(norms, q.norms.float().cpu().numpy().astype(np.float16).astype(np.float32))
+    # (c) moving the pages around (new physical ids, same logical order) does not change a bit
+    perm = torch.randperm(kv.n_pages, generator=torch.Generator().manual_seed(1))
+    rp2 = RawPool(kv.n_pages, H, dev)
+    rp2.pool[perm.to(dev)] = rp.pool
+    flat2 = [int(perm[p]) for p in flat]
+    out2 = rp2.attention(kv.q, indptr, flat2, [16] * B)
+    assert torch.equal(out, out2)
+    # (d) bit-reproducible run to run
+    assert torch.equal(out, rp.attention(kv.q, indptr, flat, [16] * B))
+    # (e) softmax of a convex combination: outputs stay inside the value range per coordinate
+    assert torch.isfinite(out).all()
+    # (f) bytes per vector in the pool: 48 code bytes + one fp16 norm
+    assert rp.pool.numel() == 2 * B * H * T * 50
+
+
+def test_turboquant_cache_trace_vs_reference(golden_cache):
+    dev = _dev()
+    steps = golden_cache["steps"].tolist()
+    cache = TurboQuantCache(bits=3, head_dim=128, num_layers=2, hot_buffer_size=4, device=dev,
+                            dtype=torch.float16, seed=42)
+    outs = {}
+    for si, t_new in enumerate(steps):
+        for layer in range(2):
+            k = torch.from_numpy(golden_cache[f"k_in_{si}_{layer}"]).to(dev)
+            v = torch.from_numpy(golden_cache[f"v_in_{si}_{layer}"]).to(dev)
+            outs[layer] = cache.update(k, v, layer)
+    assert cache.get_seq_length(0) == int(golden_cache["seq_length"]) == sum(steps)
+    assert cache._cold_lengths[0] == int(golden_cache["cold_length"])
+    assert cache.get_compressed_memory_bytes() == int(golden_cache["compressed_bytes"])
+    assert cache.get_compression_ratio() == pytest.approx(float(golden_cache["compression_ratio"]))
+    assert cache.get_mask_sizes(1, 0) == (sum(steps) + 1, 0) and len(cache) == 2 and cache.seen_tokens == sum(steps)
+    for layer in range(2):
+        K, V = outs[layer]
+        for got, name in ((K, "K_out"), (V, "V_out")):
+            want = torch.from_numpy(golden_cache[f"{name}_{layer}"])
+            assert got.shape == want.shape and got.dtype == torch.float16
+            cold = int(golden_cache["cold_length"])
+            assert torch.equal(got[:, :, cold:].cpu(), want[:, :, cold:])         # hot tokens: untouched fp16
+            assert rel_l2(got[:, :, :cold].cpu(), want[:, :, :cold]) < 1e-4        # cold: fp32 order only
+            assert (got[:, :, :cold].cpu() != want[:, :, :cold]).float().mean() < 2e-2
+    cache.print_memory_report()
+    cache.reset()
+    assert cache.get_seq_length() == 0 and not cache.is_initialized
+
+
+def test_paged_cache_api():
+    dev = _dev()
+    kv = workloads.kv_case(batch=3, n_q_heads=8, n_kv_heads=2, context=50, seed=9, device=dev)
+    cache = PagedKVCache(num_layers=2, num_kv_heads=2, num_q_heads=8, max_pages=16, device=dev)
+    for layer in range(2):
+        K, V = cache.update(kv.k[:, :, :33], kv.v[:, :, :33], layer)           # prefill
+    assert K.shape == (3, 2, 33, 128) and cache.get_pages_used() == 9
+    for t in range(33, 50):                                                     # decode steps
+        for layer in range(2):
+            cache.append(layer, kv.k[:, :, t:t + 1], kv.v[:, :, t:t + 1])
+    assert cache.get_seq_length() == 50 and cache.get_pages_used() == 12
+    out = cache.decode_attention(1, kv.q)
+    assert cache.kernel_status() == 0
+    K, V = cache[1]
+    want = otq.kv_attention(kv.q.cpu(), K.cpu(), V.cpu(), 128 ** -0.5)
+    assert rel_l2(out.cpu(), want) < ATTN_TOL
+    # the dense view equals the reference reconstruction from the same codes (fp16 norms)
+    idx, norms = cache.unpack_sequence(1, 2, 0)
+    ref = otq.dequantize(idx.cpu(), norms.cpu(), cache.key_quantizers[1].Pi.cpu(),
+                         cache.key_quantizers[1].centroids.cpu(), 3, 128)
+    assert rel_l2(K[2].cpu(), ref) < 1e-3
+    with pytest.raises(RuntimeError, match="out of pages"):
+        big = torch.zeros(3, 2, 200, 128, dtype=torch.float16, device=dev)
+        cache.update(big, big, 0)
+    cache.print_memory_report()
