@@ -187,7 +187,7 @@ def time_kernel(fn, n_variants: int, iters: int, warmup: int = 5):
     return e0.elapsed_time(e1) * 1e-3 / iters
 
 
-def kernel_legs(dev, peak_gbs):
+def kernel_legs(dev, peak_gbs, which=("gemv", "swiglu", "attn"), iters=200):
     import math
 
     import torch
@@ -198,6 +198,20 @@ def kernel_legs(dev, peak_gbs):
     st = torch.cuda.current_stream().cuda_stream
     out = {}
     copies = 5     # 5 x 117 MB (GEMV) / 5 x 235 MB (SwiGLU) > 126 MB L2
+    if "gemv" in which:
+        _leg_gemv(out, lib, st, dev, peak_gbs, copies, iters)
+    if "swiglu" in which:
+        _leg_swiglu(out, lib, st, dev, peak_gbs, copies, iters)
+    if "attn" in which:
+        _leg_attn(out, lib, st, dev, peak_gbs, iters)
+    return out
+
+
+def _leg_gemv(out, lib, st, dev, peak_gbs, copies, iters):
+    import torch
+
+    from leankv_b200 import workloads
+
     # config 1: sparse GEMV 4096 x 14336
     c = workloads.sparse_gemv_case(device=dev)
     wts = [c.weight.t().contiguous() for _ in range(copies)]
@@ -206,16 +220,22 @@ def kernel_legs(dev, peak_gbs):
     ws = torch.zeros(lib.leankv_sparse_gemv_workspace_bytes(4096, 14336) + 256, dtype=torch.uint8, device=dev)
     fn = lambda i: lib.leankv_sparse_gemv_f16(wts[i].data_ptr(), x.data_ptr(), y.data_ptr(), 4096, 14336,
                                               c.threshold, None, None, ws.data_ptr(), ws.numel(), None, st)
-    t = time_kernel(fn, copies, 200)
+    t = time_kernel(fn, copies, iters)
     alg = c.n_active * 4096 * 2 + 14336 * 2 + 4096 * 2
     out["sparse_gemv_4096x14336"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
-                                     "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 200}
+                                     "frac": alg / t / 1e9 / peak_gbs, "launches_timed": iters}
     # dense cuBLAS GEMV on the same matrix, for scale (library kernel, not part of the product path)
     wd = c.weight
     xd = c.x.reshape(-1, 1).contiguous()
     t_dense = time_kernel(lambda i: torch.matmul(wd, xd), 1, 50)
     out["cublas_dense_gemv_4096x14336_us"] = t_dense * 1e6
-    del wts, wd
+
+
+def _leg_swiglu(out, lib, st, dev, peak_gbs, copies, iters):
+    import torch
+
+    from leankv_b200 import workloads
+
     # config 2: fused gate/up SwiGLU 14336 x 4096
     s = workloads.swiglu_case(device=dev)
     g = [s.w_gate.t().contiguous() for _ in range(copies)]
@@ -226,13 +246,21 @@ def kernel_legs(dev, peak_gbs):
     fn2 = lambda i: lib.leankv_sparse_swiglu_f16(g[i].data_ptr(), u[i].data_ptr(), xs.data_ptr(), ys.data_ptr(),
                                                  14336, 4096, s.threshold, s.threshold, ws2.data_ptr(),
                                                  ws2.numel(), None, st)
-    t = time_kernel(fn2, copies, 200)
+    t = time_kernel(fn2, copies, iters)
     alg = 2 * s.n_active * 14336 * 2 + 4096 * 2 + 14336 * 2
     out["sparse_swiglu_14336x4096"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
-                                       "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 200}
-    del g, u
-    # config 3: decode attention on packed pages, B=16, 8 kv heads, 4096 tokens; 4 pools rotate
+                                       "frac": alg / t / 1e9 / peak_gbs, "launches_timed": iters}
+
+
+def _leg_attn(out, lib, st, dev, peak_gbs, iters):
+    import math
+
+    import torch
+
+    from leankv_b200 import workloads
     from leankv_b200.turboquant import codebook, rotation
+
+    # config 3: decode attention on packed pages, B=16, 8 kv heads, 4096 tokens; 4 pools rotate
 
     kv = workloads.kv_case(device=dev)
     B, H, T = 16, 8, 4096
@@ -265,12 +293,11 @@ def kernel_legs(dev, peak_gbs):
                                               kv.n_pages, indptr.data_ptr(), flat.data_ptr(), last.data_ptr(),
                                               256, Pk.data_ptr(), Pv.data_ptr(), cents_h.data_ptr(),
                                               1.0 / math.sqrt(128.0), wsa.data_ptr(), wsa.numel(), st)
-    t = time_kernel(fn3, len(pools), 200)
+    t = time_kernel(fn3, len(pools), iters)
     alg = 2 * B * H * T * 50 + 2 * B * 32 * 128 * 2 + 4 * (B * 256 + 2 * B + 1)
     out["tq_decode_attn_b16_t4096"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
-                                       "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 400,
+                                       "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 2 * iters,
                                        "note": "two launches per call: query rotation + attention"}
-    return out
 
 
 # ── main leg: the decode loop ─────────────────────────────────────────────────────────────
@@ -353,6 +380,14 @@ def run_ours(args):
     sec, clocks = timed_steps(host_io=False)
     streamed = eng.bytes_streamed()
     launches = eng.launches_per_step * K
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": K / sec, "unit": "tok/s", "n_gpus": world, "steps": K,
+                              "warmup": W, "ms_per_step": sec / K * 1e3, "quick": True,
+                              "launches_per_step": eng.launches_per_step}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     sec_e2e, _ = timed_steps(host_io=True)
 
     # the same engine with TEAL off (every weight column streamed): the dense-fp16 comparison point
@@ -415,11 +450,25 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--small", action="store_true", help="tiny model (functional check, not a benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true",
+                    help="decode loop only: no e2e / dense / kernel / CPU legs (for profiling runs)")
+    ap.add_argument("--only-legs", default="",
+                    help="comma list of gemv,swiglu,attn: run just those kernel legs and print their JSON")
+    ap.add_argument("--leg-iters", type=int, default=200)
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.only_legs:
+        import torch
+
+        from leankv_b200 import _native
+
+        _native.lib()
+        torch.cuda.set_device(0)
+        print(json.dumps(kernel_legs(torch.device("cuda", 0), _peaks()[0], tuple(args.only_legs.split(",")),
+                                     args.leg_iters)))
     else:
         run_ours(args)
 

@@ -273,7 +273,9 @@ __global__ void __launch_bounds__(128) tq_pool_append_kernel(const AppendParams 
             for (int i = 0; i < 64; ++i) xr[i] = 0.f;
         }
         const double mine = sumsq64(xr);
-        const double other = __shfl_xor_sync(0xffffffffu, mine, 1);
+        // only the 2 * kTok lanes inside this branch take part in the exchange
+        constexpr unsigned kPairMask = kTok >= 16 ? 0xffffffffu : ((1u << (2 * kTok)) - 1u);
+        const double other = __shfl_xor_sync(kPairMask, mine, 1);
         const double tot = hf == 0 ? mine + other : other + mine;
         const float norm = (float)sqrt(tot);
         const float denom = norm + 1e-10f;

@@ -437,7 +437,8 @@ class DecodeEngine:
         n = x.numel() // 128
         idx = torch.empty(n, 64, dtype=torch.uint8, device=self.dev)
         norms = torch.empty(n, dtype=torch.float32, device=self.dev)
-        _native.check(self.lib.leankv_tq_quantize(x.contiguous().data_ptr(), 0, n, 128, 3, Pi.data_ptr(),
+        x = x.contiguous()
+        _native.check(self.lib.leankv_tq_quantize(x.data_ptr(), 0, n, 128, 3, Pi.data_ptr(),
                                                   self.bounds.data_ptr(), idx.data_ptr(), norms.data_ptr(),
                                                   self._st()), "quantize")
         norms = norms.half().float()
@@ -464,7 +465,7 @@ class DecodeEngine:
                     parts = [torch.empty_like(a) for _ in range(self.tp_size)]
                     torch.distributed.all_gather(parts, a.contiguous(), group=self.group)
                     a = torch.cat(parts, dim=-1)
-                thresholds[l][p] = compute_threshold_for_sparsity(a, sparsity)
+                thresholds[l][p] = compute_threshold_for_sparsity(a.float(), sparsity)
         self.set_thresholds(thresholds)
         return thresholds
 

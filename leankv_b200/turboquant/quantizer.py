@@ -95,10 +95,17 @@ class TurboQuantMSE(torch.nn.Module):
         self.register_buffer("boundaries", boundaries)
         self.register_buffer("decision_boundaries", boundaries[1:-1].contiguous())
 
-    # kernels take fp32 constants whatever dtype the buffers were created with
     def _consts(self):
-        return (self.Pi.float().contiguous(), self.centroids.float().contiguous(),
-                self.decision_boundaries.float().contiguous())
+        """(Pi, centroids, decision boundaries) as fp32 row-major device tensors for the kernels.
+
+        Cached on the module: callers pass raw pointers to asynchronous launches, so these
+        must not be temporaries that die before the kernel runs."""
+        key = (self.Pi.data_ptr(), self.Pi.device)
+        if getattr(self, "_consts_key", None) != key:
+            self._consts_val = (self.Pi.float().contiguous(), self.centroids.float().contiguous(),
+                                self.decision_boundaries.float().contiguous())
+            self._consts_key = key
+        return self._consts_val
 
     def _check(self, t: torch.Tensor, what: str) -> None:
         _native.require_cuda(t, what)

@@ -18,7 +18,8 @@ def generate_rotation_matrix(d: int, device, dtype: torch.dtype = torch.float32,
     gauss = torch.randn(d, d, generator=gen, dtype=torch.float32)
     q, r = torch.linalg.qr(gauss)
     q = q * torch.sign(torch.diagonal(r)).unsqueeze(0)
-    return q.to(device=device, dtype=dtype)
+    # LAPACK hands Q back column-major; the kernels read Pi row-major, so fix the layout once here
+    return q.contiguous().to(device=device, dtype=dtype)
 
 
 def generate_qjl_matrix(d: int, device, dtype: torch.dtype = torch.float32,

@@ -89,7 +89,7 @@ def pack(codes: torch.Tensor, bits: int) -> torch.Tensor:
     if pad:
         c = torch.nn.functional.pad(c, (0, pad))
     c = c.reshape(*c.shape[:-1], -1, per)
-    out = torch.zeros(c.shape[:-1], dtype=torch.int64)
+    out = torch.zeros(c.shape[:-1], dtype=torch.int64, device=c.device)
     for i in range(per):
         out |= c[..., i] << (width * i)
     return out.to(torch.uint8)
@@ -131,7 +131,8 @@ def kv_attention(q: torch.Tensor, k_hat: torch.Tensor, v_hat: torch.Tensor, scal
     v = v_hat.float().repeat_interleave(rep, dim=1)
     s = torch.einsum("bhd,bhtd->bht", q.float(), k) * scale
     if lengths is not None:
-        mask = torch.arange(T).unsqueeze(0) >= torch.as_tensor(lengths).unsqueeze(1)
+        mask = (torch.arange(T, device=q.device).unsqueeze(0)
+                >= torch.as_tensor(lengths, device=q.device).unsqueeze(1))
         s = s.masked_fill(mask.unsqueeze(1), float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.einsum("bht,bhtd->bhd", p, v)

@@ -33,7 +33,8 @@ class RawPool:
         """k, v: [B, H, T, 128] fp16 on the device; page table / start positions as python lists."""
         B, H, T, _ = k.shape
         ip, ix, sp = self.i32(indptr), self.i32(indices), self.i32(start_pos)
-        rc = self.lib.leankv_tq_pool_append(k.contiguous().data_ptr(), v.contiguous().data_ptr(), B, H, T,
+        k, v = k.contiguous(), v.contiguous()      # keep the copies alive until the launch has been queued
+        rc = self.lib.leankv_tq_pool_append(k.data_ptr(), v.data_ptr(), B, H, T,
                                             self.Pi_k.data_ptr(), self.Pi_v.data_ptr(), self.bounds.data_ptr(),
                                             self.pool.data_ptr(), self.n_pages, ip.data_ptr(), ix.data_ptr(),
                                             sp.data_ptr(), torch.cuda.current_stream().cuda_stream)
@@ -59,9 +60,10 @@ class RawPool:
         need = self.lib.leankv_tq_decode_attn_workspace_bytes(B, Hq, self.H, max_pages)
         if self.ws is None or self.ws.numel() < need:
             self.ws = torch.zeros(need, dtype=torch.uint8, device=self.dev)
+        q = q.contiguous()
         out = torch.empty_like(q)
         ip, ix, ll = self.i32(indptr), self.i32(indices if len(indices) else [0]), self.i32(last_len)
-        rc = self.lib.leankv_tq_decode_attn(q.contiguous().data_ptr(), out.data_ptr(), B, Hq, self.H,
+        rc = self.lib.leankv_tq_decode_attn(q.data_ptr(), out.data_ptr(), B, Hq, self.H,
                                             self.pool.data_ptr(), self.n_pages, ip.data_ptr(), ix.data_ptr(),
                                             ll.data_ptr(), max_pages, self.Pi_k.data_ptr(), self.Pi_v.data_ptr(),
                                             self.centroids_host.data_ptr(), 1.0 / math.sqrt(128.0),

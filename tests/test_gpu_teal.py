@@ -60,7 +60,8 @@ def test_small_and_ragged_cases_vs_reference(golden_teal):
         assert rel_l2(y.cpu(), want32) < TOL, f"case {i}"
         # fp16 rounding of an fp32-accumulated sum: at most one fp16 ulp from the fp32 reference
         ulp = torch.from_numpy(np.spacing(np.abs(want32.numpy()).astype(np.float16)).astype(np.float32))
-        assert torch.all((y.cpu().float() - want32).abs() <= ulp + 1e-7)
+        # (+1e-5: where terms cancel, the two fp32 summation orders differ by more than the tiny result's ulp)
+        assert torch.all((y.cpu().float() - want32).abs() <= ulp + 1e-5)
         # the API wrapper gives the same bits
         y2 = sparse_gemv(c.x.reshape(1, 1, z), prepare_weight_for_sparse_gemv(c.weight), t)
         assert y2.shape == (1, 1, n) and torch.equal(y2.reshape(-1), y)
@@ -185,10 +186,12 @@ def test_apply_teal_kernel_mode_matches_hook_mode():
     for mode in ("hook", "kernel", "fused"):
         torch.manual_seed(0)
         model = MistralForCausalLM(cfg).half().to(dev).eval()
-        patching.apply_teal(model, thresholds=thresholds, use_triton=(mode != "hook"),
-                            fuse_mlp=(mode == "fused"))
         with torch.no_grad():
+            # dense prefill in every mode: the kernel mode of the reference is dense whenever more
+            # than one token is in flight (patching.py:178-180), the hook mode is not
             out = model(ids[:, :8], use_cache=True)
+            patching.apply_teal(model, thresholds=thresholds, use_triton=(mode != "hook"),
+                                fuse_mlp=(mode == "fused"))
             step = model(ids[:, 8:], past_key_values=out.past_key_values, use_cache=True)
         logits[mode] = step.logits.float().cpu()
         if mode != "hook":
