@@ -169,6 +169,16 @@ int leankv_tq_decode_attn(const void* q, void* out, int B, int n_q_heads, int n_
                           const float* centroids /* host, 8 */, float scale,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same attention for a caller that already holds the rotated query q_rot = Pi_k q
+ * (fp32 [B][n_q_heads][128], e.g. from leankv_decode_qkv_post): skips the query-rotation
+ * launch. Everything else as leankv_tq_decode_attn. */
+int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int B, int n_q_heads, int n_kv_heads,
+                                  const void* pool, int n_pages,
+                                  const int32_t* kv_indptr, const int32_t* kv_page_indices,
+                                  const int32_t* kv_last_page_len, int max_pages_per_seq,
+                                  const float* Pi_v, const float* centroids /* host, 8 */, float scale,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* Device status word of the bounded waits inside the attention kernel (0 = no wait
  * ever gave up). Copied to *status with a synchronous 4-byte copy from `workspace`. */
 int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
@@ -197,6 +207,14 @@ int leankv_decode_begin(const void* embed_table, const long long* token, void* h
  * 128-wide heads of a fused qkv row; inv_freq fp32 [64]. */
 int leankv_rope_f16(const void* qkv, const float* inv_freq, const int32_t* state, void* q_out,
                     void* k_out, int n_q_heads, int n_kv_heads, int head_dim, void* stream);
+/* leankv_rope_f16 + leankv_tq_pool_append (one token, one sequence) + the query rotation of
+ * leankv_tq_decode_attn in a single launch, bit-identical to the three: qkv is the fused
+ * projection row [q heads | k heads | v heads] x 128 fp16; the token's position is state[0] and
+ * its page is page_indices[state[0] / 16]; q_rot (fp32 [n_q_heads][128]) receives Pi_k rope(q). */
+int leankv_decode_qkv_post(const void* qkv, const float* inv_freq, const int32_t* state,
+                           const float* Pi_k, const float* Pi_v, const float* decision_boundaries,
+                           void* pool, int n_pages, const int32_t* page_indices,
+                           int n_q_heads, int n_kv_heads, float* q_rot, void* stream);
 /* *token = argmax(logits) (lowest index on ties); history[state[1]] = *token;
  * state[1] += 1; state[0] += 1. */
 int leankv_decode_end(const void* logits, int vocab, long long* token, long long* history,

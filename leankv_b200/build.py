@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 BUILD_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libleankv_b200.so")
 
-SOURCES = ["capi.cu", "teal_gemv.cu", "tq_quantize.cu", "tq_attn.cu", "decoder_ops.cu"]
+SOURCES = ["capi.cu", "teal_gemv.cu", "tq_quantize.cu", "tq_attn.cu", "decoder_ops.cu", "decode_fused.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -28,23 +28,58 @@ __device__ __forceinline__ float block_sum(float v, float* s_tmp) {
 
 // Optional residual update h += delta (fp16 add, as the decoder block does), then
 // y = w * fp16( h * rsqrt(mean(h^2) + eps) ), statistics in fp32.
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(__half* x, const __half* delta, const __half* w,
-                                                       __half* y, int n, float eps) {
+// One CTA; 16-byte accesses; the (updated) row stays in registers between the two phases
+// (n % 8 == 0, n <= kNormThreads * 8 * kNormVecs).
+constexpr int kNormThreads = 512;
+constexpr int kNormVecs = 4;
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(__half* x, const __half* delta,
+                                                               const __half* w, __half* y, int n, float eps) {
     __shared__ float s_tmp[32];
+    const int nvec = n >> 3;
+    uint4 v[kNormVecs];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        __half hv = x[i];
-        if (delta != nullptr) {
-            hv = __hadd(hv, delta[i]);
-            x[i] = hv;
+#pragma unroll
+    for (int it = 0; it < kNormVecs; ++it) {
+        const int i = threadIdx.x + it * kNormThreads;
+        if (i < nvec) {
+            uint4 a = reinterpret_cast<const uint4*>(x)[i];
+            if (delta != nullptr) {
+                const uint4 d = __ldg(reinterpret_cast<const uint4*>(delta) + i);
+                __half2* ah = reinterpret_cast<__half2*>(&a);
+                const __half2* dh = reinterpret_cast<const __half2*>(&d);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) ah[q] = __hadd2(ah[q], dh[q]);
+                reinterpret_cast<uint4*>(x)[i] = a;
+            }
+            v[it] = a;
+            const __half2* ah = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = __half22float2(ah[q]);
+                ss = fmaf(f.x, f.x, ss);
+                ss = fmaf(f.y, f.y, ss);
+            }
         }
-        const float v = __half2float(hv);
-        ss = fmaf(v, v, ss);
     }
     const float tot = block_sum(ss, s_tmp);
     const float r = rsqrtf(tot / (float)n + eps);
-    for (int i = threadIdx.x; i < n; i += blockDim.x)
-        y[i] = __hmul(w[i], __float2half_rn(__half2float(x[i]) * r));
+#pragma unroll
+    for (int it = 0; it < kNormVecs; ++it) {
+        const int i = threadIdx.x + it * kNormThreads;
+        if (i < nvec) {
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + i);
+            const __half2* ah = reinterpret_cast<const __half2*>(&v[it]);
+            const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = __half22float2(ah[q]);
+                oh[q] = __hmul2(wh[q], __floats2half2_rn(f.x * r, f.y * r));
+            }
+            reinterpret_cast<uint4*>(y)[i] = o;
+        }
+    }
 }
 
 // Fetch the embedding row of the current token and derive this step's page-table words.
@@ -123,7 +158,10 @@ using namespace leankv;
 extern "C" int leankv_rmsnorm_f16(void* x, const void* delta, const void* weight, void* y, int n,
                                   float eps, void* stream) {
     if (!x || !weight || !y || n <= 0) return LEANKV_EINVAL;
-    rmsnorm_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+    if (n % 8 != 0 || !aligned16(x) || !aligned16(weight) || !aligned16(y) || (delta && !aligned16(delta)))
+        return LEANKV_EALIGN;
+    if (n > kNormThreads * 8 * kNormVecs) return LEANKV_ELIMIT;
+    rmsnorm_kernel<<<1, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<__half*>(x), static_cast<const __half*>(delta), static_cast<const __half*>(weight),
         static_cast<__half*>(y), n, eps);
     LEANKV_CUDA_TRY(cudaGetLastError());

@@ -244,12 +244,42 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
         __syncthreads();
         if (!s_last) return;
         __threadfence();
+        // Final merge, spread over the whole CTA so that it costs a couple of L2 round trips
+        // instead of k_splits: warp w sums splits w, w+8, ... (ascending) for all 256 columns,
+        // then the 8 warp sums are added in warp order. The order is fixed, so the result is too.
+        {
+            float m[8], m2[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m[j] = m2[j] = 0.f;
+            const float* base = p.partials + slice * kColsPerCta + lane * 8;
+#pragma unroll 4
+            for (int k = warp; k < p.k_splits; k += kWarps) {
+                const float* src = base + ((size_t)k * kArrays) * npad;
+                const float4 a = ld_cg_f32x4(src), b = ld_cg_f32x4(src + 4);
+                m[0] += a.x; m[1] += a.y; m[2] += a.z; m[3] += a.w;
+                m[4] += b.x; m[5] += b.y; m[6] += b.z; m[7] += b.w;
+                if (kSwiglu) {
+                    const float4 c = ld_cg_f32x4(src + npad), d = ld_cg_f32x4(src + npad + 4);
+                    m2[0] += c.x; m2[1] += c.y; m2[2] += c.z; m2[3] += c.w;
+                    m2[4] += d.x; m2[5] += d.y; m2[6] += d.z; m2[7] += d.w;
+                }
+            }
+            float4* d = reinterpret_cast<float4*>(&s_red[warp][0][lane * 8]);
+            d[0] = make_float4(m[0], m[1], m[2], m[3]);
+            d[1] = make_float4(m[4], m[5], m[6], m[7]);
+            if (kSwiglu) {
+                float4* d2 = reinterpret_cast<float4*>(&s_red[warp][kArrays - 1][lane * 8]);
+                d2[0] = make_float4(m2[0], m2[1], m2[2], m2[3]);
+                d2[1] = make_float4(m2[4], m2[5], m2[6], m2[7]);
+            }
+        }
+        __syncthreads();
         sum = 0.f;
         sum2 = 0.f;
-        for (int k = 0; k < p.k_splits; ++k) {
-            const float* src = p.partials + ((size_t)k * kArrays) * npad + col;
-            sum += ld_cg_f32(src);
-            if (kSwiglu) sum2 += ld_cg_f32(src + npad);
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            sum += s_red[w][0][tid];
+            if (kSwiglu) sum2 += s_red[w][kArrays - 1][tid];
         }
         if (tid == 0) p.counters[slice] = 0;   // leave the workspace ready for the next launch
     }

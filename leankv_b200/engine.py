@@ -119,6 +119,8 @@ class DecodeEngine:
         self.h, self.x = half(cfg.hidden_size), half(cfg.hidden_size)
         self.qkv, self.q_rope, self.k_rope = half(self.n_qkv), half(self.nq * 128), half(self.nkv * 128)
         self.attn, self.o = half(self.nq * 128), half(cfg.hidden_size)
+        self.q_rot = torch.zeros(self.nq * 128, dtype=torch.float32, device=dev)
+        self.fused_post = True   # False: rope / append / query rotation as separate launches
         self.mlp_h, self.down = half(self.inter), half(cfg.hidden_size)
         self.logits = half(cfg.vocab_size)
         self.token = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -279,18 +281,27 @@ class DecodeEngine:
             torch.distributed.all_reduce(t, group=self.group)
             self.launches_per_step += 1
 
-    def _step_launches(self) -> None:
-        """One decode step: consumes ``self.token`` at position state[0], leaves the next token there."""
+    def _layer_launches(self, l: int) -> None:
+        """Block ``l`` of one decode step: expects ``self.x`` = input-normed hidden state and the decode
+        state words set; leaves the residual stream in ``self.h`` and the next norm's output in ``self.x``."""
         cfg, lib, st = self.cfg, self.lib, self._st
         sp = self.state.data_ptr()
-        self.launches_per_step = 0
-        _native.check(lib.leankv_decode_begin(self.w["embed"].data_ptr(), self.token.data_ptr(), self.h.data_ptr(),
-                                              cfg.hidden_size, cfg.vocab_size, sp, st()), "decode_begin")
-        self.launches_per_step += 1
-        self._norm(None, self.w["layers"][0]["ln1"])
-        for l, lw in enumerate(self.w["layers"]):
-            t = self.thresholds[l]
-            self._gemv(lw["wqkv_t"], self.x, self.qkv, 0.0, self._qkv_segments(l))
+        lw, t = self.w["layers"][l], self.thresholds[l]
+        self._gemv(lw["wqkv_t"], self.x, self.qkv, 0.0, self._qkv_segments(l))
+        if self.fused_post:
+            # rope(q, k) + rotate/quantize/pack of k, v into the page + query rotation: one launch
+            _native.check(lib.leankv_decode_qkv_post(self.qkv.data_ptr(), self.inv_freq.data_ptr(), sp,
+                                                     self.Pi_k[l].data_ptr(), self.Pi_v[l].data_ptr(),
+                                                     self.bounds.data_ptr(), self.pools[l].data_ptr(),
+                                                     self.max_pages, self.page_indices.data_ptr(), self.nq,
+                                                     self.nkv, self.q_rot.data_ptr(), st()), "decode_qkv_post")
+            _native.check(lib.leankv_tq_decode_attn_rotated(
+                self.q_rot.data_ptr(), self.attn.data_ptr(), 1, self.nq, self.nkv, self.pools[l].data_ptr(),
+                self.max_pages, sp + 8, self.page_indices.data_ptr(), sp + 16, self.max_pages,
+                self.Pi_v[l].data_ptr(), self.centroids_host.data_ptr(), 1.0 / math.sqrt(128.0),
+                self.ws_attn.data_ptr(), self.ws_attn.numel(), st()), "decode_attn_rotated")
+            self.launches_per_step += 2
+        else:
             _native.check(lib.leankv_rope_f16(self.qkv.data_ptr(), self.inv_freq.data_ptr(), sp,
                                               self.q_rope.data_ptr(), self.k_rope.data_ptr(), self.nq, self.nkv,
                                               128, st()), "rope")
@@ -308,19 +319,31 @@ class DecodeEngine:
                                                     self.ws_attn.data_ptr(), self.ws_attn.numel(), st()),
                           "decode_attn")
             self.launches_per_step += 4     # rope, append, query rotation, attention
-            self._gemv(lw["wo_t"], self.attn, self.o, t["o_proj"])
-            self._allreduce(self.o)
-            self._norm(self.o, lw["ln2"])
-            rc = lib.leankv_sparse_swiglu_f16(lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), self.x.data_ptr(),
-                                              self.mlp_h.data_ptr(), self.inter, cfg.hidden_size, t["gate_proj"],
-                                              t["up_proj"], self.ws_gemv.data_ptr(), self.ws_gemv.numel(),
-                                              self.active_elems.data_ptr(), st())
-            _native.check(rc, "sparse swiglu")
-            self.launches_per_step += 1
-            self._gemv(lw["wdown_t"], self.mlp_h, self.down, t["down_proj"])
-            self._allreduce(self.down)
-            nxt = self.w["layers"][l + 1]["ln1"] if l + 1 < cfg.num_layers else self.w["final_norm"]
-            self._norm(self.down, nxt)
+        self._gemv(lw["wo_t"], self.attn, self.o, t["o_proj"])
+        self._allreduce(self.o)
+        self._norm(self.o, lw["ln2"])
+        rc = lib.leankv_sparse_swiglu_f16(lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), self.x.data_ptr(),
+                                          self.mlp_h.data_ptr(), self.inter, cfg.hidden_size, t["gate_proj"],
+                                          t["up_proj"], self.ws_gemv.data_ptr(), self.ws_gemv.numel(),
+                                          self.active_elems.data_ptr(), st())
+        _native.check(rc, "sparse swiglu")
+        self.launches_per_step += 1
+        self._gemv(lw["wdown_t"], self.mlp_h, self.down, t["down_proj"])
+        self._allreduce(self.down)
+        nxt = self.w["layers"][l + 1]["ln1"] if l + 1 < cfg.num_layers else self.w["final_norm"]
+        self._norm(self.down, nxt)
+
+    def _step_launches(self) -> None:
+        """One decode step: consumes ``self.token`` at position state[0], leaves the next token there."""
+        cfg, lib, st = self.cfg, self.lib, self._st
+        sp = self.state.data_ptr()
+        self.launches_per_step = 0
+        _native.check(lib.leankv_decode_begin(self.w["embed"].data_ptr(), self.token.data_ptr(), self.h.data_ptr(),
+                                              cfg.hidden_size, cfg.vocab_size, sp, st()), "decode_begin")
+        self.launches_per_step += 1
+        self._norm(None, self.w["layers"][0]["ln1"])
+        for l in range(cfg.num_layers):
+            self._layer_launches(l)
         self._gemv(self.w["lm_head_t"], self.x, self.logits, -1.0)
         _native.check(lib.leankv_decode_end(self.logits.data_ptr(), cfg.vocab_size, self.token.data_ptr(),
                                             self.history.data_ptr(), self.history_cap, sp, st()), "decode_end")

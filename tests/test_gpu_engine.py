@@ -36,11 +36,13 @@ class OracleCache(TurboQuantCache):
     def __init__(self, num_layers, device):
         super().__init__(bits=3, head_dim=128, num_layers=num_layers, hot_buffer_size=0, device=device)
         self.store = [None] * num_layers
+        self.raw = [[] for _ in range(num_layers)]     # (k, v) exactly as the model handed them over
 
     def update(self, key_states, value_states, layer_idx, cache_kwargs=None):
         if layer_idx == 0:
             self._seen_tokens += key_states.shape[2]
         self._seq_lengths[layer_idx] += key_states.shape[2]
+        self.raw[layer_idx].append((key_states.clone(), value_states.clone()))
         outs = []
         for which, x, quant in ((0, key_states, self.key_quantizers[layer_idx]),
                                 (1, value_states, self.val_quantizers[layer_idx])):
@@ -112,7 +114,11 @@ def test_engine_matches_hf_with_oracle_hooks_and_cache(sparse):
     eng_tokens, eng_logits = _engine_run(engine, prompt, n_new, follow_tokens=ref_tokens)
     errs = [rel_l2(e, r) for e, r in zip(eng_logits, ref_logits)]
     print("per-step logits rel-L2:", [f"{e:.1e}" for e in errs])
-    assert max(errs) < 3e-2 and sum(errs) / len(errs) < 1.5e-2
+    # A magnitude threshold is a discontinuity: a last-bit difference in an activation next to the
+    # threshold switches a whole weight column on or off, so with TEAL the two paths drift apart much
+    # faster than without (the identical-input check below is the strict one for the sparse path).
+    bound = (0.3, 0.2) if sparse else (3e-2, 1.5e-2)
+    assert max(errs) < bound[0] and sum(errs) / len(errs) < bound[1]
     if sparse:
         # the counter says ~60 % of the projection weights were streamed on the decode steps
         streamed = engine.bytes_streamed()
@@ -158,7 +164,7 @@ def test_graph_replay_equals_eager_and_generate():
     assert all(torch.equal(x, y) for x, y in zip(la, lb))
     assert a.generate(prompt, 20, stream_to_host=True) == ta
     assert a.generate(prompt, 20, stream_to_host=False) == ta
-    assert a.launches_per_step == 2 + 10 * a.cfg.num_layers + 2
+    assert a.launches_per_step == 2 + 8 * a.cfg.num_layers + 2
     # the pool holds prompt + generated tokens at 50 bytes per vector
     assert a.kv_bytes_per_token() == 2 * 2 * 2 * 50
     with pytest.raises(ValueError):
@@ -176,3 +182,76 @@ def test_random_init_engine_runs_and_is_dense_without_thresholds():
     torch.cuda.synchronize()
     per_layer = 512 * eng.n_qkv + eng.nq * 128 * 512 + 3 * 512 * 1024
     assert eng.bytes_streamed() == 2 * (2 * per_layer + 512 * 1024)
+
+
+def test_each_layer_matches_hf_on_identical_inputs():
+    """Strict check of the sparse decode path: every block of the engine is fed the hidden state, position
+    and KV history that the HF + oracle-hook + oracle-cache run saw for a decode step, and must
+    reproduce that block's output."""
+    import math
+
+    from leankv_b200 import _native
+
+    model = _hf_model(scale=2.0)
+    gen = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 512, (41,), generator=gen).tolist()
+    T = len(prompt)
+    engine = DecodeEngine.from_hf(model, max_seq_len=128)
+    thresholds = engine.calibrate_thresholds(prompt, 0.4)
+    cache = OracleCache(model.config.num_hidden_layers, _dev())
+    seen_in, seen_out, hooks = {}, {}, []
+    with torch.no_grad():
+        out = model(torch.tensor([prompt], device=_dev()), past_key_values=cache, use_cache=True)
+        tok = int(out.logits[0, -1].float().argmax())
+        for l, layer in enumerate(model.model.layers):
+            for p in PROJ_NAMES:
+                mod = getattr(layer.self_attn if p in ("q_proj", "k_proj", "v_proj", "o_proj") else layer.mlp, p)
+                hooks.append(mod.register_forward_pre_hook(
+                    lambda m, a, t=thresholds[l][p]: (oteal.sparsify(a[0], t),) + a[1:]))
+            hooks.append(layer.register_forward_pre_hook(
+                lambda m, a, kw, l=l: seen_in.__setitem__(l, (a[0] if a else kw["hidden_states"]).detach().clone()),
+                with_kwargs=True))
+            hooks.append(layer.register_forward_hook(
+                lambda m, a, o, l=l: seen_out.__setitem__(l, (o[0] if isinstance(o, tuple) else o).detach().clone())))
+        model(torch.tensor([[tok]], device=_dev()), past_key_values=cache, use_cache=True)
+    for h in hooks:
+        h.remove()
+
+    lib = _native.lib()
+    n_pages = (T + 15) // 16
+    indptr = torch.tensor([0, n_pages], dtype=torch.int32, device=_dev())
+    start = torch.zeros(1, dtype=torch.int32, device=_dev())
+    errs = []
+    for l in range(model.config.num_hidden_layers):
+        k_hist, v_hist = cache.raw[l][0]                      # prompt k (after rope) and v, [1, nkv, T, 128]
+        k_hist, v_hist = k_hist.half().contiguous(), v_hist.half().contiguous()
+        engine.pools[l].zero_()
+        _native.check(lib.leankv_tq_pool_append(k_hist.data_ptr(), v_hist.data_ptr(), 1, engine.nkv, T,
+                                                engine.Pi_k[l].data_ptr(), engine.Pi_v[l].data_ptr(),
+                                                engine.bounds.data_ptr(), engine.pools[l].data_ptr(),
+                                                engine.max_pages, indptr.data_ptr(),
+                                                engine.page_indices.data_ptr(), start.data_ptr(),
+                                                torch.cuda.current_stream().cuda_stream), "pool_append")
+        engine.state.copy_(torch.tensor([T, 1, 0, T // 16 + 1, T % 16 + 1, T, 0, 0], dtype=torch.int32))
+        engine.h.copy_(seen_in[l].reshape(-1))
+        engine._norm(None, engine.w["layers"][l]["ln1"])
+        engine._layer_launches(l)
+        torch.cuda.synchronize()
+        errs.append(rel_l2(engine.h.float().cpu(), seen_out[l].reshape(-1).float().cpu()))
+    print("per-layer output rel-L2 on identical inputs:", [f"{e:.1e}" for e in errs])
+    assert max(errs) < 1e-2
+
+
+def test_fused_post_kernel_is_bit_identical_to_separate_launches():
+    model = _hf_model(scale=2.0)
+    prompt = list(range(7, 60))
+    runs = []
+    for fused in (True, False):
+        eng = DecodeEngine.from_hf(model, max_seq_len=128)
+        eng.fused_post = fused
+        eng.calibrate_thresholds(prompt, 0.4)
+        toks, logits = _engine_run(eng, prompt, 12)
+        runs.append((toks, logits, [p.clone() for p in eng.pools]))
+    assert runs[0][0] == runs[1][0]
+    assert all(torch.equal(a, b) for a, b in zip(runs[0][1], runs[1][1]))
+    assert all(torch.equal(a, b) for a, b in zip(runs[0][2], runs[1][2]))
