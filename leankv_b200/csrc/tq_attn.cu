@@ -161,12 +161,12 @@ AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     AttnPlan pl;
     if (max_pages < 1) max_pages = 1;
     const long long pairs = (long long)B * Hkv;
-    // Pages per warp: enough CTAs for about three rounds over the resident slots (6 CTAs per SM),
-    // so that the hardware scheduler evens out the load, but at least one page per warp and at
-    // most kMaxChunks chunks to merge per (sequence, kv head).
+    // Chunks per (sequence, kv head): as many as keep the whole grid resident at once (6 CTAs per
+    // SM), so that no SM idles waiting for a second round while others run a third.
     const long long slots = (long long)sm_count() * 6;
-    const long long total_pages = pairs * max_pages;
-    long long ppw = (total_pages + slots * 3 * kAttnWarps - 1) / (slots * 3 * kAttnWarps);
+    long long nc = slots / (pairs > 0 ? pairs : 1);
+    if (nc < 1) nc = 1;
+    long long ppw = (max_pages + nc * kAttnWarps - 1) / (nc * kAttnWarps);
     if (ppw < 1) ppw = 1;
     while ((max_pages + ppw * kAttnWarps - 1) / (ppw * kAttnWarps) > kMaxChunks) ++ppw;
     pl.pages_per_cta = (int)(ppw * kAttnWarps);

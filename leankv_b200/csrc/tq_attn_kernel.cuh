@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
         // ---- scores: D[16 tokens][8 = 4 heads x (hi,lo)] ----
         float d[4] = {0.f, 0.f, 0.f, 0.f};
         {
+            float d2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: halves the dependent MMA chain
             const Unit ua = load_unit(kw, lane), ub = load_unit(kw, 32 + lane);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -132,9 +133,10 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
                 const uint32_t sb = ub.s[q >> 1] >> (16 * (q & 1));
                 const uint32_t la = __byte_perm(p.tl0, p.tl1, sa), ha = __byte_perm(p.th0, p.th1, sa);
                 const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb), hb = __byte_perm(p.th0, p.th1, sb);
-                mma_16816(d, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
+                mma_16816((q & 1) ? d2 : d, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
                           __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), qf[q][0], qf[q][1]);
             }
+            d[0] += d2[0]; d[1] += d2[1]; d[2] += d2[2]; d[3] += d2[3];
         }
         float sa = (d[0] + d[1]) * __half2float(kn[g]);
         float sb = (d[2] + d[3]) * __half2float(kn[g + 8]);
