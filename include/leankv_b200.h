@@ -79,6 +79,23 @@ int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y, int N, in
                                void* workspace, size_t workspace_bytes,
                                unsigned long long* active_elems, void* stream);
 
+/* leankv_sparse_gemv_f16 for callers that cannot provide a workspace because they must not
+ * allocate device memory: a server whose pool already owns the whole GPU, a plugin host that keeps
+ * the allocator to itself, a loop that cannot afford an allocation's device-wide synchronisation.
+ * (No counterpart in the reference, which allocates its output and zeroes it on every call.)
+ * The split-K scratch is a fixed 768 KiB array inside the library image; every GPU that loads the
+ * library holds it until the process exits. This call allocates and frees nothing.
+ *  - Limits: N, Z <= LEANKV_STATIC_GEMV_MAX_DIM and the plan's scratch need <= 768 KiB, otherwise
+ *    LEANKV_ELIMIT; no bias / residual / counters.
+ *  - The first call on each device looks up the array's device address (that device must be
+ *    current, as for any call). Make that first call before starting a stream capture.
+ *  - All calls on a device share the one array: calls that can overlap on the GPU (different
+ *    streams, or graphs replayed concurrently) race on it and give wrong sums. The part of the array
+ *    that must start at zero is cleared on `stream` by each call. */
+#define LEANKV_STATIC_GEMV_MAX_DIM 65536
+int leankv_sparse_gemv_f16_static(const void* Wt, const void* x, void* y, int N, int Z,
+                                  float threshold, void* stream);
+
 /* Fused gate/up SwiGLU: y[n] = silu(Wg.x_g)[n] * (Wu.x_u)[n], where x_g / x_u are x
  * masked with t_gate / t_up (the reference installs separate thresholds on gate_proj
  * and up_proj, leankv/teal/patching.py:101-125). Replaces two sparse_gemv calls plus

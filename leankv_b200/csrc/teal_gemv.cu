@@ -435,3 +435,59 @@ extern "C" int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, 
     LEANKV_CUDA_TRY(cudaGetLastError());
     return LEANKV_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Sparse GEMV for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot hand over a workspace: a serving process whose memory pool
+// has already claimed the whole GPU (any further cudaMalloc fails or stalls the device), a plugin
+// sandbox in which only the host application may call the allocator, or a latency-critical loop
+// where an allocation's implicit device synchronisation is not acceptable. For them the split-K
+// scratch lives in the library image itself: a fixed array in device global memory that every GPU
+// loading the library carries until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace leankv {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 768u << 10;   // 768 KiB per GPU, resident for the process lifetime
+constexpr int kStaticMaxDim = 65536;                 // largest N or Z this entry point accepts
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device ordinal. In host code the symbol's name is only a
+// handle for the runtime, never a pointer a kernel could use; the address has to be asked for.
+constexpr int kStaticMaxDevices = 64;
+void* g_static_scratch_addr[kStaticMaxDevices] = {nullptr};
+
+}  // namespace
+}  // namespace leankv
+
+extern "C" int leankv_sparse_gemv_f16_static(const void* Wt, const void* x, void* y, int N, int Z,
+                                             float threshold, void* stream) {
+    int rc = check_common(Wt, x, y, N, Z);
+    if (rc != LEANKV_OK) return rc;
+    if (N > kStaticMaxDim || Z > kStaticMaxDim) return LEANKV_ELIMIT;
+    const GemvPlan pl = make_plan(N, Z, 1);
+    if (pl.counter_bytes + pl.partial_bytes > kStaticScratchBytes) return LEANKV_ELIMIT;
+
+    int dev = 0;
+    LEANKV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kStaticMaxDevices) return LEANKV_ELIMIT;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // One-time set-up for this device (it must be the current device, which it is). This may
+        // load the module, so the first call on a device belongs before any stream capture.
+        void* addr = nullptr;
+        LEANKV_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+        g_static_scratch_addr[dev] = addr;
+    }
+    void* scratch = g_static_scratch_addr[dev];
+    // The array keeps whatever the previous call left. Only the arrival counters must start at zero
+    // (partials are fully overwritten before they are read), so those are cleared on the stream.
+    if (pl.k_splits > 1)
+        LEANKV_CUDA_TRY(cudaMemsetAsync(scratch, 0, pl.counter_bytes, static_cast<cudaStream_t>(stream)));
+
+    leankv_segments_t segs{};
+    segs.n_segments = 1;
+    segs.seg_end[0] = N;
+    segs.threshold[0] = threshold;
+    return launch_gemv(Wt, x, y, N, Z, &segs, nullptr, nullptr, scratch, kStaticScratchBytes, nullptr, stream);
+}
