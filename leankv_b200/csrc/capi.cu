@@ -1,6 +1,7 @@
 // Error reporting and device queries shared by the C ABI entry points.
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -18,6 +19,16 @@ int note_cuda_error(cudaError_t e, const char* what) {
                   cudaGetErrorName(e), cudaGetErrorString(e));
     return LEANKV_ECUDA;
 }
+
+int pdl_mode() {
+    static int state = -1;
+    if (state < 0) {
+        const char* e = std::getenv("LEANKV_PDL");
+        state = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
+    }
+    return state;
+}
+bool pdl_enabled() { return pdl_mode() != 0; }
 
 int sm_count() {
     int dev = 0;

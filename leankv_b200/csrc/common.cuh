@@ -25,6 +25,37 @@ int note_cuda_error(cudaError_t e, const char* what);
 // Number of SMs of the current device (cached per device id).
 int sm_count();
 
+// Whether launches carry the programmatic-stream-serialization attribute (default on; the
+// environment variable LEANKV_PDL=0 turns it off).
+bool pdl_enabled();
+// LEANKV_PDL: 0 = never, 1 = every kernel may start early, 2 (default) = only the bandwidth-bound
+// GEMV kernels may (their ramp-up is what is worth hiding; small latency-bound kernels run best alone).
+int pdl_mode();
+
+// Launch `kernel` on `st`, allowing it to overlap its start-up with the tail of the previous
+// kernel in the stream (see pdl_begin()).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_ex(bool early_ok, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    const int mode = pdl_mode();
+    cfg.numAttrs = (mode == 1 || (mode == 2 && early_ok)) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args&&... args) {
+    return launch_kernel_ex(false, kernel, grid, block, smem, st, static_cast<Args&&>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -49,6 +80,15 @@ __device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                  : "l"(p));
     return v;
+}
+
+// Programmatic dependent launch: a kernel first lets the next kernel in the stream start
+// launching (its CTAs become resident and run up to their own pdl_wait), then waits until every
+// kernel before it has completed and its writes are visible. Nothing that depends on, or is read
+// by, an earlier kernel may be touched before pdl_wait(). Both are no-ops for a normal launch.
+__device__ __forceinline__ void pdl_begin() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __device__ __forceinline__ float2 h2_to_f2(uint32_t packed) {

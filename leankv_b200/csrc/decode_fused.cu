@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
     __shared__ float s_bounds[8];
     __shared__ uint8_t s_code[kDim];
 
+    pdl_begin();
     const int j = threadIdx.x;
     const int head = blockIdx.x;
     const int kind = head < p.nq ? 0 : (head < p.nq + p.nkv ? 1 : 2);   // 0 q, 1 k, 2 v
@@ -160,7 +161,7 @@ extern "C" int leankv_decode_qkv_post(const void* qkv, const float* inv_freq, co
     p.nq = n_q_heads;
     p.nkv = n_kv_heads;
     p.q_rot = q_rot;
-    decode_qkv_post_kernel<<<n_q_heads + 2 * n_kv_heads, kDim, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel(decode_qkv_post_kernel, dim3(n_q_heads + 2 * n_kv_heads), dim3(kDim), 0,
+                                  static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
 }

@@ -35,6 +35,7 @@ constexpr int kNormVecs = 4;
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(__half* x, const __half* delta,
                                                                const __half* w, __half* y, int n, float eps) {
     __shared__ float s_tmp[32];
+    pdl_begin();
     const int nvec = n >> 3;
     uint4 v[kNormVecs];
     float ss = 0.f;
@@ -86,6 +87,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(__half* x, const 
 __global__ void __launch_bounds__(256) decode_begin_kernel(const __half* table, const long long* token,
                                                            __half* h, int hidden, int vocab,
                                                            int* state) {
+    pdl_begin();
     long long tok = *token;
     if (tok < 0 || tok >= vocab) tok = 0;
     const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * hidden);
@@ -105,6 +107,7 @@ __global__ void __launch_bounds__(256) decode_begin_kernel(const __half* table, 
 __global__ void __launch_bounds__(64) rope_kernel(const __half* qkv, const float* inv_freq,
                                                   const int* state, __half* q_out, __half* k_out,
                                                   int n_q_heads, int n_kv_heads) {
+    pdl_begin();
     const int head = blockIdx.x;                 // q heads first, then k heads
     const int i = threadIdx.x;                   // 0..63
     const float ang = (float)state[kPos] * inv_freq[i];
@@ -123,6 +126,7 @@ __global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, 
                                                           int history_cap, int* state) {
     __shared__ float s_v[32];
     __shared__ int s_i[32];
+    pdl_begin();
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -161,10 +165,9 @@ extern "C" int leankv_rmsnorm_f16(void* x, const void* delta, const void* weight
     if (n % 8 != 0 || !aligned16(x) || !aligned16(weight) || !aligned16(y) || (delta && !aligned16(delta)))
         return LEANKV_EALIGN;
     if (n > kNormThreads * 8 * kNormVecs) return LEANKV_ELIMIT;
-    rmsnorm_kernel<<<1, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half*>(x), static_cast<const __half*>(delta), static_cast<const __half*>(weight),
-        static_cast<__half*>(y), n, eps);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel(rmsnorm_kernel, dim3(1), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                                  static_cast<__half*>(x), static_cast<const __half*>(delta),
+                                  static_cast<const __half*>(weight), static_cast<__half*>(y), n, eps));
     return LEANKV_OK;
 }
 
@@ -172,9 +175,9 @@ extern "C" int leankv_decode_begin(const void* embed_table, const long long* tok
                                    int hidden, int vocab, int32_t* state, void* stream) {
     if (!embed_table || !token || !h || !state || hidden <= 0 || vocab <= 0) return LEANKV_EINVAL;
     if (hidden % 8 != 0 || !aligned16(embed_table) || !aligned16(h)) return LEANKV_EALIGN;
-    decode_begin_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(embed_table), token, static_cast<__half*>(h), hidden, vocab, state);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel(decode_begin_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                  static_cast<const __half*>(embed_table), token, static_cast<__half*>(h),
+                                  hidden, vocab, state));
     return LEANKV_OK;
 }
 
@@ -184,18 +187,17 @@ extern "C" int leankv_rope_f16(const void* qkv, const float* inv_freq, const int
     if (!qkv || !inv_freq || !state || !q_out || !k_out || n_q_heads <= 0 || n_kv_heads <= 0)
         return LEANKV_EINVAL;
     if (head_dim != 128) return LEANKV_EUNSUPPORTED;
-    rope_kernel<<<n_q_heads + n_kv_heads, 64, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(qkv), inv_freq, state, static_cast<__half*>(q_out),
-        static_cast<__half*>(k_out), n_q_heads, n_kv_heads);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel(rope_kernel, dim3(n_q_heads + n_kv_heads), dim3(64), 0,
+                                  static_cast<cudaStream_t>(stream), static_cast<const __half*>(qkv), inv_freq,
+                                  state, static_cast<__half*>(q_out), static_cast<__half*>(k_out), n_q_heads,
+                                  n_kv_heads));
     return LEANKV_OK;
 }
 
 extern "C" int leankv_decode_end(const void* logits, int vocab, long long* token, long long* history,
                                  int history_cap, int32_t* state, void* stream) {
     if (!logits || !token || !history || !state || vocab <= 0 || history_cap < 0) return LEANKV_EINVAL;
-    decode_end_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(logits), vocab, token, history, history_cap, state);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel(decode_end_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream),
+                                  static_cast<const __half*>(logits), vocab, token, history, history_cap, state));
     return LEANKV_OK;
 }

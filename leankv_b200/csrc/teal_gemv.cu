@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
     __shared__ int s_wcount[kWarps];
     __shared__ int s_last;
 
+    pdl_begin();
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int slice = blockIdx.x;
@@ -354,8 +355,8 @@ int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const lean
     }
     p.thr_up = 0.f;
     dim3 grid(pl.n_slices, pl.k_splits);
-    sparse_gemv_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel_ex(true, sparse_gemv_kernel<false>, grid, dim3(kThreads), 0,
+                                  static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
 }
 
@@ -431,8 +432,8 @@ extern "C" int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, 
     }
     p.thr_up = t_up;
     dim3 grid(pl.n_slices, pl.k_splits);
-    sparse_gemv_kernel<true><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel_ex(true, sparse_gemv_kernel<true>, grid, dim3(kThreads), 0,
+                                  static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
 }
 

@@ -132,6 +132,7 @@ __device__ __forceinline__ Unit load_unit(const uint32_t* words, int ui) {
 // ---- query rotation --------------------------------------------------------
 __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const float* Pi_k, float* qprime) {
     __shared__ float s_q[kDim];
+    pdl_begin();
     const int v = blockIdx.x, j = threadIdx.x;
     s_q[j] = __half2float(q[(size_t)v * kDim + j]);
     __syncthreads();
@@ -275,8 +276,8 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     const float* qprime = q_rot;
     if (q != nullptr) {
         float* dst = reinterpret_cast<float*>(ws + pl.off_qprime);
-        tq_qrot_kernel<<<B * n_q_heads, 128, 0, st>>>(static_cast<const __half*>(q), Pi_k, dst);
-        LEANKV_CUDA_TRY(cudaGetLastError());
+        LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel, dim3(B * n_q_heads), dim3(128), 0, st,
+                                      static_cast<const __half*>(q), Pi_k, dst));
         qprime = dst;
     }
 
@@ -300,8 +301,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
     dim3 grid(pl.n_chunks, n_kv_heads, B);
-    tq_decode_attn_kernel<<<grid, kAttnThreads, 0, st>>>(p);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+    LEANKV_CUDA_TRY(launch_kernel(tq_decode_attn_kernel, grid, dim3(kAttnThreads), 0, st, p));
     return LEANKV_OK;
 }
 

@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
     __shared__ float s_m[kAttnWarps][kGroup], s_l[kAttnWarps][kGroup];
     __shared__ int s_last;
 
+    pdl_begin();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;

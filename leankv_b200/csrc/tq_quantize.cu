@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(128) tq_pool_append_kernel(const AppendParams 
     __shared__ float s_norm[kTok];
     __shared__ float s_bounds[8];
 
+    pdl_begin();
     const int tid = threadIdx.x;
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const int which = blockIdx.z;                         // 0 = K, 1 = V
@@ -492,10 +493,9 @@ extern "C" int leankv_tq_pool_append(const void* k, const void* v, int B, int n_
     if (groups > 65535) return LEANKV_ELIMIT;
     dim3 grid(B * n_kv_heads, groups, 2);
     if (T_new == 1)
-        tq_pool_append_kernel<1><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        LEANKV_CUDA_TRY(launch_kernel(tq_pool_append_kernel<1>, grid, dim3(128), 0, static_cast<cudaStream_t>(stream), p));
     else
-        tq_pool_append_kernel<16><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    LEANKV_CUDA_TRY(cudaGetLastError());
+        LEANKV_CUDA_TRY(launch_kernel(tq_pool_append_kernel<16>, grid, dim3(128), 0, static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
 }
 

@@ -281,13 +281,17 @@ class DecodeEngine:
             torch.distributed.all_reduce(t, group=self.group)
             self.launches_per_step += 1
 
-    def _layer_launches(self, l: int) -> None:
+    def _layer_launches(self, l: int, probe=None) -> None:
         """Block ``l`` of one decode step: expects ``self.x`` = input-normed hidden state and the decode
-        state words set; leaves the residual stream in ``self.h`` and the next norm's output in ``self.x``."""
+        state words set; leaves the residual stream in ``self.h`` and the next norm's output in ``self.x``.
+        ``probe(stage)`` (eager debugging / tests only) is called after each stage's launch with the name
+        of the buffer that stage just wrote: "qkv", "attn", "o", "x", "mlp_h", "down"."""
+        probe = probe or (lambda stage: None)
         cfg, lib, st = self.cfg, self.lib, self._st
         sp = self.state.data_ptr()
         lw, t = self.w["layers"][l], self.thresholds[l]
         self._gemv(lw["wqkv_t"], self.x, self.qkv, 0.0, self._qkv_segments(l))
+        probe("qkv")
         if self.fused_post:
             # rope(q, k) + rotate/quantize/pack of k, v into the page + query rotation: one launch
             _native.check(lib.leankv_decode_qkv_post(self.qkv.data_ptr(), self.inv_freq.data_ptr(), sp,
@@ -319,17 +323,22 @@ class DecodeEngine:
                                                     self.ws_attn.data_ptr(), self.ws_attn.numel(), st()),
                           "decode_attn")
             self.launches_per_step += 4     # rope, append, query rotation, attention
+        probe("attn")
         self._gemv(lw["wo_t"], self.attn, self.o, t["o_proj"])
         self._allreduce(self.o)
+        probe("o")
         self._norm(self.o, lw["ln2"])
+        probe("x")
         rc = lib.leankv_sparse_swiglu_f16(lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), self.x.data_ptr(),
                                           self.mlp_h.data_ptr(), self.inter, cfg.hidden_size, t["gate_proj"],
                                           t["up_proj"], self.ws_gemv.data_ptr(), self.ws_gemv.numel(),
                                           self.active_elems.data_ptr(), st())
         _native.check(rc, "sparse swiglu")
         self.launches_per_step += 1
+        probe("mlp_h")
         self._gemv(lw["wdown_t"], self.mlp_h, self.down, t["down_proj"])
         self._allreduce(self.down)
+        probe("down")
         nxt = self.w["layers"][l + 1]["ln1"] if l + 1 < cfg.num_layers else self.w["final_norm"]
         self._norm(self.down, nxt)
 

@@ -184,12 +184,11 @@ def test_random_init_engine_runs_and_is_dense_without_thresholds():
     assert eng.bytes_streamed() == 2 * (2 * per_layer + 512 * 1024)
 
 
-def test_each_layer_matches_hf_on_identical_inputs():
-    """Strict check of the sparse decode path: every block of the engine is fed the hidden state, position
-    and KV history that the HF + oracle-hook + oracle-cache run saw for a decode step, and must
-    reproduce that block's output."""
-    import math
-
+def test_each_stage_matches_hf_on_identical_inputs():
+    """Strict check of the sparse decode path. A TEAL threshold is a discontinuity, so whole-model
+    comparisons drift; here every stage of every block (qkv projection, attention on the packed
+    pages, o_proj, norm, fused gate/up, down_proj) is fed exactly the tensors the HF + oracle-hook +
+    oracle-cache run saw at that point of a decode step and must reproduce HF's next tensor."""
     from leankv_b200 import _native
 
     model = _hf_model(scale=2.0)
@@ -199,20 +198,27 @@ def test_each_layer_matches_hf_on_identical_inputs():
     engine = DecodeEngine.from_hf(model, max_seq_len=128)
     thresholds = engine.calibrate_thresholds(prompt, 0.4)
     cache = OracleCache(model.config.num_hidden_layers, _dev())
-    seen_in, seen_out, hooks = {}, {}, []
+    cap, hooks = {}, []
+
+    def grab(key, pick):
+        return lambda m, a, o=None: cap.__setitem__(key, pick(a, o).detach().clone().reshape(-1))
+
     with torch.no_grad():
         out = model(torch.tensor([prompt], device=_dev()), past_key_values=cache, use_cache=True)
         tok = int(out.logits[0, -1].float().argmax())
         for l, layer in enumerate(model.model.layers):
             for p in PROJ_NAMES:
                 mod = getattr(layer.self_attn if p in ("q_proj", "k_proj", "v_proj", "o_proj") else layer.mlp, p)
+                # record the raw input first, then let the oracle hook sparsify it
+                hooks.append(mod.register_forward_pre_hook(grab((l, p, "in"), lambda a, o: a[0])))
                 hooks.append(mod.register_forward_pre_hook(
                     lambda m, a, t=thresholds[l][p]: (oteal.sparsify(a[0], t),) + a[1:]))
+                hooks.append(mod.register_forward_hook(grab((l, p, "out"), lambda a, o: o)))
             hooks.append(layer.register_forward_pre_hook(
-                lambda m, a, kw, l=l: seen_in.__setitem__(l, (a[0] if a else kw["hidden_states"]).detach().clone()),
+                lambda m, a, kw, l=l: cap.__setitem__((l, "h_in"), (a[0] if a else kw["hidden_states"]).detach().clone().reshape(-1)),
                 with_kwargs=True))
             hooks.append(layer.register_forward_hook(
-                lambda m, a, o, l=l: seen_out.__setitem__(l, (o[0] if isinstance(o, tuple) else o).detach().clone())))
+                lambda m, a, o, l=l: cap.__setitem__((l, "h_out"), (o[0] if isinstance(o, tuple) else o).detach().clone().reshape(-1))))
         model(torch.tensor([[tok]], device=_dev()), past_key_values=cache, use_cache=True)
     for h in hooks:
         h.remove()
@@ -221,7 +227,7 @@ def test_each_layer_matches_hf_on_identical_inputs():
     n_pages = (T + 15) // 16
     indptr = torch.tensor([0, n_pages], dtype=torch.int32, device=_dev())
     start = torch.zeros(1, dtype=torch.int32, device=_dev())
-    errs = []
+    report = {}
     for l in range(model.config.num_hidden_layers):
         k_hist, v_hist = cache.raw[l][0]                      # prompt k (after rope) and v, [1, nkv, T, 128]
         k_hist, v_hist = k_hist.half().contiguous(), v_hist.half().contiguous()
@@ -233,13 +239,40 @@ def test_each_layer_matches_hf_on_identical_inputs():
                                                 engine.page_indices.data_ptr(), start.data_ptr(),
                                                 torch.cuda.current_stream().cuda_stream), "pool_append")
         engine.state.copy_(torch.tensor([T, 1, 0, T // 16 + 1, T % 16 + 1, T, 0, 0], dtype=torch.int32))
-        engine.h.copy_(seen_in[l].reshape(-1))
+        engine.h.copy_(cap[(l, "h_in")])
         engine._norm(None, engine.w["layers"][l]["ln1"])
-        engine._layer_launches(l)
         torch.cuda.synchronize()
-        errs.append(rel_l2(engine.h.float().cpu(), seen_out[l].reshape(-1).float().cpu()))
-    print("per-layer output rel-L2 on identical inputs:", [f"{e:.1e}" for e in errs])
-    assert max(errs) < 1e-2
+        report[(l, "x1")] = rel_l2(engine.x.float().cpu(), cap[(l, "q_proj", "in")].float().cpu())
+        engine.x.copy_(cap[(l, "q_proj", "in")])
+
+        def probe(stage, l=l):
+            """Compare the buffer this stage wrote with HF's tensor, then overwrite it with HF's so that
+            the next stage starts from identical inputs (same mask, bit for bit)."""
+            torch.cuda.synchronize()
+            if stage == "qkv":
+                want = torch.cat([cap[(l, p, "out")] for p in ("q_proj", "k_proj", "v_proj")])
+                buf = engine.qkv
+            elif stage == "attn":
+                want, buf = cap[(l, "o_proj", "in")], engine.attn
+            elif stage == "o":
+                want, buf = cap[(l, "o_proj", "out")], engine.o
+            elif stage == "x":
+                want, buf = cap[(l, "gate_proj", "in")], engine.x
+            elif stage == "mlp_h":
+                want, buf = cap[(l, "down_proj", "in")], engine.mlp_h
+            else:
+                want, buf = cap[(l, "down_proj", "out")], engine.down
+            report[(l, stage)] = rel_l2(buf.float().cpu(), want.float().cpu())
+            buf.copy_(want)
+
+        engine._layer_launches(l, probe)
+        torch.cuda.synchronize()
+        report[(l, "h_out")] = rel_l2(engine.h.float().cpu(), cap[(l, "h_out")].float().cpu())
+    print("per-stage rel-L2 on identical inputs:", {k: f"{v:.1e}" for k, v in report.items()})
+    for (l, stage), err in report.items():
+        # attention: the new token's k/v codes come from this path's own projection output (copied
+        # from HF here, so identical) -> only fp16/fp32 rounding remains everywhere
+        assert err < (3e-3 if stage == "attn" else 1.5e-3), (l, stage, err)
 
 
 def test_fused_post_kernel_is_bit_identical_to_separate_launches():
