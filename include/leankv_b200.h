@@ -79,6 +79,20 @@ int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y, int N, in
                                void* workspace, size_t workspace_bytes,
                                unsigned long long* active_elems, void* stream);
 
+/* The two kernels above with the block's RMSNorm fused in front (no reference counterpart: HF runs
+ * MistralRMSNorm as separate ops before the patched projections): h is the un-normalised row and
+ *   x[z] = norm_weight[z] * fp16( h[z] * rsqrt(mean(h^2) + eps) )
+ * is formed on the fly by every CTA (Z % 8 == 0, h 16-byte aligned). With residual == y == h the
+ * GEMV updates the residual stream in place (each output element is read and written by one thread). */
+int leankv_sparse_gemv_rmsnorm_f16(const void* Wt, const void* h, const void* norm_weight, float eps,
+                                   void* y, int N, int Z, const leankv_segments_t* segs /* host */,
+                                   const void* residual, void* workspace, size_t workspace_bytes,
+                                   unsigned long long* active_elems, void* stream);
+int leankv_sparse_swiglu_rmsnorm_f16(const void* Wt_gate, const void* Wt_up, const void* h,
+                                     const void* norm_weight, float eps, void* y, int N, int Z,
+                                     float t_gate, float t_up, void* workspace, size_t workspace_bytes,
+                                     unsigned long long* active_elems, void* stream);
+
 /* leankv_sparse_gemv_f16 for callers that cannot provide a workspace because they must not
  * allocate device memory: a server whose pool already owns the whole GPU, a plugin host that keeps
  * the allocator to itself, a loop that cannot afford an allocation's device-wide synchronisation.
@@ -227,9 +241,10 @@ int leankv_rope_f16(const void* qkv, const float* inv_freq, const int32_t* state
 /* leankv_rope_f16 + leankv_tq_pool_append (one token, one sequence) + the query rotation of
  * leankv_tq_decode_attn in a single launch, bit-identical to the three: qkv is the fused
  * projection row [q heads | k heads | v heads] x 128 fp16; the token's position is state[0] and
- * its page is page_indices[state[0] / 16]; q_rot (fp32 [n_q_heads][128]) receives Pi_k rope(q). */
+ * its page is page_indices[state[0] / 16]; q_rot (fp32 [n_q_heads][128]) receives Pi_k rope(q).
+ * The rotations are passed TRANSPOSED (Pi_k_t[k][j] = Pi_k[j][k], row-major) for coalesced reads. */
 int leankv_decode_qkv_post(const void* qkv, const float* inv_freq, const int32_t* state,
-                           const float* Pi_k, const float* Pi_v, const float* decision_boundaries,
+                           const float* Pi_k_t, const float* Pi_v_t, const float* decision_boundaries,
                            void* pool, int n_pages, const int32_t* page_indices,
                            int n_q_heads, int n_kv_heads, float* q_rot, void* stream);
 /* *token = argmax(logits) (lowest index on ties); history[state[1]] = *token;

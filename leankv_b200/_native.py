@@ -41,6 +41,12 @@ SIGNATURES = {
     "leankv_sparse_gemv_seg_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int,
                                            POINTER(Segments), c_void_p, c_void_p, c_void_p,
                                            c_size_t, c_void_p, c_void_p]),
+    "leankv_sparse_gemv_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                                               POINTER(Segments), c_void_p, c_void_p, c_size_t, c_void_p,
+                                               c_void_p]),
+    "leankv_sparse_swiglu_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                                 c_int, c_int, c_float, c_float, c_void_p, c_size_t,
+                                                 c_void_p, c_void_p]),
     "leankv_sparse_gemv_f16_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "leankv_sparse_swiglu_workspace_bytes": (c_size_t, [c_int, c_int]),
     "leankv_sparse_swiglu_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

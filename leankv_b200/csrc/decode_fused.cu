@@ -20,8 +20,8 @@ struct PostParams {
     const __half* qkv;
     const float* inv_freq;
     const int* state;
-    const float* Pi_k;
-    const float* Pi_v;
+    const float* Pi_k_t;   // transposes of the rotations: Pi_k_t[k][j] = Pi_k[j][k]
+    const float* Pi_v_t;
     const float* bounds;
     uint8_t* pool;
     int n_pages;
@@ -37,10 +37,17 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
     __shared__ float s_bounds[8];
     __shared__ uint8_t s_code[kDim];
 
-    pdl_begin();
     const int j = threadIdx.x;
     const int head = blockIdx.x;
     const int kind = head < p.nq ? 0 : (head < p.nq + p.nkv ? 1 : 2);   // 0 q, 1 k, 2 v
+    // The rotation matrix is a constant of the cache, not an output of the previous kernel: fetch this
+    // thread's column of it right away (128 independent loads, one memory round trip) so that it
+    // is in registers by the time the vector has been prepared.
+    const float* PiT = kind == 2 ? p.Pi_v_t : p.Pi_k_t;
+    float pi_col[kDim];
+#pragma unroll
+    for (int k = 0; k < kDim; ++k) pi_col[k] = __ldg(PiT + k * kDim + j);
+    pdl_begin();
     const int pos = p.state[kPos];
     const __half* src = p.qkv + (size_t)head * kDim;
 
@@ -81,18 +88,11 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
     }
     __syncthreads();
 
-    // y_j = sum_k Pi[j][k] u[k], k ascending
-    const float* Pi = kind == 2 ? p.Pi_v : p.Pi_k;
-    const float4* row = reinterpret_cast<const float4*>(Pi + (size_t)j * kDim);
+    // y_j = sum_k Pi[j][k] u[k], k ascending; Pi is read through its transpose so that the 32 lanes
+    // of a warp fetch 128 consecutive bytes per k
     float y = 0.f;
-#pragma unroll 16
-    for (int k4 = 0; k4 < kDim / 4; ++k4) {
-        const float4 pv = __ldg(row + k4);
-        y = fmaf(pv.x, s_u[4 * k4 + 0], y);
-        y = fmaf(pv.y, s_u[4 * k4 + 1], y);
-        y = fmaf(pv.z, s_u[4 * k4 + 2], y);
-        y = fmaf(pv.w, s_u[4 * k4 + 3], y);
-    }
+#pragma unroll
+    for (int k = 0; k < kDim; ++k) y = fmaf(pi_col[k], s_u[k], y);
     if (kind == 0) {
         p.q_rot[(size_t)head * kDim + j] = y;
         return;
@@ -140,20 +140,20 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
 using namespace leankv;
 
 extern "C" int leankv_decode_qkv_post(const void* qkv, const float* inv_freq, const int32_t* state,
-                                      const float* Pi_k, const float* Pi_v,
+                                      const float* Pi_k_t, const float* Pi_v_t,
                                       const float* decision_boundaries, void* pool, int n_pages,
                                       const int32_t* page_indices, int n_q_heads, int n_kv_heads,
                                       float* q_rot, void* stream) {
-    if (!qkv || !inv_freq || !state || !Pi_k || !Pi_v || !decision_boundaries || !pool || !page_indices ||
+    if (!qkv || !inv_freq || !state || !Pi_k_t || !Pi_v_t || !decision_boundaries || !pool || !page_indices ||
         !q_rot || n_pages <= 0 || n_q_heads <= 0 || n_kv_heads <= 0)
         return LEANKV_EINVAL;
-    if (!aligned16(Pi_k) || !aligned16(Pi_v) || !aligned16(pool)) return LEANKV_EALIGN;
+    if (!aligned16(pool)) return LEANKV_EALIGN;
     PostParams p{};
     p.qkv = static_cast<const __half*>(qkv);
     p.inv_freq = inv_freq;
     p.state = state;
-    p.Pi_k = Pi_k;
-    p.Pi_v = Pi_v;
+    p.Pi_k_t = Pi_k_t;
+    p.Pi_v_t = Pi_v_t;
     p.bounds = decision_boundaries;
     p.pool = static_cast<uint8_t*>(pool);
     p.n_pages = n_pages;
@@ -161,7 +161,7 @@ extern "C" int leankv_decode_qkv_post(const void* qkv, const float* inv_freq, co
     p.nq = n_q_heads;
     p.nkv = n_kv_heads;
     p.q_rot = q_rot;
-    LEANKV_CUDA_TRY(launch_kernel(decode_qkv_post_kernel, dim3(n_q_heads + 2 * n_kv_heads), dim3(kDim), 0,
+    LEANKV_CUDA_TRY(launch_kernel_ex(true, decode_qkv_post_kernel, dim3(n_q_heads + 2 * n_kv_heads), dim3(kDim), 0,
                                   static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
 }

@@ -43,6 +43,8 @@ struct GemvParams {
     int seg_end[LEANKV_MAX_SEGMENTS];
     float thr[LEANKV_MAX_SEGMENTS];
     float thr_up;        // SwiGLU: thr[0] masks gate, thr_up masks up
+    const __half* norm_w;   // if set, x is an un-normalised row h and the kernel uses
+    float norm_eps;         // x[z] = norm_w[z] * fp16(h[z] * rsqrt(mean(h^2) + eps))  (RMSNorm fused in)
 };
 
 struct GemvPlan {
@@ -101,6 +103,43 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
     const int z0 = blockIdx.y * p.rows_per_split;
     const int nrows = min(p.rows_per_split, p.Z - z0);
 
+    // Fused RMSNorm: every CTA derives the row's scale itself (Z * 2 bytes from L2, a few hundred
+    // FMAs) instead of waiting for a separate one-CTA kernel. The summation order is the same in
+    // every CTA, so all of them see the same x.
+    float rnorm = 0.f;
+    // rows this lane will test during compaction: start their loads now, they overlap the norm's reduction
+    const int per_warp = (nrows + kWarps - 1) / kWarps;
+    const int w0 = warp * per_warp;
+    const int w1 = min(nrows, w0 + per_warp);
+    __half xraw[kLaneSlots], nw[kLaneSlots];
+#pragma unroll
+    for (int s = 0; s < kLaneSlots; ++s) {
+        const int r = w0 + s * 32 + lane;
+        xraw[s] = r < w1 ? p.x[z0 + r] : __float2half_rn(0.f);
+        nw[s] = (r < w1 && p.norm_w != nullptr) ? p.norm_w[z0 + r] : __float2half_rn(0.f);
+    }
+    if (p.norm_w != nullptr) {
+        float ss = 0.f;
+        const uint4* hv = reinterpret_cast<const uint4*>(p.x);
+        for (int i = tid; i < (p.Z >> 3); i += kThreads) {
+            const uint4 a = hv[i];
+            const float2 f0 = h2_to_f2(a.x), f1 = h2_to_f2(a.y), f2 = h2_to_f2(a.z), f3 = h2_to_f2(a.w);
+            ss = fmaf(f0.x, f0.x, ss); ss = fmaf(f0.y, f0.y, ss);
+            ss = fmaf(f1.x, f1.x, ss); ss = fmaf(f1.y, f1.y, ss);
+            ss = fmaf(f2.x, f2.x, ss); ss = fmaf(f2.y, f2.y, ss);
+            ss = fmaf(f3.x, f3.x, ss); ss = fmaf(f3.y, f3.y, ss);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_red[0][0][warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) tot += s_red[0][0][w];
+        rnorm = rsqrtf(tot / (float)p.Z + p.norm_eps);
+        __syncthreads();   // s_red is reused below
+    }
+
     // Threshold of the projection this column slice belongs to.
     float thr = p.thr[0];
     if (!kSwiglu) {
@@ -113,9 +152,6 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
     const __half thr2_h = __float2half_rn(kSwiglu ? p.thr_up : thr);
 
     // ---- threshold test + ordered compaction of this CTA's input channels ----
-    const int per_warp = (nrows + kWarps - 1) / kWarps;
-    const int w0 = warp * per_warp;
-    const int w1 = min(nrows, w0 + per_warp);
     float xv[kLaneSlots], xv2[kLaneSlots];
     int pos[kLaneSlots];
     bool act[kLaneSlots];
@@ -126,7 +162,8 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
         bool a = false;
         float v = 0.f, v2 = 0.f;
         if (r < w1) {
-            const __half h = p.x[z0 + r];
+            __half h = xraw[s];
+            if (p.norm_w != nullptr) h = __hmul(nw[s], __float2half_rn(__half2float(h) * rnorm));
             const __half m = __habs(h);
             const bool a1 = __hgt(m, thr_h);
             const bool a2 = kSwiglu ? __hgt(m, thr2_h) : a1;
@@ -311,10 +348,18 @@ int check_common(const void* Wt, const void* x, const void* y, int N, int Z) {
     return LEANKV_OK;
 }
 
+int check_norm(const void* x, const void* norm_w, int Z) {
+    if (norm_w == nullptr) return LEANKV_OK;
+    if (Z % 8 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(norm_w) & 1u) != 0) return LEANKV_EALIGN;
+    return LEANKV_OK;
+}
+
 int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const leankv_segments_t* segs,
                 const void* bias, const void* residual, void* workspace, size_t workspace_bytes,
-                unsigned long long* active, void* stream) {
+                unsigned long long* active, void* stream, const void* norm_w = nullptr, float norm_eps = 0.f) {
     int rc = check_common(Wt, x, y, N, Z);
+    if (rc != LEANKV_OK) return rc;
+    rc = check_norm(x, norm_w, Z);
     if (rc != LEANKV_OK) return rc;
     if (segs == nullptr || segs->n_segments < 1 || segs->n_segments > LEANKV_MAX_SEGMENTS)
         return LEANKV_EINVAL;
@@ -354,6 +399,8 @@ int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const lean
         p.thr[s] = s < segs->n_segments ? segs->threshold[s] : 0.f;
     }
     p.thr_up = 0.f;
+    p.norm_w = static_cast<const __half*>(norm_w);
+    p.norm_eps = norm_eps;
     dim3 grid(pl.n_slices, pl.k_splits);
     LEANKV_CUDA_TRY(launch_kernel_ex(true, sparse_gemv_kernel<false>, grid, dim3(kThreads), 0,
                                   static_cast<cudaStream_t>(stream), p));
@@ -398,11 +445,12 @@ extern "C" int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y
                        active_elems, stream);
 }
 
-extern "C" int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, const void* x,
-                                        void* y, int N, int Z, float t_gate, float t_up,
-                                        void* workspace, size_t workspace_bytes,
-                                        unsigned long long* active_elems, void* stream) {
+static int launch_swiglu(const void* Wt_gate, const void* Wt_up, const void* x, void* y, int N, int Z,
+                         float t_gate, float t_up, void* workspace, size_t workspace_bytes,
+                         unsigned long long* active_elems, void* stream, const void* norm_w, float norm_eps) {
     int rc = check_common(Wt_gate, x, y, N, Z);
+    if (rc != LEANKV_OK) return rc;
+    rc = check_norm(x, norm_w, Z);
     if (rc != LEANKV_OK) return rc;
     if (Wt_up == nullptr) return LEANKV_EINVAL;
     if (!aligned16(Wt_up)) return LEANKV_EALIGN;
@@ -431,10 +479,40 @@ extern "C" int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, 
         p.thr[s] = t_gate;
     }
     p.thr_up = t_up;
+    p.norm_w = static_cast<const __half*>(norm_w);
+    p.norm_eps = norm_eps;
     dim3 grid(pl.n_slices, pl.k_splits);
     LEANKV_CUDA_TRY(launch_kernel_ex(true, sparse_gemv_kernel<true>, grid, dim3(kThreads), 0,
                                   static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
+}
+
+extern "C" int leankv_sparse_swiglu_f16(const void* Wt_gate, const void* Wt_up, const void* x,
+                                        void* y, int N, int Z, float t_gate, float t_up,
+                                        void* workspace, size_t workspace_bytes,
+                                        unsigned long long* active_elems, void* stream) {
+    return launch_swiglu(Wt_gate, Wt_up, x, y, N, Z, t_gate, t_up, workspace, workspace_bytes, active_elems,
+                         stream, nullptr, 0.f);
+}
+
+extern "C" int leankv_sparse_gemv_rmsnorm_f16(const void* Wt, const void* h, const void* norm_weight,
+                                              float eps, void* y, int N, int Z,
+                                              const leankv_segments_t* segs, const void* residual,
+                                              void* workspace, size_t workspace_bytes,
+                                              unsigned long long* active_elems, void* stream) {
+    if (norm_weight == nullptr) return LEANKV_EINVAL;
+    return launch_gemv(Wt, h, y, N, Z, segs, nullptr, residual, workspace, workspace_bytes, active_elems,
+                       stream, norm_weight, eps);
+}
+
+extern "C" int leankv_sparse_swiglu_rmsnorm_f16(const void* Wt_gate, const void* Wt_up, const void* h,
+                                                const void* norm_weight, float eps, void* y, int N, int Z,
+                                                float t_gate, float t_up, void* workspace,
+                                                size_t workspace_bytes, unsigned long long* active_elems,
+                                                void* stream) {
+    if (norm_weight == nullptr) return LEANKV_EINVAL;
+    return launch_swiglu(Wt_gate, Wt_up, h, y, N, Z, t_gate, t_up, workspace, workspace_bytes, active_elems,
+                         stream, norm_weight, eps);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -24,10 +24,15 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
     __shared__ float s_m[kAttnWarps][kGroup], s_l[kAttnWarps][kGroup];
     __shared__ int s_last;
 
-    pdl_begin();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // Pull the inverse rotation (a constant, 64 KB) towards L2 early: whichever CTA ends up merging
+    // the chunks needs it at the very end of the critical path.
+    if (chunk == 0 && kvh == 0 && b == 0)
+        for (int i = tid; i < kDim * kDim / 32; i += kAttnThreads)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Pi_v + i * 32));
+    pdl_begin();
     const int Hq = p.H * kGroup;
 
     const int seq_pg0 = p.indptr[b];
@@ -286,7 +291,7 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
 #pragma unroll
         for (int h = 0; h < kGroup; ++h) r[h][0] = r[h][1] = r[h][2] = r[h][3] = 0.f;
         const float4* pv = reinterpret_cast<const float4*>(p.Pi_v) + (size_t)(32 * warp) * (kDim / 4) + lane;
-#pragma unroll 8
+#pragma unroll
         for (int ii = 0; ii < 32; ++ii) {
             const float4 w4 = __ldg(pv + (size_t)ii * (kDim / 4));
             const int i = 32 * warp + ii;

@@ -103,6 +103,8 @@ class DecodeEngine:
         # per-layer rotations: seed + 2l for K, seed + 2l + 1 for V (leankv/turboquant/cache.py:59-71)
         self.Pi_k = [generate_rotation_matrix(128, dev, torch.float32, tq_seed + 2 * l).contiguous() for l in range(L)]
         self.Pi_v = [generate_rotation_matrix(128, dev, torch.float32, tq_seed + 2 * l + 1).contiguous() for l in range(L)]
+        self.Pi_k_t = [m.t().contiguous() for m in self.Pi_k]
+        self.Pi_v_t = [m.t().contiguous() for m in self.Pi_v]
         cents, bounds = get_codebook_tensors(128, 3, "cpu")
         self.centroids_host = cents.float().contiguous()
         self.centroids = self.centroids_host.to(dev)
@@ -121,6 +123,7 @@ class DecodeEngine:
         self.attn, self.o = half(self.nq * 128), half(cfg.hidden_size)
         self.q_rot = torch.zeros(self.nq * 128, dtype=torch.float32, device=dev)
         self.fused_post = True   # False: rope / append / query rotation as separate launches
+        self.fused_norm = True   # False: RMSNorm + residual add as launches of their own (always so under TP)
         self.mlp_h, self.down = half(self.inter), half(cfg.hidden_size)
         self.logits = half(cfg.vocab_size)
         self.token = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -257,16 +260,24 @@ class DecodeEngine:
     def _st(self) -> int:
         return torch.cuda.current_stream().cuda_stream
 
-    def _gemv(self, wt, x, y, t, segs=None):
+    def _gemv(self, wt, x, y, t, segs=None, residual=None, norm_w=None):
+        """y = [residual +] Wt^T . mask_t(x); with ``norm_w`` the kernel first applies RMSNorm(x; norm_w)."""
         z, n = wt.shape
         if segs is None:
-            rc = self.lib.leankv_sparse_gemv_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), n, z, t, None, None,
-                                                 self.ws_gemv.data_ptr(), self.ws_gemv.numel(),
-                                                 self.active_elems.data_ptr(), self._st())
+            segs = _native.Segments()
+            segs.n_segments = 1
+            segs.seg_end[0], segs.threshold[0] = n, t
+        if norm_w is not None:
+            rc = self.lib.leankv_sparse_gemv_rmsnorm_f16(wt.data_ptr(), x.data_ptr(), norm_w.data_ptr(),
+                                                         self.cfg.rms_eps, y.data_ptr(), n, z, ctypes.byref(segs),
+                                                         _native.ptr(residual), self.ws_gemv.data_ptr(),
+                                                         self.ws_gemv.numel(), self.active_elems.data_ptr(),
+                                                         self._st())
         else:
             rc = self.lib.leankv_sparse_gemv_seg_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), n, z,
-                                                     ctypes.byref(segs), None, None, self.ws_gemv.data_ptr(),
-                                                     self.ws_gemv.numel(), self.active_elems.data_ptr(), self._st())
+                                                     ctypes.byref(segs), None, _native.ptr(residual),
+                                                     self.ws_gemv.data_ptr(), self.ws_gemv.numel(),
+                                                     self.active_elems.data_ptr(), self._st())
         _native.check(rc, "sparse gemv")
         self.launches_per_step += 1
 
@@ -290,12 +301,16 @@ class DecodeEngine:
         cfg, lib, st = self.cfg, self.lib, self._st
         sp = self.state.data_ptr()
         lw, t = self.w["layers"][l], self.thresholds[l]
-        self._gemv(lw["wqkv_t"], self.x, self.qkv, 0.0, self._qkv_segments(l))
+        fused_norm = self.fused_norm and self.tp_size == 1
+        if fused_norm:   # RMSNorm of the residual stream happens inside the projection kernels
+            self._gemv(lw["wqkv_t"], self.h, self.qkv, 0.0, self._qkv_segments(l), norm_w=lw["ln1"])
+        else:
+            self._gemv(lw["wqkv_t"], self.x, self.qkv, 0.0, self._qkv_segments(l))
         probe("qkv")
         if self.fused_post:
             # rope(q, k) + rotate/quantize/pack of k, v into the page + query rotation: one launch
             _native.check(lib.leankv_decode_qkv_post(self.qkv.data_ptr(), self.inv_freq.data_ptr(), sp,
-                                                     self.Pi_k[l].data_ptr(), self.Pi_v[l].data_ptr(),
+                                                     self.Pi_k_t[l].data_ptr(), self.Pi_v_t[l].data_ptr(),
                                                      self.bounds.data_ptr(), self.pools[l].data_ptr(),
                                                      self.max_pages, self.page_indices.data_ptr(), self.nq,
                                                      self.nkv, self.q_rot.data_ptr(), st()), "decode_qkv_post")
@@ -324,6 +339,17 @@ class DecodeEngine:
                           "decode_attn")
             self.launches_per_step += 4     # rope, append, query rotation, attention
         probe("attn")
+        if fused_norm:
+            self._gemv(lw["wo_t"], self.attn, self.h, t["o_proj"], residual=self.h)      # h += o_proj(attn)
+            rc = lib.leankv_sparse_swiglu_rmsnorm_f16(
+                lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), self.h.data_ptr(), lw["ln2"].data_ptr(),
+                cfg.rms_eps, self.mlp_h.data_ptr(), self.inter, cfg.hidden_size, t["gate_proj"], t["up_proj"],
+                self.ws_gemv.data_ptr(), self.ws_gemv.numel(), self.active_elems.data_ptr(), st())
+            _native.check(rc, "sparse swiglu")
+            self.launches_per_step += 1
+            probe("mlp_h")
+            self._gemv(lw["wdown_t"], self.mlp_h, self.h, t["down_proj"], residual=self.h)  # h += down_proj(..)
+            return
         self._gemv(lw["wo_t"], self.attn, self.o, t["o_proj"])
         self._allreduce(self.o)
         probe("o")
@@ -350,10 +376,15 @@ class DecodeEngine:
         _native.check(lib.leankv_decode_begin(self.w["embed"].data_ptr(), self.token.data_ptr(), self.h.data_ptr(),
                                               cfg.hidden_size, cfg.vocab_size, sp, st()), "decode_begin")
         self.launches_per_step += 1
-        self._norm(None, self.w["layers"][0]["ln1"])
+        fused_norm = self.fused_norm and self.tp_size == 1
+        if not fused_norm:
+            self._norm(None, self.w["layers"][0]["ln1"])
         for l in range(cfg.num_layers):
             self._layer_launches(l)
-        self._gemv(self.w["lm_head_t"], self.x, self.logits, -1.0)
+        if fused_norm:
+            self._gemv(self.w["lm_head_t"], self.h, self.logits, -1.0, norm_w=self.w["final_norm"])
+        else:
+            self._gemv(self.w["lm_head_t"], self.x, self.logits, -1.0)
         _native.check(lib.leankv_decode_end(self.logits.data_ptr(), cfg.vocab_size, self.token.data_ptr(),
                                             self.history.data_ptr(), self.history_cap, sp, st()), "decode_end")
         self.launches_per_step += 1
