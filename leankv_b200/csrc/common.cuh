@@ -87,8 +87,15 @@ __device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
 // kernel before it has completed and its writes are visible. Nothing that depends on, or is read
 // by, an earlier kernel may be touched before pdl_wait(). Both are no-ops for a normal launch.
 __device__ __forceinline__ void pdl_begin() {
+#ifdef LEANKV_PDL_TRIGGER_FIRST
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+#else
+    // wait first: when a dependent starts early, everything before its immediate predecessor is
+    // complete and visible, and at most one kernel sits waiting behind the running one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+#endif
 }
 
 __device__ __forceinline__ float2 h2_to_f2(uint32_t packed) {

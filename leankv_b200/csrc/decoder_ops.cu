@@ -129,7 +129,17 @@ __global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, 
     pdl_begin();
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const int nvec = vocab >> 3;     // 16-byte loads; indices ascend within a thread, so '>' keeps the lowest
+    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(logits) + vi);
+        const __half* hp = reinterpret_cast<const __half*>(&a);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float v = __half2float(hp[q]);
+            if (v > best) { best = v; best_i = vi * 8 + q; }
+        }
+    }
+    for (int i = nvec * 8 + threadIdx.x; i < vocab; i += blockDim.x) {
         const float v = __half2float(logits[i]);
         if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
     }
@@ -197,6 +207,7 @@ extern "C" int leankv_rope_f16(const void* qkv, const float* inv_freq, const int
 extern "C" int leankv_decode_end(const void* logits, int vocab, long long* token, long long* history,
                                  int history_cap, int32_t* state, void* stream) {
     if (!logits || !token || !history || !state || vocab <= 0 || history_cap < 0) return LEANKV_EINVAL;
+    if (!aligned16(logits)) return LEANKV_EALIGN;
     LEANKV_CUDA_TRY(launch_kernel(decode_end_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream),
                                   static_cast<const __half*>(logits), vocab, token, history, history_cap, state));
     return LEANKV_OK;

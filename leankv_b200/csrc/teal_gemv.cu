@@ -55,7 +55,8 @@ struct GemvPlan {
 GemvPlan make_plan(int N, int Z, int arrays) {
     GemvPlan pl;
     pl.n_slices = (N + kColsPerCta - 1) / kColsPerCta;
-    int target = sm_count() * kCtasPerSm;
+    // resident CTAs per SM: 4 for the plain kernel (64 registers), 3 for the SwiGLU kernel (80)
+    int target = sm_count() * (arrays == 2 ? 3 : kCtasPerSm);
     int ks = target / pl.n_slices;
     if (ks < 1) ks = 1;
     int by_rows = Z / 32;            // keep at least ~32 input channels per split
