@@ -93,7 +93,9 @@ def test_config2_fused_swiglu_full_size(golden_teal):
     # equals two sparse GEMVs + act_fn(gate) * up, the way the reference composes it
     g = sparse_gemv(c.x.reshape(1, 1, -1), wg, c.threshold)
     u = sparse_gemv(c.x.reshape(1, 1, -1), wu, c.threshold)
-    assert torch.equal(y, (torch.nn.functional.silu(g) * u).reshape(-1))
+    # (the fused kernel splits the input channels differently, so its fp32 sums round differently)
+    composed = (torch.nn.functional.silu(g) * u).reshape(-1)
+    assert rel_l2(y.cpu(), composed.cpu()) < TOL and (y != composed).float().mean() < 0.05
     assert torch.equal(y, sparse_swiglu(c.x.reshape(1, 1, -1), wg, wu, c.threshold, c.threshold).reshape(-1))
 
 
