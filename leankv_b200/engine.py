@@ -405,7 +405,8 @@ class DecodeEngine:
                 p.copy_(s)
             self.active_elems.copy_(snap[4])
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
+            # thread_local: the NCCL watchdog thread (tensor parallel runs) may touch CUDA while we capture
+            with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
                 self._step_launches()
             # capture does not execute; state is unchanged
 
