@@ -130,23 +130,30 @@ __device__ __forceinline__ Unit load_unit(const uint32_t* words, int ui) {
 }
 
 // ---- query rotation --------------------------------------------------------
+// q_rot[v][j] = sum_k Pi_k[j][k] q[v][k] (ascending k). One CTA rotates the kGroup query heads of a
+// (sequence, kv head) pair, so each row of Pi_k is fetched once per four heads.
 __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const float* Pi_k, float* qprime) {
-    __shared__ float s_q[kDim];
+    __shared__ float s_q[kGroup][kDim];
     pdl_begin();
-    const int v = blockIdx.x, j = threadIdx.x;
-    s_q[j] = __half2float(q[(size_t)v * kDim + j]);
+    const int v0 = blockIdx.x * kGroup, j = threadIdx.x;
+#pragma unroll
+    for (int h = 0; h < kGroup; ++h) s_q[h][j] = __half2float(q[(size_t)(v0 + h) * kDim + j]);
     __syncthreads();
     const float4* row = reinterpret_cast<const float4*>(Pi_k + (size_t)j * kDim);
-    float acc = 0.f;
-#pragma unroll 8
+    float acc[kGroup] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 16
     for (int k4 = 0; k4 < kDim / 4; ++k4) {
         const float4 pv = __ldg(row + k4);
-        acc = fmaf(pv.x, s_q[4 * k4 + 0], acc);
-        acc = fmaf(pv.y, s_q[4 * k4 + 1], acc);
-        acc = fmaf(pv.z, s_q[4 * k4 + 2], acc);
-        acc = fmaf(pv.w, s_q[4 * k4 + 3], acc);
+#pragma unroll
+        for (int h = 0; h < kGroup; ++h) {
+            acc[h] = fmaf(pv.x, s_q[h][4 * k4 + 0], acc[h]);
+            acc[h] = fmaf(pv.y, s_q[h][4 * k4 + 1], acc[h]);
+            acc[h] = fmaf(pv.z, s_q[h][4 * k4 + 2], acc[h]);
+            acc[h] = fmaf(pv.w, s_q[h][4 * k4 + 3], acc[h]);
+        }
     }
-    qprime[(size_t)v * kDim + j] = acc;
+#pragma unroll
+    for (int h = 0; h < kGroup; ++h) qprime[(size_t)(v0 + h) * kDim + j] = acc[h];
 }
 
 // ---- main kernel -----------------------------------------------------------
@@ -276,7 +283,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     const float* qprime = q_rot;
     if (q != nullptr) {
         float* dst = reinterpret_cast<float*>(ws + pl.off_qprime);
-        LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel, dim3(B * n_q_heads), dim3(128), 0, st,
+        LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel, dim3(B * n_kv_heads), dim3(128), 0, st,
                                       static_cast<const __half*>(q), Pi_k, dst));
         qprime = dst;
     }

@@ -178,8 +178,11 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
         const int src0 = (2 * t) * 4 + head, src1 = src0 + 4;
         const float x0 = __shfl_sync(0xffffffffu, wa, src0), x1 = __shfl_sync(0xffffffffu, wa, src1);
         const float x2 = __shfl_sync(0xffffffffu, wb, src0), x3 = __shfl_sync(0xffffffffu, wb, src1);
-        const uint32_t b0 = pack_h2(split_part(x0, part), split_part(x1, part));
-        const uint32_t b1 = pack_h2(split_part(x2, part), split_part(x3, part));
+        // fp16 rounding of the probabilities is independent from token to token and averages out over
+        // the sum, unlike rounding of the query or of the centroids: no hi/lo split here, the "lo"
+        // columns of the value MMA are fed zeros
+        const uint32_t b0 = part ? 0u : pack_h2(x0, x1);
+        const uint32_t b1 = part ? 0u : pack_h2(x2, x3);
         {
             const Unit ua = load_unit(vw, lane), ub = load_unit(vw, 32 + lane);
 #pragma unroll
