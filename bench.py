@@ -300,6 +300,116 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
                                        "note": "two launches per call: query rotation + attention"}
 
 
+# ── batched long-context decode (sequences sharded over the ranks, no collective) ────────
+
+BATCH_TOTAL, BATCH_CTX = 80, 4096
+BATCH_METRIC = "batched decode tok/s (Llama-3-8B shape, 80 seq x 4096 ctx, 3-bit paged KV)"
+
+
+def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
+    """Every rank serves its slice of the 80 sequences with a full copy of the weights. Returns the
+    whole-job numbers (identical on every rank): device-timed and host-I/O-timed tok/s, and the
+    attention kernel of one layer timed alone."""
+    import torch
+    import torch.distributed as dist
+
+    from leankv_b200.batch_engine import BatchDecodeEngine, partition_batch
+    from leankv_b200.engine import DecoderConfig
+
+    cfg = DecoderConfig.llama3_8b() if not small else DecoderConfig(
+        vocab_size=4096, hidden_size=1024, intermediate_size=2048, num_layers=4, num_q_heads=8, num_kv_heads=2,
+        rope_theta=5e5)
+    total, ctx = (BATCH_TOTAL, BATCH_CTX) if not small else (16, 256)
+    mine = partition_batch(total, world, rank)
+    B = len(mine)
+    eng = BatchDecodeEngine.random_init(cfg, dev, B, seed=0, max_seq_len=ctx + 2 * (W + K) + 32)
+    gen = torch.Generator().manual_seed(4321)
+    prompts = torch.randint(0, cfg.vocab_size, (total, ctx), generator=gen)[mine.start:mine.stop]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(sec):
+        if world > 1:
+            t = torch.tensor([sec], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        return sec
+
+    t0 = time.perf_counter()
+    eng.prefill(prompts)
+    torch.cuda.synchronize()
+    prefill_s = reduce_max(time.perf_counter() - t0)
+    eng.capture()
+    pin_in = torch.zeros(B, dtype=torch.int64).pin_memory()
+    pin_out = torch.zeros(B, dtype=torch.int64).pin_memory()
+
+    def timed(host_io):
+        for _ in range(W):
+            eng.graph.replay()
+        torch.cuda.synchronize()
+        pin_in.copy_(eng.tokens.cpu())
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(K):
+            if host_io:
+                eng.tokens.copy_(pin_in, non_blocking=True)
+            eng.graph.replay()
+            if host_io:
+                pin_out.copy_(eng.tokens, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                pin_in.copy_(pin_out)
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        barrier()
+        return reduce_max(wall if host_io else e0.elapsed_time(e1) * 1e-3)
+
+    sec = timed(False)
+    sec_e2e = timed(True)
+    ctx_mid = ctx + W + K // 2
+
+    # the attention launch of one layer alone, rotating over the layers' pools (each larger than L2)
+    st = torch.cuda.current_stream().cuda_stream
+    import math
+    lib = eng.lib
+    n_l = cfg.num_layers
+
+    def attn(i):
+        l = i % n_l
+        lib.leankv_tq_decode_attn_rotated(eng.q_rot.data_ptr(), eng.attn.data_ptr(), B, eng.nq, eng.nkv,
+                                          eng.pools[l].data_ptr(), eng.max_pages, eng.kv_indptr.data_ptr(),
+                                          eng.kv_page_indices.data_ptr(), eng.kv_last.data_ptr(), eng.pps,
+                                          eng.Pi_v[l].data_ptr(), eng.centroids_host.data_ptr(),
+                                          1.0 / math.sqrt(128.0), eng.ws_attn.data_ptr(), eng.ws_attn.numel(), st)
+    t_attn = time_kernel(attn, n_l, attn_iters)
+    n_tok = int(eng.pos[0].item())
+    alg_attn = 2 * B * eng.nkv * n_tok * 50 + B * eng.nq * 128 * (4 + 2) + 4 * (B * ((n_tok + 15) // 16) + 2 * B + 1)
+    weight_bytes = 2 * sum(w.numel() for lw in eng.w["layers"] for k, w in lw.items()
+                           if k in ("wqkv_t", "wo_t", "wgu_t", "wdown_t")) + 2 * eng.w["lm_head_t"].numel()
+    kv_step = eng.kv_bytes_per_sequence(ctx_mid) * B
+    out = {
+        "metric": BATCH_METRIC, "value": total * K / sec, "unit": "tok/s", "steps": K, "warmup": W,
+        "ms_per_step": sec / K * 1e3, "scaling": "strong", "sequences_total": total, "sequences_per_gpu": B,
+        "context": ctx, "e2e": {"value": total * K / sec_e2e, "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
+                                "d2h_bytes_per_step": 8 * B},
+        "kv_bytes_per_sequence": eng.kv_bytes_per_sequence(ctx),
+        "kv_bytes_per_sequence_fp16": 2 * cfg.num_layers * cfg.num_kv_heads * 128 * 2 * ctx,
+        "prefill_s": prefill_s, "gpu_launches": eng.launches_per_step * K, "library_gemms": eng.gemms_per_step * K,
+        "bytes_per_step_per_gpu": {"weights": weight_bytes, "kv": kv_step},
+        "step_gbs_per_gpu": (weight_bytes + kv_step) / (sec / K) / 1e9,
+        "attn_kernel": {"us": t_attn * 1e6, "algorithmic_bytes": alg_attn, "gbs": alg_attn / t_attn / 1e9,
+                        "tokens_per_sequence": n_tok},
+    }
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
 # ── main leg: the decode loop ─────────────────────────────────────────────────────────────
 
 def run_ours(args):
@@ -397,13 +507,19 @@ def run_ours(args):
     dense_streamed = eng.bytes_streamed()
     eng.set_thresholds({l: t for l, t in enumerate(sparse_thresholds)})
 
+    ctx_mid = PROMPT_LEN + W + K // 2
+    kv_bytes = eng.kv_bytes_per_token() * ctx_mid                       # read per step, this rank
+    launches_per_step = eng.launches_per_step
+    del eng
+    torch.cuda.empty_cache()
+    batched = None
+    if not args.no_batched:
+        batched = batched_decode_leg(dev, world, rank, args.batched_steps, W, small=args.small)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    ctx_mid = PROMPT_LEN + W + K // 2
-    kv_bytes = eng.kv_bytes_per_token() * ctx_mid                       # read per step, this rank
     step_bytes = streamed / K + kv_bytes
     line = {
         "metric": METRIC, "value": K / sec, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -413,14 +529,16 @@ def run_ours(args):
         "gpu_launches": launches,
         "step": {"weight_bytes_streamed_per_step_per_gpu": streamed / K, "kv_bytes_per_step_per_gpu": kv_bytes,
                  "gbs_per_gpu": step_bytes / (sec / K) / 1e9, "frac_of_peak": step_bytes / (sec / K) / 1e9 / peak_gbs,
-                 "launches_per_step": eng.launches_per_step,
+                 "launches_per_step": launches_per_step,
                  "dense_same_engine_tok_s": K / sec_dense,
                  "dense_weight_bytes_per_step_per_gpu": dense_streamed / K,
                  "speedup_vs_dense_same_engine": sec_dense / sec},
     }
+    if batched is not None:
+        batched["attn_kernel"]["frac"] = batched["attn_kernel"]["gbs"] / peak_gbs
+        batched["step_frac_of_peak"] = batched["step_gbs_per_gpu"] / peak_gbs
+        line["batched_decode"] = batched
     if world == 1 and not args.small:
-        del eng
-        torch.cuda.empty_cache()
         legs = kernel_legs(dev, peak_gbs)
         g = legs["sparse_gemv_4096x14336"]
         line["roofline"] = {"bound": "hbm", "kernel": "sparse_gemv_kernel<false> (config 1: 4096 x 14336, 40 % sparse)",
@@ -442,6 +560,45 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_batched(args):
+    """``--workload batched``: the 80-sequence decode alone, as a line of its own (128 steps by default)."""
+    import torch
+    import torch.distributed as dist
+
+    from leankv_b200 import _native
+
+    _native.lib()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)   # barrier + max-over-ranks timing only
+    K = args.steps if args.steps_given else 128
+    sampler = ClockSampler(local)
+    sampler.start()
+    out = batched_decode_leg(dev, world, rank, K, args.warmup, small=args.small)
+    sampler.stop()
+    if rank == 0:
+        peak_gbs, peak_src = _peaks()
+        a = out["attn_kernel"]
+        out.update({"n_gpus": world, "higher_is_better": True, "vs_baseline": None, "dtype": "f16",
+                    "data": "synthetic", "clocks": sampler.summary(),
+                    "config": {"workload": "Llama-3-8B shape, random-init fp16, 80 sequences x 4096-token context of "
+                                           "uniform-random tokens, 3-bit TurboQuant paged KV, dense projections",
+                               "parallelism": f"sequences sharded over {world} GPU(s), weights replicated, no collective",
+                               "l2": "weights + KV read per step exceed L2"},
+                    "roofline": {"bound": "hbm", "kernel": "tq_decode_attn_kernel (one layer, this rank's sequences)",
+                                 "achieved": a["gbs"], "peak": peak_gbs, "unit": "GB/s", "frac": a["gbs"] / peak_gbs,
+                                 "traffic": None, "peak_source": peak_src}})
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -455,11 +612,19 @@ def main():
     ap.add_argument("--only-legs", default="",
                     help="comma list of gemv,swiglu,attn: run just those kernel legs and print their JSON")
     ap.add_argument("--leg-iters", type=int, default=200)
+    ap.add_argument("--workload", choices=["decode", "batched"], default="decode",
+                    help="decode: batch-1 TEAL + TurboQuant decode loop (the headline metric), with a short "
+                         "batched leg attached; batched: only the 80-sequence long-context decode, its own line")
+    ap.add_argument("--no-batched", action="store_true", help="skip the batched-decode leg of the default run")
+    ap.add_argument("--batched-steps", type=int, default=32)
     args = ap.parse_args()
+    args.steps_given = any(a == "--steps" or a.startswith("--steps=") for a in sys.argv[1:])
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "batched":
+        run_batched(args)
     elif args.only_legs:
         import torch
 

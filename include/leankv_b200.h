@@ -252,6 +252,42 @@ int leankv_decode_qkv_post(const void* qkv, const float* inv_freq, const int32_t
 int leankv_decode_end(const void* logits, int vocab, long long* token, long long* history,
                       int history_cap, int32_t* state, void* stream);
 
+/* ------------------------------------------------------------------------- *
+ * Glue kernels of a batched decode step (B sequences, one new token each, dense library
+ * GEMMs between them: the reference runs its dense path at batch > 1,
+ * leankv/teal/patching.py:155-157, with HF modules around the cache). Like the batch-1
+ * set they have no reference counterpart; they keep positions and the page table on the
+ * device so that a step replays as one CUDA graph.
+ *
+ * Sequence b has pos[b] tokens cached and owns the pages block_table[b][0..max_pages_per_seq);
+ * each step the flat (kv_indptr, kv_page_indices, kv_last_page_len) triple of
+ * leankv/turboquant/paged_cache.py:215-233 is rebuilt from them.
+ * ------------------------------------------------------------------------- */
+/* RMSNorm of `rows` independent vectors (x, delta, y: fp16 [rows][n]); see leankv_rmsnorm_f16. */
+int leankv_rmsnorm_rows_f16(void* x, const void* delta, const void* weight, void* y, int rows, int n,
+                            float eps, void* stream);
+/* h[b] = embed_table[tokens[b]]; kv_indptr [B+1], kv_page_indices [sum of pages in use],
+ * kv_last_page_len [B] for the step that appends one token to every sequence. */
+int leankv_batch_decode_begin(const void* embed_table, const long long* tokens, void* h, int hidden,
+                              int vocab, int B, const int32_t* pos, const int32_t* block_table,
+                              int max_pages_per_seq, int32_t* kv_indptr, int32_t* kv_page_indices,
+                              int32_t* kv_last_page_len, void* stream);
+/* leankv_decode_qkv_post for B sequences: qkv fp16 [B][(n_q_heads + 2 n_kv_heads) * 128],
+ * q_rot fp32 [B][n_q_heads][128]; token of sequence b goes to position pos[b], page
+ * kv_page_indices[kv_indptr[b] + pos[b] / 16]. */
+int leankv_batch_qkv_post(const void* qkv, int B, const float* inv_freq, const int32_t* pos,
+                          const int32_t* kv_indptr, const float* Pi_k_t, const float* Pi_v_t,
+                          const float* decision_boundaries, void* pool, int n_pages,
+                          const int32_t* kv_page_indices, int n_q_heads, int n_kv_heads,
+                          float* q_rot, void* stream);
+/* out[r][i] = fp16(silu(gate_up[r][i])) * gate_up[r][inter + i]  (LlamaMLP's act_fn(gate) * up). */
+int leankv_silu_mul_f16(const void* gate_up, void* out, int rows, int inter, void* stream);
+/* Per sequence: tokens[b] = argmax(logits[b]) (lowest index on ties);
+ * history[b][steps[b]] = tokens[b]; steps[b] += 1; pos[b] += 1. vocab % 8 == 0. */
+int leankv_batch_decode_end(const void* logits, int vocab, int B, long long* tokens,
+                            long long* history, int history_cap, int32_t* pos, int32_t* steps,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

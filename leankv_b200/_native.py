@@ -77,6 +77,14 @@ SIGNATURES = {
     "leankv_rope_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                 c_void_p]),
     "leankv_decode_end": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "leankv_rmsnorm_rows_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "leankv_batch_decode_begin": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "leankv_batch_qkv_post": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "leankv_silu_mul_f16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "leankv_batch_decode_end": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p]),
 }
 
 _lib = None

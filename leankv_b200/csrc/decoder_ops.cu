@@ -5,6 +5,8 @@
 // Rounding points follow the HF eager modules the reference runs around its kernels
 // (transformers modeling_mistral.py: MistralRMSNorm, apply_rotary_pos_emb).
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace leankv {
@@ -28,7 +30,7 @@ __device__ __forceinline__ float block_sum(float v, float* s_tmp) {
 
 // Optional residual update h += delta (fp16 add, as the decoder block does), then
 // y = w * fp16( h * rsqrt(mean(h^2) + eps) ), statistics in fp32.
-// One CTA; 16-byte accesses; the (updated) row stays in registers between the two phases
+// One CTA per row; 16-byte accesses; the (updated) row stays in registers between the two phases
 // (n % 8 == 0, n <= kNormThreads * 8 * kNormVecs).
 constexpr int kNormThreads = 512;
 constexpr int kNormVecs = 4;
@@ -37,6 +39,9 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(__half* x, const 
     __shared__ float s_tmp[32];
     pdl_begin();
     const int nvec = n >> 3;
+    x += (size_t)blockIdx.x * n;
+    y += (size_t)blockIdx.x * n;
+    if (delta != nullptr) delta += (size_t)blockIdx.x * n;
     uint4 v[kNormVecs];
     float ss = 0.f;
 #pragma unroll
@@ -121,12 +126,18 @@ __global__ void __launch_bounds__(64) rope_kernel(const __half* qkv, const float
 }
 
 // Greedy next token (lowest index wins ties), appended to the history; advances the position.
+// One CTA per sequence: pos / step are that sequence's words.
 __global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, int vocab,
                                                           long long* token, long long* history,
-                                                          int history_cap, int* state) {
+                                                          int history_cap, int* pos, int* step_ptr) {
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     pdl_begin();
+    logits += (size_t)blockIdx.x * vocab;
+    token += blockIdx.x;
+    history += (size_t)blockIdx.x * history_cap;
+    pos += blockIdx.x;
+    step_ptr += blockIdx.x;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     const int nvec = vocab >> 3;     // 16-byte loads; indices ascend within a thread, so '>' keeps the lowest
@@ -157,10 +168,71 @@ __global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, 
             if (s_v[w] > best || (s_v[w] == best && s_i[w] < best_i)) { best = s_v[w]; best_i = s_i[w]; }
         if (best_i == 0x7fffffff) best_i = 0;   // all-NaN row
         *token = best_i;
-        const int step = state[kStep];
+        const int step = *step_ptr;
         if (step < history_cap) history[step] = best_i;
-        state[kStep] = step + 1;
-        state[kPos] = state[kPos] + 1;
+        *step_ptr = step + 1;
+        *pos = *pos + 1;
+    }
+}
+
+// Batched step prologue: embedding rows of B tokens, and the flat page table of this step built from
+// a per-sequence block table. Sequence b caches pos[b] tokens and appends one: it uses
+// pos[b] / 16 + 1 pages, the first entries of block_table[b][0..max_pps). One CTA per sequence; each
+// derives its own offset from the positions of the sequences before it, so no CTA waits on another.
+__global__ void __launch_bounds__(256) batch_begin_kernel(const __half* table, const long long* tokens,
+                                                          __half* h, int hidden, int vocab, int B,
+                                                          const int* pos, const int* block_table, int max_pps,
+                                                          int* kv_indptr, int* kv_page_indices,
+                                                          int* kv_last_page_len) {
+    __shared__ int s_part[8];
+    pdl_begin();
+    const int b = blockIdx.x;
+    long long tok = tokens[b];
+    if (tok < 0 || tok >= vocab) tok = 0;
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(h + (size_t)b * hidden);
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+
+    int before = 0;
+    for (int i = threadIdx.x; i < b; i += blockDim.x) before += min(pos[i] / 16 + 1, max_pps);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = before;
+    __syncthreads();
+    int start = 0;
+    for (int w = 0; w < 8; ++w) start += s_part[w];
+    const int mine = min(pos[b] / 16 + 1, max_pps);
+    for (int i = threadIdx.x; i < mine; i += blockDim.x)
+        kv_page_indices[start + i] = block_table[(size_t)b * max_pps + i];
+    if (threadIdx.x == 0) {
+        kv_indptr[b] = start;
+        if (b == B - 1) kv_indptr[B] = start + mine;
+        kv_last_page_len[b] = pos[b] % 16 + 1;
+    }
+}
+
+// out = fp16(silu(gate)) * up, the rounding points of the HF MLP (act_fn output is an fp16 tensor).
+// gate_up: [rows][2 * inter] (gate columns first); out: [rows][inter].
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gate_up, __half* out, int inter, int rows) {
+    pdl_begin();
+    const int nvec = inter >> 3;
+    const long long total = (long long)rows * nvec;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / nvec), c = (int)(i - (long long)r * nvec);
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gate_up + (size_t)r * 2 * inter) + c);
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(gate_up + (size_t)r * 2 * inter + inter) + c);
+        const __half2* gh = reinterpret_cast<const __half2*>(&g);
+        const __half2* uh = reinterpret_cast<const __half2*>(&u);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 f = __half22float2(gh[q]);
+            const __half2 act = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+            oh[q] = __hmul2(act, uh[q]);
+        }
+        reinterpret_cast<uint4*>(out + (size_t)r * inter)[c] = o;
     }
 }
 
@@ -209,6 +281,57 @@ extern "C" int leankv_decode_end(const void* logits, int vocab, long long* token
     if (!logits || !token || !history || !state || vocab <= 0 || history_cap < 0) return LEANKV_EINVAL;
     if (!aligned16(logits)) return LEANKV_EALIGN;
     LEANKV_CUDA_TRY(launch_kernel(decode_end_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream),
-                                  static_cast<const __half*>(logits), vocab, token, history, history_cap, state));
+                                  static_cast<const __half*>(logits), vocab, token, history, history_cap,
+                                  state + kPos, state + kStep));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_rmsnorm_rows_f16(void* x, const void* delta, const void* weight, void* y, int rows, int n,
+                                       float eps, void* stream) {
+    if (!x || !weight || !y || n <= 0 || rows <= 0) return LEANKV_EINVAL;
+    if (n % 8 != 0 || !aligned16(x) || !aligned16(weight) || !aligned16(y) || (delta && !aligned16(delta)))
+        return LEANKV_EALIGN;
+    if (n > kNormThreads * 8 * kNormVecs) return LEANKV_ELIMIT;
+    LEANKV_CUDA_TRY(launch_kernel(rmsnorm_kernel, dim3(rows), dim3(kNormThreads), 0,
+                                  static_cast<cudaStream_t>(stream), static_cast<__half*>(x),
+                                  static_cast<const __half*>(delta), static_cast<const __half*>(weight),
+                                  static_cast<__half*>(y), n, eps));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_batch_decode_begin(const void* embed_table, const long long* tokens, void* h, int hidden,
+                                         int vocab, int B, const int32_t* pos, const int32_t* block_table,
+                                         int max_pages_per_seq, int32_t* kv_indptr, int32_t* kv_page_indices,
+                                         int32_t* kv_last_page_len, void* stream) {
+    if (!embed_table || !tokens || !h || !pos || !block_table || !kv_indptr || !kv_page_indices ||
+        !kv_last_page_len || hidden <= 0 || vocab <= 0 || B <= 0 || max_pages_per_seq <= 0)
+        return LEANKV_EINVAL;
+    if (hidden % 8 != 0 || !aligned16(embed_table) || !aligned16(h)) return LEANKV_EALIGN;
+    LEANKV_CUDA_TRY(launch_kernel(batch_begin_kernel, dim3(B), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                  static_cast<const __half*>(embed_table), tokens, static_cast<__half*>(h), hidden,
+                                  vocab, B, pos, block_table, max_pages_per_seq, kv_indptr, kv_page_indices,
+                                  kv_last_page_len));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_silu_mul_f16(const void* gate_up, void* out, int rows, int inter, void* stream) {
+    if (!gate_up || !out || rows <= 0 || inter <= 0) return LEANKV_EINVAL;
+    if (inter % 8 != 0 || !aligned16(gate_up) || !aligned16(out)) return LEANKV_EALIGN;
+    const long long total = (long long)rows * (inter / 8);
+    const int grid = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 8);
+    LEANKV_CUDA_TRY(launch_kernel(silu_mul_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                  static_cast<const __half*>(gate_up), static_cast<__half*>(out), inter, rows));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_batch_decode_end(const void* logits, int vocab, int B, long long* tokens,
+                                       long long* history, int history_cap, int32_t* pos, int32_t* steps,
+                                       void* stream) {
+    if (!logits || !tokens || !history || !pos || !steps || vocab <= 0 || B <= 0 || history_cap < 0)
+        return LEANKV_EINVAL;
+    if (!aligned16(logits) || vocab % 8 != 0) return LEANKV_EALIGN;
+    LEANKV_CUDA_TRY(launch_kernel(decode_end_kernel, dim3(B), dim3(1024), 0, static_cast<cudaStream_t>(stream),
+                                  static_cast<const __half*>(logits), vocab, tokens, history, history_cap, pos,
+                                  steps));
     return LEANKV_OK;
 }

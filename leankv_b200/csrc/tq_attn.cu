@@ -169,10 +169,22 @@ AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     AttnPlan pl;
     if (max_pages < 1) max_pages = 1;
     const long long pairs = (long long)B * Hkv;
-    // Chunks per (sequence, kv head): as many as keep the whole grid resident at once (6 CTAs per
-    // SM), so that no SM idles waiting for a second round while others run a third.
+    // Chunks per (sequence, kv head). A warp tracks at most 32 pages, which sets the minimum. When the
+    // whole grid fits on the GPU at once (6 CTAs per SM) use as many chunks as still fit, so that no
+    // SM idles waiting for a second round. Otherwise pick, among the next few chunk counts, the one
+    // whose last round of CTAs is fullest.
     const long long slots = (long long)sm_count() * 6;
-    long long nc = slots / (pairs > 0 ? pairs : 1);
+    const long long np = pairs > 0 ? pairs : 1;
+    const long long nc_min = (max_pages + 32 * kAttnWarps - 1) / (32 * kAttnWarps);
+    long long nc = slots / np;
+    if (nc < nc_min) {
+        double best = -1.0;
+        for (long long c = nc_min; c < nc_min + 8 && c <= kMaxChunks; ++c) {
+            const long long ctas = np * c, rounds = (ctas + slots - 1) / slots;
+            const double eff = (double)ctas / (double)(rounds * slots);
+            if (eff > best + 0.02) { best = eff; nc = c; }
+        }
+    }
     if (nc < 1) nc = 1;
     long long ppw = (max_pages + nc * kAttnWarps - 1) / (nc * kAttnWarps);
     if (ppw < 1) ppw = 1;

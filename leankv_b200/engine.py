@@ -118,12 +118,12 @@ class DecodeEngine:
         self.page_indices = perm.to(torch.int32).to(dev)
 
         half = lambda n: torch.zeros(n, dtype=torch.float16, device=dev)
-        self.h, self.x = half(cfg.hidden_size), half(cfg.hidden_size)
+        self.h, self.x, self.h2 = half(cfg.hidden_size), half(cfg.hidden_size), half(cfg.hidden_size)
         self.qkv, self.q_rope, self.k_rope = half(self.n_qkv), half(self.nq * 128), half(self.nkv * 128)
         self.attn, self.o = half(self.nq * 128), half(cfg.hidden_size)
         self.q_rot = torch.zeros(self.nq * 128, dtype=torch.float32, device=dev)
         self.fused_post = True   # False: rope / append / query rotation as separate launches
-        self.fused_norm = True   # False: RMSNorm + residual add as launches of their own (always so under TP)
+        self.fused_norm = True   # False: RMSNorm + residual add as launches of their own
         self.mlp_h, self.down = half(self.inter), half(cfg.hidden_size)
         self.logits = half(cfg.vocab_size)
         self.token = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -196,6 +196,12 @@ class DecodeEngine:
         keeps its slice, so that the sharded model equals the single-GPU one.
         """
         dev = torch.device(device)
+        return cls(cfg, cls.random_weights(cfg, dev, seed, tp_rank, tp_size), dev, tp_rank=tp_rank,
+                   tp_size=tp_size, **kw)
+
+    @staticmethod
+    def random_weights(cfg: DecoderConfig, dev, seed: int = 0, tp_rank: int = 0, tp_size: int = 1) -> dict:
+        """The weight dict of ``random_init`` (kernel layout, this rank's slices)."""
         gen = torch.Generator(device=dev).manual_seed(seed)
         nq, nkv, it = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.intermediate_size // tp_size
         H = cfg.hidden_size
@@ -226,7 +232,7 @@ class DecodeEngine:
                 "wdown_t": d_t[tp_rank * it:(tp_rank + 1) * it].contiguous(),
             })
             del o_t, g_t, u_t, d_t
-        return cls(cfg, w, dev, tp_rank=tp_rank, tp_size=tp_size, **kw)
+        return w
 
     # ── thresholds ───────────────────────────────────────────────────────
 
@@ -301,7 +307,7 @@ class DecodeEngine:
         cfg, lib, st = self.cfg, self.lib, self._st
         sp = self.state.data_ptr()
         lw, t = self.w["layers"][l], self.thresholds[l]
-        fused_norm = self.fused_norm and self.tp_size == 1
+        fused_norm = self.fused_norm
         if fused_norm:   # RMSNorm of the residual stream happens inside the projection kernels
             self._gemv(lw["wqkv_t"], self.h, self.qkv, 0.0, self._qkv_segments(l), norm_w=lw["ln1"])
         else:
@@ -340,15 +346,25 @@ class DecodeEngine:
             self.launches_per_step += 4     # rope, append, query rotation, attention
         probe("attn")
         if fused_norm:
-            self._gemv(lw["wo_t"], self.attn, self.h, t["o_proj"], residual=self.h)      # h += o_proj(attn)
+            # Single rank: h += o_proj(attn) in place. Tensor parallel: every rank writes its partial
+            # product to a second buffer, rank 0 alone adds the residual stream to its partial, and the
+            # all-reduce leaves the updated stream on every rank (the down projection comes back the
+            # same way), so a block is 5 kernels + 2 all-reduces.
+            tp = self.tp_size > 1
+            h_mid = self.h2 if tp else self.h
+            res = self.h if (not tp or self.tp_rank == 0) else None
+            self._gemv(lw["wo_t"], self.attn, h_mid, t["o_proj"], residual=res)
+            self._allreduce(h_mid)
             rc = lib.leankv_sparse_swiglu_rmsnorm_f16(
-                lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), self.h.data_ptr(), lw["ln2"].data_ptr(),
+                lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), h_mid.data_ptr(), lw["ln2"].data_ptr(),
                 cfg.rms_eps, self.mlp_h.data_ptr(), self.inter, cfg.hidden_size, t["gate_proj"], t["up_proj"],
                 self.ws_gemv.data_ptr(), self.ws_gemv.numel(), self.active_elems.data_ptr(), st())
             _native.check(rc, "sparse swiglu")
             self.launches_per_step += 1
             probe("mlp_h")
-            self._gemv(lw["wdown_t"], self.mlp_h, self.h, t["down_proj"], residual=self.h)  # h += down_proj(..)
+            res = h_mid if (not tp or self.tp_rank == 0) else None
+            self._gemv(lw["wdown_t"], self.mlp_h, self.h, t["down_proj"], residual=res)  # h = h_mid + down_proj(..)
+            self._allreduce(self.h)
             return
         self._gemv(lw["wo_t"], self.attn, self.o, t["o_proj"])
         self._allreduce(self.o)
@@ -376,7 +392,7 @@ class DecodeEngine:
         _native.check(lib.leankv_decode_begin(self.w["embed"].data_ptr(), self.token.data_ptr(), self.h.data_ptr(),
                                               cfg.hidden_size, cfg.vocab_size, sp, st()), "decode_begin")
         self.launches_per_step += 1
-        fused_norm = self.fused_norm and self.tp_size == 1
+        fused_norm = self.fused_norm
         if not fused_norm:
             self._norm(None, self.w["layers"][0]["ln1"])
         for l in range(cfg.num_layers):
@@ -421,11 +437,14 @@ class DecodeEngine:
 
     # ── prefill (dense) ──────────────────────────────────────────────────
 
-    def _dense_forward(self, ids: torch.Tensor, write_cache: bool, collect: Optional[dict] = None):
-        """Prompt pass with library GEMMs. Returns the final hidden state of the last token."""
+    def _dense_forward(self, ids: torch.Tensor, write_cache: bool, collect: Optional[dict] = None,
+                       page_indices: Optional[torch.Tensor] = None):
+        """Prompt pass with library GEMMs. Returns the final hidden state of the last token.
+        ``page_indices``: the pages of the sequence being filled (default: the engine's single sequence)."""
         from .turboquant.quantizer import MSEQuantized, TurboQuantMSE  # noqa: F401
 
         cfg, T = self.cfg, ids.numel()
+        pages = self.page_indices if page_indices is None else page_indices
         pos = torch.arange(T, device=self.dev).float()
         ang = torch.outer(pos, self.inv_freq)
         emb = torch.cat((ang, ang), dim=-1)
@@ -454,9 +473,9 @@ class DecodeEngine:
                                                     self.Pi_k[l].data_ptr(), self.Pi_v[l].data_ptr(),
                                                     self.bounds.data_ptr(), self.pools[l].data_ptr(),
                                                     self.max_pages, indptr.data_ptr(),
-                                                    self.page_indices.data_ptr(), start.data_ptr(), self._st())
+                                                    pages.data_ptr(), start.data_ptr(), self._st())
                 _native.check(rc, "pool_append")
-                kh, vh = self._dense_kv(l, T)
+                kh, vh = self._dense_kv(l, T, pages)
             else:
                 kh, vh = self._roundtrip(kh, l, 0), self._roundtrip(vh, l, 1)
             a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), kh, vh, is_causal=True,
@@ -476,15 +495,16 @@ class DecodeEngine:
             h = h + d
         return _rmsnorm(h[-1], self.w["final_norm"], cfg.rms_eps)
 
-    def _dense_kv(self, l: int, T: int):
+    def _dense_kv(self, l: int, T: int, page_indices: Optional[torch.Tensor] = None):
         """fp16 K_hat, V_hat [1, nkv, T, 128] of layer ``l`` de-quantized from the pool."""
         outs = []
         n_pages = (T + PAGE - 1) // PAGE
+        pages = (self.page_indices if page_indices is None else page_indices)[:n_pages].contiguous()
         for which, Pi in ((0, self.Pi_k[l]), (1, self.Pi_v[l])):
             idx = torch.empty(self.nkv, T, 64, dtype=torch.uint8, device=self.dev)
             norms = torch.empty(self.nkv, T, dtype=torch.float32, device=self.dev)
             rc = self.lib.leankv_tq_pool_unpack(self.pools[l].data_ptr(), self.max_pages, self.nkv,
-                                                self.page_indices[:n_pages].contiguous().data_ptr(), T, which,
+                                                pages.data_ptr(), T, which,
                                                 idx.data_ptr(), norms.data_ptr(), self._st())
             _native.check(rc, "pool_unpack")
             out = torch.empty(1, self.nkv, T, 128, dtype=torch.float16, device=self.dev)

@@ -81,3 +81,39 @@ def test_shard_shapes():
         assert all(t.is_contiguous() for t in lw.values())
     with pytest.raises(RuntimeError):
         DecodeEngine(DecoderConfig(num_q_heads=8, num_kv_heads=8), {}, "cpu")
+
+
+def _batch_worker(rank, world, port, out):
+    """Batch-sharded decode has no data-path collective: each rank only needs to know its slice.
+    The ranks gather their slices (control plane only) so the test can see the whole partition."""
+    from leankv_b200.batch_engine import partition_batch
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mine = partition_batch(81, world, rank)
+        counts = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([mine.start, mine.stop]))
+        # per-rank token throughput adds up: sum of "tokens per step" over ranks == the batch
+        tok = torch.tensor([len(mine)], dtype=torch.int64)
+        dist.all_reduce(tok)
+        if rank == 0:
+            torch.save({"ranges": [c.tolist() for c in counts], "total": int(tok)}, out)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_batch_partition_covers_every_sequence_once(tmp_path):
+    from leankv_b200.batch_engine import partition_batch
+
+    out = str(tmp_path / "part.pt")
+    mp.spawn(_batch_worker, args=(2, 29741, out), nprocs=2, join=True)
+    r = torch.load(out)
+    assert r["ranges"] == [[0, 41], [41, 81]] and r["total"] == 81
+    for total, world in ((80, 1), (80, 2), (80, 4), (80, 8), (7, 8), (0, 2)):
+        seen = [i for rk in range(world) for i in partition_batch(total, world, rk)]
+        assert seen == list(range(total))
+        sizes = [len(partition_batch(total, world, rk)) for rk in range(world)]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        partition_batch(8, 2, 2)
