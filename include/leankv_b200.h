@@ -253,6 +253,52 @@ int leankv_decode_end(const void* logits, int vocab, long long* token, long long
                       int history_cap, int32_t* state, void* stream);
 
 /* ------------------------------------------------------------------------- *
+ * Tensor-parallel row-split projections: GEMV + all-reduce in one kernel.
+ * The reference has no multi-GPU path; this is the exchange step of the tensor-parallel
+ * decode (one process per GPU). Rank r computes its partial y_r = Wt_r^T . mask(x_r) over
+ * its slice of the input channels; the CTA that finishes a 256-column tile stores it into
+ * every rank's receive area through peer-mapped pointers (NVLink), flags it, waits until
+ * all ranks' copies of the tile have landed locally and adds them in rank order (fp32,
+ * rounded once, then + residual): every rank gets bit-identical y without a separate
+ * collective launch.
+ *
+ * Receive area of a rank: fp32 [n_slots][world][max_cols]; flags: int32 [n_slots][world]
+ * [max_cols / 256]. Both start zeroed and are never reset: a flag holds the epoch of the
+ * step that wrote it. Every all-reduce inside one decode step uses its own slot (>= 2 slots
+ * per step), *epoch (device word, same on all ranks) changes between steps
+ * (leankv_xchg_advance). Waits give up after max_wait_iters polls: the kernel then sets
+ * *status (device word, sticky: later launches skip their waits) and returns normally.
+ * ------------------------------------------------------------------------- */
+#define LEANKV_MAX_RANKS 8
+typedef struct {
+    int   world, rank;
+    int   n_slots, max_cols;                 /* max_cols % 256 == 0 */
+    int   max_wait_iters;
+    void* recv[LEANKV_MAX_RANKS];            /* rank r's receive area as mapped in this process */
+    void* flags[LEANKV_MAX_RANKS];           /* rank r's flags as mapped in this process */
+    const int32_t* epoch;
+    int32_t* status;
+} leankv_xchg_t;
+
+size_t leankv_xchg_recv_bytes(int world, int n_slots, int max_cols);
+size_t leankv_xchg_flag_bytes(int world, int n_slots, int max_cols);
+/* *epoch += 1 (one thread). */
+int leankv_xchg_advance(int32_t* epoch, void* stream);
+/* y = residual + fp16( sum over ranks of Wt_r^T . mask_t(x_r) ), see above. */
+int leankv_sparse_gemv_allreduce_f16(const void* Wt, const void* x, void* y, int N, int Z,
+                                     float threshold, const void* residual,
+                                     void* workspace, size_t workspace_bytes,
+                                     unsigned long long* active_elems,
+                                     const leankv_xchg_t* xchg, int slot, void* stream);
+/* Device memory that other processes on this node can map (cudaMalloc + CUDA IPC):
+ * alloc returns the pointer and a 64-byte handle to hand to the peers; open maps a peer's
+ * handle into this process (enables peer access); close / free undo them. */
+int leankv_ipc_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+int leankv_ipc_open(const unsigned char handle[64], void** ptr);
+int leankv_ipc_close(void* ptr);
+int leankv_ipc_free(void* ptr);
+
+/* ------------------------------------------------------------------------- *
  * Glue kernels of a batched decode step (B sequences, one new token each, dense library
  * GEMMs between them: the reference runs its dense path at batch > 1,
  * leankv/teal/patching.py:155-157, with HF modules around the cache). Like the batch-1

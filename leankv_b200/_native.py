@@ -30,6 +30,23 @@ class Segments(Structure):
     ]
 
 
+MAX_RANKS = 8
+
+
+class Xchg(Structure):
+    """Mirror of ``leankv_xchg_t``."""
+
+    _fields_ = [
+        ("world", c_int), ("rank", c_int),
+        ("n_slots", c_int), ("max_cols", c_int),
+        ("max_wait_iters", c_int),
+        ("recv", c_void_p * MAX_RANKS),
+        ("flags", c_void_p * MAX_RANKS),
+        ("epoch", c_void_p),
+        ("status", c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares appears here.
 SIGNATURES = {
     "leankv_strerror": (c_char_p, [c_int]),
@@ -77,6 +94,15 @@ SIGNATURES = {
     "leankv_rope_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                 c_void_p]),
     "leankv_decode_end": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "leankv_xchg_recv_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "leankv_xchg_flag_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "leankv_xchg_advance": (c_int, [c_void_p, c_void_p]),
+    "leankv_sparse_gemv_allreduce_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
+                                                 c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p]),
+    "leankv_ipc_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_char_p]),
+    "leankv_ipc_open": (c_int, [c_char_p, POINTER(c_void_p)]),
+    "leankv_ipc_close": (c_int, [c_void_p]),
+    "leankv_ipc_free": (c_int, [c_void_p]),
     "leankv_rmsnorm_rows_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "leankv_batch_decode_begin": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                           c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -60,3 +60,44 @@ extern "C" const char* leankv_strerror(int code) {
 extern "C" int leankv_abi_version(void) { return 1; }
 
 extern "C" const char* leankv_last_cuda_error(void) { return leankv::g_last_cuda_error; }
+
+// ---- device memory shared between the ranks of one node (CUDA IPC) ----
+
+extern "C" int leankv_ipc_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!ptr || !handle || bytes == 0) return LEANKV_EINVAL;
+    void* d = nullptr;
+    LEANKV_CUDA_TRY(cudaMalloc(&d, bytes));
+    cudaError_t e = cudaMemset(d, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d);
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        LEANKV_CUDA_TRY(e);
+    }
+    std::memcpy(handle, &h, 64);
+    *ptr = d;
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_ipc_open(const unsigned char handle[64], void** ptr) {
+    if (!ptr || !handle) return LEANKV_EINVAL;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    void* d = nullptr;
+    LEANKV_CUDA_TRY(cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = d;
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_ipc_close(void* ptr) {
+    if (!ptr) return LEANKV_EINVAL;
+    LEANKV_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_ipc_free(void* ptr) {
+    if (!ptr) return LEANKV_EINVAL;
+    LEANKV_CUDA_TRY(cudaFree(ptr));
+    return LEANKV_OK;
+}

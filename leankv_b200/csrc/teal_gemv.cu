@@ -45,7 +45,24 @@ struct GemvParams {
     float thr_up;        // SwiGLU: thr[0] masks gate, thr_up masks up
     const __half* norm_w;   // if set, x is an un-normalised row h and the kernel uses
     float norm_eps;         // x[z] = norm_w[z] * fp16(h[z] * rsqrt(mean(h^2) + eps))  (RMSNorm fused in)
+    // All-reduce of the row-parallel partial products over peer memory (xw = 0: off).
+    // xrecv[r] / xflag[r]: rank r's receive area / arrival flags for this launch's slot, as mapped
+    // into this process: fp32 [world][npad] and int [world][n_slices], indexed by source rank.
+    int xw, xrank, xlimit;
+    float* xrecv[LEANKV_MAX_RANKS];
+    int* xflag[LEANKV_MAX_RANKS];
+    const int* xepoch;
+    int* xstatus;
 };
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 struct GemvPlan {
     int n_slices, k_splits, rows_per_split;
@@ -323,6 +340,35 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
         if (tid == 0) p.counters[slice] = 0;   // leave the workspace ready for the next launch
     }
 
+    if (!kSwiglu && p.xw > 0) {
+        // Sum of the ranks' partial products, inside this kernel: the CTA that holds the finished
+        // 256-column tile stores it (fp32) into every rank's receive area, raises that tile's flag
+        // there, waits (bounded) until every rank's copy of the tile has arrived here, and adds the
+        // copies in rank order. Every rank ends up with the same bits. Flags carry the step's epoch,
+        // so nothing is ever reset; a wait that runs out sets the status word, which also turns all
+        // later waits off (the result is then meaningless, but no kernel hangs).
+        const int ep = *reinterpret_cast<const volatile int*>(p.xepoch);
+        for (int r = 0; r < p.xw; ++r) p.xrecv[r][(size_t)p.xrank * npad + col] = sum;
+        __threadfence_system();
+        __syncthreads();
+        if (tid < p.xw) {
+            st_release_sys(p.xflag[tid] + p.xrank * p.n_slices + slice, ep);
+            const int* f = p.xflag[p.xrank] + tid * p.n_slices + slice;
+            bool ok = false;
+            if (*reinterpret_cast<volatile int*>(p.xstatus) == 0) {
+                for (int it = 0; it < p.xlimit; ++it) {
+                    if (ld_acquire_sys(f) == ep) { ok = true; break; }
+                    __nanosleep(40);
+                }
+            }
+            if (!ok) atomicOr(p.xstatus, 1);
+        }
+        __syncthreads();
+        float tot = 0.f;
+        for (int r = 0; r < p.xw; ++r) tot += ld_cg_f32(p.xrecv[p.xrank] + (size_t)r * npad + col);
+        sum = tot;
+    }
+
     if (col >= p.N) return;
     if (kSwiglu) {
         // Rounding points of the two-GEMV + act_fn(gate)*up path: fp16 gate, fp16 up,
@@ -357,7 +403,8 @@ int check_norm(const void* x, const void* norm_w, int Z) {
 
 int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const leankv_segments_t* segs,
                 const void* bias, const void* residual, void* workspace, size_t workspace_bytes,
-                unsigned long long* active, void* stream, const void* norm_w = nullptr, float norm_eps = 0.f) {
+                unsigned long long* active, void* stream, const void* norm_w = nullptr, float norm_eps = 0.f,
+                const leankv_xchg_t* xchg = nullptr, int slot = 0) {
     int rc = check_common(Wt, x, y, N, Z);
     if (rc != LEANKV_OK) return rc;
     rc = check_norm(x, norm_w, Z);
@@ -402,6 +449,24 @@ int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const lean
     p.thr_up = 0.f;
     p.norm_w = static_cast<const __half*>(norm_w);
     p.norm_eps = norm_eps;
+    if (xchg != nullptr) {
+        const int npad = pl.n_slices * kColsPerCta;
+        if (xchg->world < 1 || xchg->world > LEANKV_MAX_RANKS || xchg->rank < 0 || xchg->rank >= xchg->world ||
+            slot < 0 || slot >= xchg->n_slots || npad > xchg->max_cols || !xchg->epoch || !xchg->status ||
+            xchg->max_wait_iters < 1)
+            return LEANKV_EINVAL;
+        p.xw = xchg->world;
+        p.xrank = xchg->rank;
+        p.xlimit = xchg->max_wait_iters;
+        p.xepoch = xchg->epoch;
+        p.xstatus = xchg->status;
+        const int max_tiles = xchg->max_cols / kColsPerCta;
+        for (int r = 0; r < xchg->world; ++r) {
+            if (!xchg->recv[r] || !xchg->flags[r]) return LEANKV_EINVAL;
+            p.xrecv[r] = static_cast<float*>(xchg->recv[r]) + (size_t)slot * xchg->world * xchg->max_cols;
+            p.xflag[r] = static_cast<int*>(xchg->flags[r]) + (size_t)slot * xchg->world * max_tiles;
+        }
+    }
     dim3 grid(pl.n_slices, pl.k_splits);
     LEANKV_CUDA_TRY(launch_kernel_ex(true, sparse_gemv_kernel<false>, grid, dim3(kThreads), 0,
                                   static_cast<cudaStream_t>(stream), p));
@@ -444,6 +509,40 @@ extern "C" int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y
                                           void* stream) {
     return launch_gemv(Wt, x, y, N, Z, segs, bias, residual, workspace, workspace_bytes,
                        active_elems, stream);
+}
+
+extern "C" size_t leankv_xchg_recv_bytes(int world, int n_slots, int max_cols) {
+    if (world < 1 || n_slots < 1 || max_cols < 1) return 0;
+    return sizeof(float) * (size_t)n_slots * world * max_cols;
+}
+
+extern "C" size_t leankv_xchg_flag_bytes(int world, int n_slots, int max_cols) {
+    if (world < 1 || n_slots < 1 || max_cols < 1) return 0;
+    return sizeof(int) * (size_t)n_slots * world * (max_cols / kColsPerCta);
+}
+
+static __global__ void xchg_advance_kernel(int* epoch) {
+    pdl_begin();
+    *epoch = *epoch + 1;
+}
+
+extern "C" int leankv_xchg_advance(int32_t* epoch, void* stream) {
+    if (!epoch) return LEANKV_EINVAL;
+    LEANKV_CUDA_TRY(launch_kernel(xchg_advance_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(stream), epoch));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_sparse_gemv_allreduce_f16(const void* Wt, const void* x, void* y, int N, int Z,
+                                                float threshold, const void* residual, void* workspace,
+                                                size_t workspace_bytes, unsigned long long* active_elems,
+                                                const leankv_xchg_t* xchg, int slot, void* stream) {
+    if (!xchg || xchg->max_cols % kColsPerCta != 0) return LEANKV_EINVAL;
+    leankv_segments_t segs{};
+    segs.n_segments = 1;
+    segs.seg_end[0] = N;
+    segs.threshold[0] = threshold;
+    return launch_gemv(Wt, x, y, N, Z, &segs, nullptr, residual, workspace, workspace_bytes, active_elems,
+                       stream, nullptr, 0.f, xchg, slot);
 }
 
 static int launch_swiglu(const void* Wt_gate, const void* Wt_up, const void* x, void* y, int N, int Z,

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -142,6 +143,13 @@ class DecodeEngine:
             self.ws_gemv = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
             need = self.lib.leankv_tq_decode_attn_workspace_bytes(1, self.nq, self.nkv, self.max_pages)
             self.ws_attn = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+        # Tensor parallel: the o / down projections sum their partial products over peer memory inside
+        # the GEMV kernel (LEANKV_TP_EXCHANGE=nccl keeps a separate NCCL all-reduce launch instead).
+        self.xchg = None
+        if tp_size > 1 and os.environ.get("LEANKV_TP_EXCHANGE", "peer") != "nccl":
+            from .peer_exchange import PeerExchange
+
+            self.xchg = PeerExchange(dev, tp_rank, tp_size, group, n_slots=2 * L, max_cols=cfg.hidden_size)
         self.set_thresholds(thresholds)
         self.graph = None
         self.launches_per_step = 0
@@ -287,6 +295,16 @@ class DecodeEngine:
         _native.check(rc, "sparse gemv")
         self.launches_per_step += 1
 
+    def _gemv_allreduce(self, wt, x, y, t, residual, slot):
+        """y = residual + sum over ranks of Wt_r^T . mask_t(x_r): GEMV and exchange in one kernel."""
+        z, n = wt.shape
+        rc = self.lib.leankv_sparse_gemv_allreduce_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), n, z, t,
+                                                       _native.ptr(residual), self.ws_gemv.data_ptr(),
+                                                       self.ws_gemv.numel(), self.active_elems.data_ptr(),
+                                                       ctypes.byref(self.xchg.c), slot, self._st())
+        _native.check(rc, "sparse gemv + all-reduce")
+        self.launches_per_step += 1
+
     def _norm(self, delta, w):
         rc = self.lib.leankv_rmsnorm_f16(self.h.data_ptr(), _native.ptr(delta), w.data_ptr(), self.x.data_ptr(),
                                          self.cfg.hidden_size, self.cfg.rms_eps, self._st())
@@ -346,10 +364,23 @@ class DecodeEngine:
             self.launches_per_step += 4     # rope, append, query rotation, attention
         probe("attn")
         if fused_norm:
-            # Single rank: h += o_proj(attn) in place. Tensor parallel: every rank writes its partial
-            # product to a second buffer, rank 0 alone adds the residual stream to its partial, and the
-            # all-reduce leaves the updated stream on every rank (the down projection comes back the
-            # same way), so a block is 5 kernels + 2 all-reduces.
+            # Single rank: h += o_proj(attn) in place.
+            # Tensor parallel, peer exchange: the same two launches, each summing the ranks' partial
+            # products over peer memory before it adds the residual stream (6 kernels per block).
+            # Tensor parallel, NCCL: every rank writes its partial product to a second buffer, rank 0
+            # alone adds the residual stream to its partial, and an all-reduce launch leaves the updated
+            # stream on every rank (6 kernels + 2 all-reduces per block).
+            if self.xchg is not None:
+                self._gemv_allreduce(lw["wo_t"], self.attn, self.h, t["o_proj"], self.h, 2 * l)
+                rc = lib.leankv_sparse_swiglu_rmsnorm_f16(
+                    lw["wgate_t"].data_ptr(), lw["wup_t"].data_ptr(), self.h.data_ptr(), lw["ln2"].data_ptr(),
+                    cfg.rms_eps, self.mlp_h.data_ptr(), self.inter, cfg.hidden_size, t["gate_proj"], t["up_proj"],
+                    self.ws_gemv.data_ptr(), self.ws_gemv.numel(), self.active_elems.data_ptr(), st())
+                _native.check(rc, "sparse swiglu")
+                self.launches_per_step += 1
+                probe("mlp_h")
+                self._gemv_allreduce(lw["wdown_t"], self.mlp_h, self.h, t["down_proj"], self.h, 2 * l + 1)
+                return
             tp = self.tp_size > 1
             h_mid = self.h2 if tp else self.h
             res = self.h if (not tp or self.tp_rank == 0) else None
@@ -393,6 +424,9 @@ class DecodeEngine:
                                               cfg.hidden_size, cfg.vocab_size, sp, st()), "decode_begin")
         self.launches_per_step += 1
         fused_norm = self.fused_norm
+        if self.xchg is not None and fused_norm:
+            self.xchg.advance(st())
+            self.launches_per_step += 1
         if not fused_norm:
             self._norm(None, self.w["layers"][0]["ln1"])
         for l in range(cfg.num_layers):

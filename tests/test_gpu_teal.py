@@ -200,3 +200,84 @@ def test_apply_teal_kernel_mode_matches_hook_mode():
             assert model.model.layers[0].mlp.down_proj._teal_patched
     assert rel_l2(logits["kernel"], logits["hook"]) < 5e-3
     assert rel_l2(logits["fused"], logits["kernel"]) < 5e-3
+
+
+def _allreduce_gemv(wt, x, t, residual, xchg_c, slot):
+    lib = _native.lib()
+    z, n = wt.shape
+    y = torch.empty(n, dtype=torch.float16, device=wt.device)
+    ws = torch.zeros(max(lib.leankv_sparse_gemv_workspace_bytes(n, z), 256), dtype=torch.uint8, device=wt.device)
+    rc = lib.leankv_sparse_gemv_allreduce_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), n, z, float(t),
+                                              _native.ptr(residual), ws.data_ptr(), ws.numel(), None,
+                                              ctypes.byref(xchg_c), slot, torch.cuda.current_stream().cuda_stream)
+    _native.check(rc, "gemv + all-reduce")
+    torch.cuda.synchronize()
+    return y
+
+
+def test_allreduce_gemv_with_one_rank_equals_plain_gemv():
+    """A single rank exchanges with itself: same publish / flag / wait / ordered-sum code path, and the
+    sum of one partial is that partial, so the output must equal the plain kernel's bit for bit."""
+    from leankv_b200.peer_exchange import PeerExchange
+
+    dev = _dev()
+    gen = torch.Generator(device="cpu").manual_seed(11)
+    ex = PeerExchange(dev, n_slots=3, max_cols=4096)
+    try:
+        for step, (z, n, t) in enumerate([(14336, 4096, 0.6), (300, 1000, 0.2), (4096, 4096, -1.0)]):
+            w = (torch.randn(n, z, generator=gen) * 0.02).half().to(dev)
+            x = torch.randn(z, generator=gen).half().to(dev)
+            res = torch.randn(n, generator=gen).half().to(dev)
+            wt = w.t().contiguous()
+            want, _ = _raw_gemv(wt, x, t, residual=res)
+            for slot in range(3):
+                got = _allreduce_gemv(wt, x, t, res, ex.c, slot)
+                assert torch.equal(got, want), (step, slot)
+            ex.advance(torch.cuda.current_stream().cuda_stream)     # next step: flags of this one are stale
+        assert not ex.timed_out()
+        lib = _native.lib()
+        bad = _native.Xchg.from_buffer_copy(ex.c)
+        bad.rank = 1
+        y = torch.empty(256, dtype=torch.float16, device=dev)
+        ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
+        assert lib.leankv_sparse_gemv_allreduce_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), 256, 64, 0.0, None,
+                                                    ws.data_ptr(), ws.numel(), None, ctypes.byref(bad), 0,
+                                                    None) == -1          # rank outside the world
+        assert lib.leankv_sparse_gemv_allreduce_f16(wt.data_ptr(), x.data_ptr(), y.data_ptr(), 256, 64, 0.0, None,
+                                                    ws.data_ptr(), ws.numel(), None, ctypes.byref(ex.c), 3,
+                                                    None) == -1          # slot outside the area
+    finally:
+        ex.close()
+
+
+def test_allreduce_wait_gives_up_when_a_peer_never_arrives():
+    """Two-rank exchange where nobody plays rank 1 (its area is a second local buffer): the bounded
+    wait runs out, the kernel returns, the status word is set and later launches skip their waits."""
+    lib = _native.lib()
+    dev = _dev()
+    world, slots, cols = 2, 2, 1024
+    recv = [torch.zeros(lib.leankv_xchg_recv_bytes(world, slots, cols), dtype=torch.uint8, device=dev)
+            for _ in range(world)]
+    flags = [torch.zeros(lib.leankv_xchg_flag_bytes(world, slots, cols), dtype=torch.uint8, device=dev)
+             for _ in range(world)]
+    epoch = torch.ones(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    xc = _native.Xchg()
+    xc.world, xc.rank, xc.n_slots, xc.max_cols, xc.max_wait_iters = world, 0, slots, cols, 2000
+    for r in range(world):
+        xc.recv[r], xc.flags[r] = recv[r].data_ptr(), flags[r].data_ptr()
+    xc.epoch, xc.status = epoch.data_ptr(), status.data_ptr()
+    gen = torch.Generator(device="cpu").manual_seed(12)
+    wt = (torch.randn(512, 1024, generator=gen) * 0.02).half().to(dev)
+    x = torch.randn(512, generator=gen).half().to(dev)
+    y = _allreduce_gemv(wt, x, 0.1, None, xc, 0)
+    assert int(status.item()) == 1
+    assert bool(torch.isfinite(y.float()).all())
+    # rank 0's tile reached the absent peer's area and flag even though nothing came back
+    plain, _ = _raw_gemv(wt, x, 0.1)
+    sent = recv[1].view(torch.float32)[:1024]
+    assert rel_l2(sent, plain) < 1e-3
+    assert int(flags[1].view(torch.int32)[0]) == 1
+    y2 = _allreduce_gemv(wt, x, 0.1, None, xc, 1)          # sticky status: returns without polling
+    assert int(status.item()) == 1 and bool(torch.isfinite(y2.float()).all())
+    torch.cuda.synchronize()
