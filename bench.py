@@ -300,6 +300,65 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
                                        "note": "two launches per call: query rotation + attention"}
 
 
+def exchange_leg(dev, world, rank, group, iters=200):
+    """Tensor-parallel o_proj (this rank's [4096 / world][4096] slice) three ways: the GEMV alone, the
+    GEMV with the all-reduce inside the kernel, and the GEMV followed by an NCCL all-reduce launch."""
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+
+    from leankv_b200 import _native
+    from leankv_b200.peer_exchange import PeerExchange
+
+    lib = _native.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    z, n = 4096 // world, 4096
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    copies = 24                                             # 24 x (32 / world) MB: rotates through more than L2
+    wts = [(torch.randn(z, n, device=dev, generator=gen) * 0.02).half() for _ in range(copies)]
+    x = torch.randn(z, device=dev, generator=gen).half()
+    res = torch.randn(n, device=dev, generator=gen).half()
+    y = torch.empty(n, dtype=torch.float16, device=dev)
+    ws = torch.zeros(lib.leankv_sparse_gemv_workspace_bytes(n, z) + 256, dtype=torch.uint8, device=dev)
+    ex = PeerExchange(dev, rank, world, group, n_slots=8, max_cols=n)
+
+    def plain(i):
+        lib.leankv_sparse_gemv_f16(wts[i % copies].data_ptr(), x.data_ptr(), y.data_ptr(), n, z, 0.5, None,
+                                   res.data_ptr(), ws.data_ptr(), ws.numel(), None, st)
+
+    def fused(i):
+        if i % 8 == 0:
+            ex.advance(st)
+        lib.leankv_sparse_gemv_allreduce_f16(wts[i % copies].data_ptr(), x.data_ptr(), y.data_ptr(), n, z, 0.5,
+                                             res.data_ptr(), ws.data_ptr(), ws.numel(), None,
+                                             ctypes.byref(ex.c), i % 8, st)
+
+    def nccl(i):
+        plain(i)
+        dist.all_reduce(y, group=group)
+
+    out = {}
+    for name, fn in (("gemv_alone_us", plain), ("gemv_allreduce_fused_us", fused), ("gemv_then_nccl_us", nccl)):
+        dist.barrier(group=group)
+        torch.cuda.synchronize()
+        for i in range(16):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(16, 16 + iters):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        out[name] = float(t.item())
+    out["timed_out"] = ex.timed_out()
+    out["shape"] = f"o_proj slice [{z}][{n}] fp16, threshold 0.5 on N(0,1) input, residual add"
+    ex.close()
+    return out
+
+
 # ── batched long-context decode (sequences sharded over the ranks, no collective) ────────
 
 BATCH_TOTAL, BATCH_CTX = 80, 4096
@@ -429,7 +488,10 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a collective that never completes aborts the run after 3 minutes instead of hanging it
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         group = dist.group.WORLD
     K, W = args.steps, args.warmup
     cfg = DecoderConfig.mistral_7b() if not args.small else DecoderConfig(
@@ -512,6 +574,7 @@ def run_ours(args):
     launches_per_step = eng.launches_per_step
     del eng
     torch.cuda.empty_cache()
+    exchange = exchange_leg(dev, world, rank, group) if world > 1 else None
     batched = None
     if not args.no_batched:
         batched = batched_decode_leg(dev, world, rank, args.batched_steps, W, small=args.small)
@@ -534,6 +597,8 @@ def run_ours(args):
                  "dense_weight_bytes_per_step_per_gpu": dense_streamed / K,
                  "speedup_vs_dense_same_engine": sec_dense / sec},
     }
+    if exchange is not None:
+        line["tp_exchange"] = exchange
     if batched is not None:
         batched["attn_kernel"]["frac"] = batched["attn_kernel"]["gbs"] / peak_gbs
         batched["step_frac_of_peak"] = batched["step_gbs_per_gpu"] / peak_gbs
@@ -576,7 +641,10 @@ def run_batched(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)   # barrier + max-over-ranks timing only
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev,   # barrier + max-over-ranks timing only
+                                timeout=datetime.timedelta(seconds=180))
     K = args.steps if args.steps_given else 128
     sampler = ClockSampler(local)
     sampler.start()
@@ -612,6 +680,8 @@ def main():
     ap.add_argument("--only-legs", default="",
                     help="comma list of gemv,swiglu,attn: run just those kernel legs and print their JSON")
     ap.add_argument("--leg-iters", type=int, default=200)
+    ap.add_argument("--only-exchange", action="store_true",
+                    help="under torchrun: time the GEMV + all-reduce leg alone and print its JSON")
     ap.add_argument("--workload", choices=["decode", "batched"], default="decode",
                     help="decode: batch-1 TEAL + TurboQuant decode loop (the headline metric), with a short "
                          "batched leg attached; batched: only the 80-sequence long-context decode, its own line")
@@ -623,6 +693,20 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.only_exchange:
+        import datetime
+
+        import torch
+        import torch.distributed as dist
+
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        out = exchange_leg(dev, dist.get_world_size(), dist.get_rank(), dist.group.WORLD, args.leg_iters)
+        if dist.get_rank() == 0:
+            print(json.dumps(out))
+        dist.destroy_process_group()
     elif args.workload == "batched":
         run_batched(args)
     elif args.only_legs:

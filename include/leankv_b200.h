@@ -256,18 +256,18 @@ int leankv_decode_end(const void* logits, int vocab, long long* token, long long
  * Tensor-parallel row-split projections: GEMV + all-reduce in one kernel.
  * The reference has no multi-GPU path; this is the exchange step of the tensor-parallel
  * decode (one process per GPU). Rank r computes its partial y_r = Wt_r^T . mask(x_r) over
- * its slice of the input channels; the CTA that finishes a 256-column tile stores it into
- * every rank's receive area through peer-mapped pointers (NVLink), flags it, waits until
- * all ranks' copies of the tile have landed locally and adds them in rank order (fp32,
- * rounded once, then + residual): every rank gets bit-identical y without a separate
- * collective launch.
+ * its slice of the input channels. Every thread of the CTA that finishes a 256-column tile
+ * sends its column's fp32 value, tagged with the step's epoch in the same 64-bit store, into
+ * every rank's receive area through peer-mapped pointers (NVLink); it then polls its
+ * column's words in the local area until all ranks' values of this epoch are there and adds
+ * them in rank order (fp32, rounded once, then + residual). Every rank gets bit-identical y
+ * without a separate collective launch, fence or flag.
  *
- * Receive area of a rank: fp32 [n_slots][world][max_cols]; flags: int32 [n_slots][world]
- * [max_cols / 256]. Both start zeroed and are never reset: a flag holds the epoch of the
- * step that wrote it. Every all-reduce inside one decode step uses its own slot (>= 2 slots
- * per step), *epoch (device word, same on all ranks) changes between steps
- * (leankv_xchg_advance). Waits give up after max_wait_iters polls: the kernel then sets
- * *status (device word, sticky: later launches skip their waits) and returns normally.
+ * Receive area of a rank: 64-bit words [n_slots][world][max_cols], zeroed once and never
+ * reset. Every all-reduce inside one decode step uses its own slot (>= 2 slots per step);
+ * *epoch (device word, > 0, same on all ranks) changes between steps (leankv_xchg_advance).
+ * A poll gives up after max_wait_iters tries: the kernel then sets *status (device word,
+ * sticky: later launches do not poll) and returns normally.
  * ------------------------------------------------------------------------- */
 #define LEANKV_MAX_RANKS 8
 typedef struct {
@@ -275,13 +275,11 @@ typedef struct {
     int   n_slots, max_cols;                 /* max_cols % 256 == 0 */
     int   max_wait_iters;
     void* recv[LEANKV_MAX_RANKS];            /* rank r's receive area as mapped in this process */
-    void* flags[LEANKV_MAX_RANKS];           /* rank r's flags as mapped in this process */
     const int32_t* epoch;
     int32_t* status;
 } leankv_xchg_t;
 
 size_t leankv_xchg_recv_bytes(int world, int n_slots, int max_cols);
-size_t leankv_xchg_flag_bytes(int world, int n_slots, int max_cols);
 /* *epoch += 1 (one thread). */
 int leankv_xchg_advance(int32_t* epoch, void* stream);
 /* y = residual + fp16( sum over ranks of Wt_r^T . mask_t(x_r) ), see above. */

@@ -41,7 +41,6 @@ class Xchg(Structure):
         ("n_slots", c_int), ("max_cols", c_int),
         ("max_wait_iters", c_int),
         ("recv", c_void_p * MAX_RANKS),
-        ("flags", c_void_p * MAX_RANKS),
         ("epoch", c_void_p),
         ("status", c_void_p),
     ]
@@ -95,7 +94,6 @@ SIGNATURES = {
                                 c_void_p]),
     "leankv_decode_end": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "leankv_xchg_recv_bytes": (c_size_t, [c_int, c_int, c_int]),
-    "leankv_xchg_flag_bytes": (c_size_t, [c_int, c_int, c_int]),
     "leankv_xchg_advance": (c_int, [c_void_p, c_void_p]),
     "leankv_sparse_gemv_allreduce_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
                                                  c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p]),

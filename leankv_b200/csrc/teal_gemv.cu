@@ -46,21 +46,22 @@ struct GemvParams {
     const __half* norm_w;   // if set, x is an un-normalised row h and the kernel uses
     float norm_eps;         // x[z] = norm_w[z] * fp16(h[z] * rsqrt(mean(h^2) + eps))  (RMSNorm fused in)
     // All-reduce of the row-parallel partial products over peer memory (xw = 0: off).
-    // xrecv[r] / xflag[r]: rank r's receive area / arrival flags for this launch's slot, as mapped
-    // into this process: fp32 [world][npad] and int [world][n_slices], indexed by source rank.
+    // xrecv[r]: rank r's receive area for this launch's slot, as mapped into this process:
+    // 64-bit words [world][npad] indexed by source rank, each {fp32 value, epoch}.
     int xw, xrank, xlimit;
-    float* xrecv[LEANKV_MAX_RANKS];
-    int* xflag[LEANKV_MAX_RANKS];
+    unsigned long long* xrecv[LEANKV_MAX_RANKS];
     const int* xepoch;
     int* xstatus;
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// One 64-bit access carries a value together with the epoch that marks it as arrived, so the
+// exchange needs no fence and no separate flag (a scalar 64-bit access is never torn).
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 
@@ -341,31 +342,34 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
     }
 
     if (!kSwiglu && p.xw > 0) {
-        // Sum of the ranks' partial products, inside this kernel: the CTA that holds the finished
-        // 256-column tile stores it (fp32) into every rank's receive area, raises that tile's flag
-        // there, waits (bounded) until every rank's copy of the tile has arrived here, and adds the
-        // copies in rank order. Every rank ends up with the same bits. Flags carry the step's epoch,
-        // so nothing is ever reset; a wait that runs out sets the status word, which also turns all
-        // later waits off (the result is then meaningless, but no kernel hangs).
-        const int ep = *reinterpret_cast<const volatile int*>(p.xepoch);
-        for (int r = 0; r < p.xw; ++r) p.xrecv[r][(size_t)p.xrank * npad + col] = sum;
-        __threadfence_system();
-        __syncthreads();
-        if (tid < p.xw) {
-            st_release_sys(p.xflag[tid] + p.xrank * p.n_slices + slice, ep);
-            const int* f = p.xflag[p.xrank] + tid * p.n_slices + slice;
-            bool ok = false;
-            if (*reinterpret_cast<volatile int*>(p.xstatus) == 0) {
-                for (int it = 0; it < p.xlimit; ++it) {
-                    if (ld_acquire_sys(f) == ep) { ok = true; break; }
-                    __nanosleep(40);
-                }
-            }
-            if (!ok) atomicOr(p.xstatus, 1);
-        }
-        __syncthreads();
+        // Sum of the ranks' partial products, inside this kernel: every thread of the CTA that holds
+        // a finished 256-column tile sends its column's fp32 value, tagged with the step's epoch, to
+        // every rank's receive area (one 64-bit store each, NVLink for the peers), then polls its
+        // column's words here until each carries this epoch, and adds them in rank order, so every
+        // rank ends up with the same bits. Epochs only grow, so nothing is ever reset. A poll that
+        // runs out sets the status word, which also turns all later polls off (the result is then
+        // meaningless, but no kernel hangs).
+        const unsigned int ep = (unsigned int)*reinterpret_cast<const volatile int*>(p.xepoch);
+        const unsigned long long word = ((unsigned long long)ep << 32) | (unsigned long long)__float_as_uint(sum);
+        for (int r = 0; r < p.xw; ++r) st_relaxed_sys_u64(p.xrecv[r] + (size_t)p.xrank * npad + col, word);
+        const bool live = *reinterpret_cast<volatile int*>(p.xstatus) == 0;
         float tot = 0.f;
-        for (int r = 0; r < p.xw; ++r) tot += ld_cg_f32(p.xrecv[p.xrank] + (size_t)r * npad + col);
+        bool ok = live;
+        for (int r = 0; r < p.xw; ++r) {
+            const unsigned long long* src = p.xrecv[p.xrank] + (size_t)r * npad + col;
+            unsigned long long v = ld_relaxed_sys_u64(src);
+            if (live) {
+                int it = 0;
+                while ((unsigned int)(v >> 32) != ep && it < p.xlimit) {
+                    __nanosleep(20);
+                    v = ld_relaxed_sys_u64(src);
+                    ++it;
+                }
+                ok = ok && (unsigned int)(v >> 32) == ep;
+            }
+            tot += __uint_as_float((unsigned int)v);
+        }
+        if (!ok && live) atomicOr(p.xstatus, 1);
         sum = tot;
     }
 
@@ -460,11 +464,10 @@ int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const lean
         p.xlimit = xchg->max_wait_iters;
         p.xepoch = xchg->epoch;
         p.xstatus = xchg->status;
-        const int max_tiles = xchg->max_cols / kColsPerCta;
         for (int r = 0; r < xchg->world; ++r) {
-            if (!xchg->recv[r] || !xchg->flags[r]) return LEANKV_EINVAL;
-            p.xrecv[r] = static_cast<float*>(xchg->recv[r]) + (size_t)slot * xchg->world * xchg->max_cols;
-            p.xflag[r] = static_cast<int*>(xchg->flags[r]) + (size_t)slot * xchg->world * max_tiles;
+            if (!xchg->recv[r] || (reinterpret_cast<uintptr_t>(xchg->recv[r]) & 7u) != 0) return LEANKV_EINVAL;
+            p.xrecv[r] = static_cast<unsigned long long*>(xchg->recv[r]) +
+                         (size_t)slot * xchg->world * xchg->max_cols;
         }
     }
     dim3 grid(pl.n_slices, pl.k_splits);
@@ -513,12 +516,7 @@ extern "C" int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y
 
 extern "C" size_t leankv_xchg_recv_bytes(int world, int n_slots, int max_cols) {
     if (world < 1 || n_slots < 1 || max_cols < 1) return 0;
-    return sizeof(float) * (size_t)n_slots * world * max_cols;
-}
-
-extern "C" size_t leankv_xchg_flag_bytes(int world, int n_slots, int max_cols) {
-    if (world < 1 || n_slots < 1 || max_cols < 1) return 0;
-    return sizeof(int) * (size_t)n_slots * world * (max_cols / kColsPerCta);
+    return sizeof(unsigned long long) * (size_t)n_slots * world * max_cols;
 }
 
 static __global__ void xchg_advance_kernel(int* epoch) {

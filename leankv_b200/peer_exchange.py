@@ -1,8 +1,8 @@
 """Peer-mapped receive areas for the in-kernel all-reduce of the tensor-parallel decode.
 
-Every rank allocates one receive area + one flag array with ``leankv_ipc_alloc`` (plain
-``cudaMalloc`` memory exported over CUDA IPC), the 64-byte handles travel through the process
-group's control plane (``all_gather_object``), and each rank maps its peers' areas. The resulting
+Every rank allocates one receive area with ``leankv_ipc_alloc`` (plain ``cudaMalloc`` memory
+exported over CUDA IPC), the 64-byte handles travel through the process group's control plane
+(``all_gather_object``), and each rank maps its peers' areas. The resulting
 ``leankv_xchg_t`` is what ``leankv_sparse_gemv_allreduce_f16`` takes. With ``world == 1`` nothing
 is exported: the rank exchanges with itself (useful on a single GPU to exercise the code path).
 """
@@ -28,41 +28,32 @@ class PeerExchange:
         self.n_slots, self.max_cols = n_slots, max_cols
         self._mine, self._opened = [], []
         with torch.cuda.device(self.dev):
-            sizes = (self.lib.leankv_xchg_recv_bytes(world, n_slots, max_cols),
-                     self.lib.leankv_xchg_flag_bytes(world, n_slots, max_cols))
-            ptrs, handles = [], []
-            for nbytes in sizes:
-                p = ctypes.c_void_p()
-                h = ctypes.create_string_buffer(64)
-                _native.check(self.lib.leankv_ipc_alloc(nbytes, ctypes.byref(p), h), "ipc_alloc")
-                self._mine.append(p.value)
-                ptrs.append(p.value)
-                handles.append(h.raw)
+            nbytes = self.lib.leankv_xchg_recv_bytes(world, n_slots, max_cols)
+            p = ctypes.c_void_p()
+            h = ctypes.create_string_buffer(64)
+            _native.check(self.lib.leankv_ipc_alloc(nbytes, ctypes.byref(p), h), "ipc_alloc")
+            self._mine.append(p.value)
             recv = [None] * world
-            flags = [None] * world
-            recv[rank], flags[rank] = ptrs
+            recv[rank] = p.value
             if world > 1:
                 import torch.distributed as dist
 
                 gathered = [None] * world
-                dist.all_gather_object(gathered, handles, group=group)
+                dist.all_gather_object(gathered, h.raw, group=group)
                 for r in range(world):
                     if r == rank:
                         continue
-                    mapped = []
-                    for h in gathered[r]:
-                        p = ctypes.c_void_p()
-                        _native.check(self.lib.leankv_ipc_open(h, ctypes.byref(p)), "ipc_open")
-                        self._opened.append(p.value)
-                        mapped.append(p.value)
-                    recv[r], flags[r] = mapped
+                    q = ctypes.c_void_p()
+                    _native.check(self.lib.leankv_ipc_open(gathered[r], ctypes.byref(q)), "ipc_open")
+                    self._opened.append(q.value)
+                    recv[r] = q.value
                 dist.barrier(group=group)      # every area is zeroed and mapped before anyone writes
             self.epoch = torch.ones(1, dtype=torch.int32, device=self.dev)
             self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
             x = _native.Xchg()
             x.world, x.rank, x.n_slots, x.max_cols, x.max_wait_iters = world, rank, n_slots, max_cols, max_wait_iters
             for r in range(world):
-                x.recv[r], x.flags[r] = recv[r], flags[r]
+                x.recv[r] = recv[r]
             x.epoch, x.status = self.epoch.data_ptr(), self.status.data_ptr()
             self.c = x
 

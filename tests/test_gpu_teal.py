@@ -258,14 +258,12 @@ def test_allreduce_wait_gives_up_when_a_peer_never_arrives():
     world, slots, cols = 2, 2, 1024
     recv = [torch.zeros(lib.leankv_xchg_recv_bytes(world, slots, cols), dtype=torch.uint8, device=dev)
             for _ in range(world)]
-    flags = [torch.zeros(lib.leankv_xchg_flag_bytes(world, slots, cols), dtype=torch.uint8, device=dev)
-             for _ in range(world)]
     epoch = torch.ones(1, dtype=torch.int32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     xc = _native.Xchg()
     xc.world, xc.rank, xc.n_slots, xc.max_cols, xc.max_wait_iters = world, 0, slots, cols, 2000
     for r in range(world):
-        xc.recv[r], xc.flags[r] = recv[r].data_ptr(), flags[r].data_ptr()
+        xc.recv[r] = recv[r].data_ptr()
     xc.epoch, xc.status = epoch.data_ptr(), status.data_ptr()
     gen = torch.Generator(device="cpu").manual_seed(12)
     wt = (torch.randn(512, 1024, generator=gen) * 0.02).half().to(dev)
@@ -273,11 +271,11 @@ def test_allreduce_wait_gives_up_when_a_peer_never_arrives():
     y = _allreduce_gemv(wt, x, 0.1, None, xc, 0)
     assert int(status.item()) == 1
     assert bool(torch.isfinite(y.float()).all())
-    # rank 0's tile reached the absent peer's area and flag even though nothing came back
+    # rank 0's values reached the absent peer's area, tagged with the epoch, though nothing came back
     plain, _ = _raw_gemv(wt, x, 0.1)
-    sent = recv[1].view(torch.float32)[:1024]
-    assert rel_l2(sent, plain) < 1e-3
-    assert int(flags[1].view(torch.int32)[0]) == 1
+    words = recv[1].view(torch.int32).reshape(-1, 2)[:1024]
+    assert rel_l2(words[:, 0].contiguous().view(torch.float32), plain) < 1e-3
+    assert bool((words[:, 1] == 1).all())
     y2 = _allreduce_gemv(wt, x, 0.1, None, xc, 1)          # sticky status: returns without polling
     assert int(status.item()) == 1 and bool(torch.isfinite(y2.float()).all())
     torch.cuda.synchronize()
