@@ -353,21 +353,28 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
         const unsigned long long word = ((unsigned long long)ep << 32) | (unsigned long long)__float_as_uint(sum);
         for (int r = 0; r < p.xw; ++r) st_relaxed_sys_u64(p.xrecv[r] + (size_t)p.xrank * npad + col, word);
         const bool live = *reinterpret_cast<volatile int*>(p.xstatus) == 0;
+        // first look at every source at once (independent loads), then poll whatever is still missing
+        unsigned long long v[LEANKV_MAX_RANKS];
+        const unsigned long long* src0 = p.xrecv[p.xrank] + col;
+#pragma unroll
+        for (int r = 0; r < LEANKV_MAX_RANKS; ++r)
+            v[r] = r < p.xw ? ld_relaxed_sys_u64(src0 + (size_t)r * npad) : 0ull;
         float tot = 0.f;
         bool ok = live;
-        for (int r = 0; r < p.xw; ++r) {
-            const unsigned long long* src = p.xrecv[p.xrank] + (size_t)r * npad + col;
-            unsigned long long v = ld_relaxed_sys_u64(src);
-            if (live) {
-                int it = 0;
-                while ((unsigned int)(v >> 32) != ep && it < p.xlimit) {
-                    __nanosleep(20);
-                    v = ld_relaxed_sys_u64(src);
-                    ++it;
+#pragma unroll
+        for (int r = 0; r < LEANKV_MAX_RANKS; ++r) {
+            if (r < p.xw) {
+                if (live) {
+                    int it = 0;
+                    while ((unsigned int)(v[r] >> 32) != ep && it < p.xlimit) {
+                        __nanosleep(20);
+                        v[r] = ld_relaxed_sys_u64(src0 + (size_t)r * npad);
+                        ++it;
+                    }
+                    ok = ok && (unsigned int)(v[r] >> 32) == ep;
                 }
-                ok = ok && (unsigned int)(v >> 32) == ep;
+                tot += __uint_as_float((unsigned int)v[r]);
             }
-            tot += __uint_as_float((unsigned int)v);
         }
         if (!ok && live) atomicOr(p.xstatus, 1);
         sum = tot;
