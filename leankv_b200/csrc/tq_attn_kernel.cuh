@@ -261,24 +261,38 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
         __syncthreads();
         if (!s_last) return;
         __threadfence();
-        // last CTA of this (sequence, kv head): merge the chunk partials in chunk order
+        // last CTA of this (sequence, kv head): merge the chunk partials in chunk order.
+        // All maxima / sums first (one round trip, staged in the now idle ring), then the value rows
+        // with the loads of several chunks and all four heads in flight together.
         const float* base = p.partials + (((size_t)b * p.H + kvh) * p.n_chunks) * kPartialFloats;
+        float* s_ml = ring_f;                                     // [n_chunks_b][2 * kGroup]: m then l
+        for (int i = tid; i < n_chunks_b * 2 * kGroup; i += kAttnThreads)
+            s_ml[i] = ld_cg_f32(base + (size_t)(i >> 3) * kPartialFloats + kGroup * kDim + (i & 7));
+        __syncthreads();
+        float mg[kGroup];
 #pragma unroll
         for (int h = 0; h < kGroup; ++h) {
             float m = -INFINITY;
-            for (int c = 0; c < n_chunks_b; ++c)
-                m = fmaxf(m, ld_cg_f32(base + (size_t)c * kPartialFloats + kGroup * kDim + h));
-            float ov = 0.f, lv = 0.f;
-#pragma unroll 4
-            for (int c = 0; c < n_chunks_b; ++c) {
-                const float* pc = base + (size_t)c * kPartialFloats;
-                const float mc = ld_cg_f32(pc + kGroup * kDim + h);
-                const float f = mc == -INFINITY ? 0.f : ex2_approx(mc - m);
-                ov = fmaf(f, ld_cg_f32(pc + h * kDim + tid), ov);
-                lv = fmaf(f, ld_cg_f32(pc + kGroup * kDim + kGroup + h), lv);
-            }
-            o[h] = ov; lh[h] = lv;
+            for (int c = 0; c < n_chunks_b; ++c) m = fmaxf(m, s_ml[c * 2 * kGroup + h]);
+            mg[h] = m;
+            o[h] = 0.f;
+            lh[h] = 0.f;
         }
+#pragma unroll 4
+        for (int c = 0; c < n_chunks_b; ++c) {
+            const float* pc = base + (size_t)c * kPartialFloats + tid;
+            float ov[kGroup];
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) ov[h] = ld_cg_f32(pc + h * kDim);
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) {
+                const float mc = s_ml[c * 2 * kGroup + h];
+                const float f = mc == -INFINITY ? 0.f : ex2_approx(mc - mg[h]);
+                o[h] = fmaf(f, ov[h], o[h]);
+                lh[h] = fmaf(f, s_ml[c * 2 * kGroup + kGroup + h], lh[h]);
+            }
+        }
+        __syncthreads();                                          // s_ml is overwritten below (s_o / s_part)
         if (tid == 0) p.counters[b * p.H + kvh] = 0;
     }
 
