@@ -6,7 +6,10 @@
 A "step" is one decode step (one token through all layers). ``value`` is tok/s with the token fed
 back on the device (CUDA-graph replays, CUDA-event timing); ``e2e`` is the same loop with the token
 copied host->device before and device->host after every step. With N > 1 (torchrun) the model is
-tensor-parallel over N ranks (fixed total work: strong scaling). ``--impl reference`` times the CPU
+tensor-parallel over N ranks (fixed total work: strong scaling); the row-parallel projections sum
+their partial products over NVLink peer memory inside the GEMV kernel. The line also carries the
+per-kernel roofline legs, the batched 80-sequence decode (``batched_decode``; ``--workload batched``
+prints it alone) and the host-CPU baseline. ``--impl reference`` times the CPU
 restatement of the reference's PyTorch path (``oracle/``) on the host cores instead.
 Prints exactly one JSON line on rank 0.
 """
@@ -24,6 +27,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "B=1 decode tok/s (Mistral-7B shape)"
+GEMV_CONFIG1_DRAM_BYTES = 70_497_280 + 1_027_840
 PROMPT_LEN = 512
 SPARSITY = 0.4
 
@@ -608,7 +612,9 @@ def run_ours(args):
         g = legs["sparse_gemv_4096x14336"]
         line["roofline"] = {"bound": "hbm", "kernel": "sparse_gemv_kernel<false> (config 1: 4096 x 14336, 40 % sparse)",
                             "achieved": g["gbs"], "peak": peak_gbs, "unit": "GB/s", "frac": g["frac"],
-                            "traffic": None, "peak_source": peak_src,
+                            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this same leg
+                            # (ncu capture summarised in profiles/sparse_gemv_config1.md)
+                            "traffic": GEMV_CONFIG1_DRAM_BYTES, "peak_source": peak_src,
                             "algorithmic_bytes_per_launch": g["algorithmic_bytes"], "us_per_launch": g["us"]}
         line["kernels"] = legs
         if not args.no_cpu_baseline:

@@ -202,7 +202,13 @@ int leankv_tq_decode_attn(const void* q, void* out, int B, int n_q_heads, int n_
 
 /* Same attention for a caller that already holds the rotated query q_rot = Pi_k q
  * (fp32 [B][n_q_heads][128], e.g. from leankv_decode_qkv_post): skips the query-rotation
- * launch. Everything else as leankv_tq_decode_attn. */
+ * launch. Everything else as leankv_tq_decode_attn.
+ * Stream-ordering note: the kernel starts fetching the page table and every page except each
+ * sequence's last one while the launch queued directly before it may still be running (programmatic
+ * dependent launch). That launch may therefore write only q_rot and the last page of each sequence,
+ * which is what leankv_decode_qkv_post / leankv_batch_qkv_post do; a multi-page
+ * leankv_tq_pool_append must not be the launch directly before this call (leankv_tq_decode_attn
+ * is safe after it: its query-rotation launch sits in between). */
 int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int B, int n_q_heads, int n_kv_heads,
                                   const void* pool, int n_pages,
                                   const int32_t* kv_indptr, const int32_t* kv_page_indices,

@@ -320,7 +320,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
     dim3 grid(pl.n_chunks, n_kv_heads, B);
-    LEANKV_CUDA_TRY(launch_kernel(tq_decode_attn_kernel, grid, dim3(kAttnThreads), 0, st, p));
+    LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel, grid, dim3(kAttnThreads), 0, st, p));
     return LEANKV_OK;
 }
 

@@ -32,7 +32,9 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
     if (chunk == 0 && kvh == 0 && b == 0)
         for (int i = tid; i < kDim * kDim / 32; i += kAttnThreads)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Pi_v + i * 32));
-    pdl_begin();
+    // Everything up to pdl_begin() may run while the launch before this one is still executing. It
+    // reads only what older launches produced: the page table and every page except each sequence's
+    // last one (the page the preceding append / post kernel is writing the new token into).
     const int Hq = p.H * kGroup;
 
     const int seq_pg0 = p.indptr[b];
@@ -42,6 +44,7 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
     __half* out_base = p.out + ((size_t)b * Hq + (size_t)kvh * kGroup) * kDim;
 
     if (n_pages_b <= 0) {
+        pdl_begin();
         if (chunk == 0)
             for (int i = tid; i < kGroup * kDim; i += kAttnThreads) out_base[i] = __float2half_rn(0.f);
         return;
@@ -65,20 +68,6 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
         }
     }
 
-    // Query as the B operand of the score MMA: column n = g is (head g/2, hi|lo part g%2);
-    // k-step s covers rotated coordinates 32t + 4s .. +3.
-    const int head = g >> 1, part = g & 1;
-    uint32_t qf[8][2];
-    {
-        const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const float4 v = *reinterpret_cast<const float4*>(qp + 4 * s);
-            qf[s][0] = pack_h2(split_part(v.x * p.qscale, part), split_part(v.y * p.qscale, part));
-            qf[s][1] = pack_h2(split_part(v.z * p.qscale, part), split_part(v.w * p.qscale, part));
-        }
-    }
-
     const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
     const uint32_t ring0 = smem_u32(&s_ring[warp][0][0][0]);
     if (lane == 0) {
@@ -97,10 +86,32 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
         bulk_g2s(ring0 + s * 2 * kChunkBytes, src, kChunkBytes, bar0 + 8 * s);
         bulk_g2s(ring0 + s * 2 * kChunkBytes + kChunkBytes, src + kv_stride, kChunkBytes, bar0 + 8 * s);
     };
+    // first copies: all but the sequence's last page start now, that one after the wait
+    const int i_seq_last = n_pages_b - 1 - w_pg0;                   // index of the last page in this warp, if it has it
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
         const int pg = __shfl_sync(0xffffffffu, my_page, s);
-        if (lane == 0 && s < n_my) issue(s, pg);
+        if (lane == 0 && s < n_my && s != i_seq_last) issue(s, pg);
+    }
+
+    pdl_begin();
+    if (i_seq_last >= 0 && i_seq_last < kStages && i_seq_last < n_my) {
+        const int pg = __shfl_sync(0xffffffffu, my_page, i_seq_last);
+        if (lane == 0) issue(i_seq_last, pg);
+    }
+
+    // Query as the B operand of the score MMA: column n = g is (head g/2, hi|lo part g%2);
+    // k-step s covers rotated coordinates 32t + 4s .. +3.
+    const int head = g >> 1, part = g & 1;
+    uint32_t qf[8][2];
+    {
+        const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(qp + 4 * s);
+            qf[s][0] = pack_h2(split_part(v.x * p.qscale, part), split_part(v.y * p.qscale, part));
+            qf[s][1] = pack_h2(split_part(v.z * p.qscale, part), split_part(v.w * p.qscale, part));
+        }
     }
 
     float m_ref = -INFINITY, l_run = 0.f;     // m_ref: reference value of the exponentials (per head t)
