@@ -47,11 +47,14 @@ def load_model(model_name: str, dtype=torch.float16, device_map="cuda"):
 def optimize_model(model, teal_sparsity: Optional[float] = None,
                    teal_thresholds_path: Optional[str] = None,
                    turboquant_bits: Optional[int] = None, use_paged_cache: bool = False,
-                   page_size: int = 16, max_pages: int = 2048, use_triton: bool = False):
+                   page_size: int = 16, max_pages: int = 2048, use_triton: bool = False,
+                   fused_attention: bool = False):
     """Apply TEAL and/or build a TurboQuant cache; returns ``(model, cache)``.
 
     ``use_triton`` (an addition: the reference's ``optimize_model`` cannot select its kernel
     path, ``combined.py:83-87``) forwards to ``apply_teal`` and selects the CUDA sparse GEMV.
+    ``fused_attention`` (an addition, paged cache only) registers the HF attention function of
+    ``turboquant/hf_attention.py`` so that decode steps of ``model.generate`` run on the packed pages.
     """
     if teal_sparsity is not None or teal_thresholds_path is not None:
         apply_teal(model, sparsity=teal_sparsity, thresholds_path=teal_thresholds_path,
@@ -73,6 +76,11 @@ def optimize_model(model, teal_sparsity: Optional[float] = None,
                              bits=turboquant_bits if turboquant_bits is not None else 3)
         print(f"[LeanKV] PagedKVCache enabled (pages={max_pages}, page_size={page_size}, "
               f"pool={cache.get_total_pool_mb():.0f} MB)")
+        if fused_attention:
+            from .turboquant.hf_attention import enable_paged_attention
+
+            enable_paged_attention(model, cache)
+            print("[LeanKV] decode attention runs on the packed pages")
     elif turboquant_bits is not None:
         cache = TurboQuantCache(bits=turboquant_bits, head_dim=head_dim, num_layers=num_layers,
                                 device=model.device, dtype=torch.float16)
@@ -81,6 +89,9 @@ def optimize_model(model, teal_sparsity: Optional[float] = None,
 
 
 def reset_optimizations(model):
-    """Remove the TEAL hooks from ``model``."""
+    """Remove the TEAL hooks (and the paged attention function, if installed) from ``model``."""
+    from .turboquant.hf_attention import disable_paged_attention
+
     remove_teal(model)
+    disable_paged_attention(model)
     print("[LeanKV] All optimizations removed.")

@@ -64,6 +64,7 @@ class PagedKVCache:
         self._pending_start: list[int] = []   # start positions of the append in flight (per layer pass)
         self._meta = None                     # device copies of the page table, rebuilt when stale
         self._workspace = None
+        self.fused_decode = False             # set by hf_attention.enable_paged_attention
 
     # ── page management ────────────────────────────────────────────────
 
@@ -104,8 +105,14 @@ class PagedKVCache:
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
                cache_kwargs=None):
-        """Quantize-append ``[B, Hkv, T_new, D]`` K/V of one layer; return dense ``(K, V)``."""
+        """Quantize-append ``[B, Hkv, T_new, D]`` K/V of one layer; return dense ``(K, V)``.
+
+        With ``fused_decode`` set (``hf_attention.enable_paged_attention``) a one-token update only
+        appends and hands the new token's own K/V back as a placeholder: the registered attention
+        function answers from the packed pages and never looks at it."""
         self.append(layer_idx, key_states, value_states)
+        if self.fused_decode and key_states.shape[2] == 1:
+            return key_states, value_states
         return self._gather_kv(layer_idx, key_states.shape[0])
 
     def append(self, layer_idx: int, key_states: torch.Tensor, value_states: torch.Tensor):
