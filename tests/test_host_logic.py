@@ -212,3 +212,26 @@ def test_paged_cache_page_accounting():
     assert c.get_pages_used() == 0 and c.get_max_length() == 64
     with pytest.raises(RuntimeError):
         PagedKVCache(head_dim=64, device="cpu")
+
+
+def test_threshold_files_round_trip_in_the_reference_format(tmp_path, capsys):
+    """thresholds_s{NN}.json as the reference's calibration writes it (leankv/teal/greedy_opt.py:183-199):
+    string layer keys, 0.0 = projection left dense; saved files load back and feed apply_teal."""
+    from leankv_b200.teal.greedy_opt import load_thresholds, save_thresholds
+
+    thr = {0: {p: 0.25 * (i + 1) for i, p in enumerate(patching.PROJ_NAMES)}, 1: {"q_proj": 0.0, "down_proj": 1.5}}
+    path = tmp_path / "thresholds" / "thresholds_s40.json"
+    save_thresholds(thr, str(path))
+    assert "Saved thresholds" in capsys.readouterr().out
+    on_disk = json.loads(path.read_text())
+    assert set(on_disk) == {"0", "1"} and on_disk["1"] == {"q_proj": 0.0, "down_proj": 1.5}
+    assert load_thresholds(str(path)) == thr
+    # a file written by hand the way the reference does (keys already strings)
+    ref_style = tmp_path / "ref.json"
+    ref_style.write_text(json.dumps({"1": {"o_proj": 0.5}, "0": {"q_proj": 0.125}}, indent=2))
+    assert load_thresholds(str(ref_style)) == {1: {"o_proj": 0.5}, 0: {"q_proj": 0.125}}
+    model = _tiny_model()
+    sp = patching.apply_teal(model, thresholds_path=str(path))
+    assert sp[(0, "k_proj")].threshold == 0.5 and not sp[(1, "q_proj")].enabled
+    assert sp[(1, "down_proj")].threshold == 1.5
+    patching.remove_teal(model)
