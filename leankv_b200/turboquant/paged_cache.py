@@ -64,6 +64,7 @@ class PagedKVCache:
         self._pending_start: list[int] = []   # start positions of the append in flight (per layer pass)
         self._meta = None                     # device copies of the page table, rebuilt when stale
         self._workspace = None
+        self._start_dev = None
         self.fused_decode = False             # set by hf_attention.enable_paged_attention
 
     # ── page management ────────────────────────────────────────────────
@@ -130,8 +131,11 @@ class PagedKVCache:
                     self._seq_page_indices[b].append(self._allocate_page())
                 self._seq_lengths[b] += t_new
             self._meta = None
+            self._start_dev = torch.tensor(self._pending_start[:batch], dtype=torch.int32, device=self._device)
         indptr, flat, _ = self._device_meta(batch)
-        start = torch.tensor(self._pending_start[:batch], dtype=torch.int32, device=self._device)
+        if self._start_dev is None or self._start_dev.numel() != batch:
+            self._start_dev = torch.tensor(self._pending_start[:batch], dtype=torch.int32, device=self._device)
+        start = self._start_dev          # one host-to-device copy per step, shared by all layers
         k = key_states.to(torch.float16).contiguous()
         v = value_states.to(torch.float16).contiguous()
         kq, vq = self.key_quantizers[layer_idx], self.val_quantizers[layer_idx]
@@ -249,6 +253,8 @@ class PagedKVCache:
         self._batch_size = 0
         self._seen_tokens = 0
         self._meta = None
+        self._start_dev = None
+        self._pending_start = []
         self.kv_data.zero_()
 
     @property
