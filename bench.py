@@ -173,7 +173,7 @@ def _config(n_gpus):
             "l2": "weights streamed per step (8.7 GB) exceed L2 (126 MB); kernel legs rotate 5 weight copies"}
 
 
-# ── kernel legs: each hot kernel alone on its BASELINE configuration ─────────────────────────
+# ── kernel legs: each hot kernel alone on its benchmark configuration ────────────────────────
 
 def time_kernel(fn, n_variants: int, iters: int, warmup: int = 5):
     """Average device time of fn(i % n_variants) over ``iters`` launches (CUDA events, current stream)."""
