@@ -235,3 +235,51 @@ def test_threshold_files_round_trip_in_the_reference_format(tmp_path, capsys):
     assert sp[(0, "k_proj")].threshold == 0.5 and not sp[(1, "q_proj")].enabled
     assert sp[(1, "down_proj")].threshold == 1.5
     patching.remove_teal(model)
+
+
+def test_argument_validation_of_the_decode_and_exchange_entry_points():
+    """Glue kernels, batched glue kernels and the GEMV + all-reduce entry reject bad arguments with a
+    status code before anything is launched (so this runs without a GPU)."""
+    lib = _native.lib()
+    fake, odd = 0x10000, 0x10002
+    assert lib.leankv_rmsnorm_f16(None, None, fake, fake, 4096, 1e-5, None) == -1
+    assert lib.leankv_rmsnorm_f16(fake, None, fake, fake, 4100, 1e-5, None) == -2
+    assert lib.leankv_rmsnorm_f16(fake, None, fake, fake, 1 << 20, 1e-5, None) == -6
+    assert lib.leankv_rmsnorm_rows_f16(fake, None, fake, fake, 0, 4096, 1e-5, None) == -1
+    assert lib.leankv_rmsnorm_rows_f16(odd, None, fake, fake, 4, 4096, 1e-5, None) == -2
+    assert lib.leankv_rope_f16(fake, fake, fake, fake, fake, 32, 8, 64, None) == -5      # head_dim != 128
+    assert lib.leankv_decode_begin(fake, fake, fake, 4100, 100, fake, None) == -2
+    assert lib.leankv_decode_end(odd, 32768, fake, fake, 8, fake, None) == -2
+    assert lib.leankv_decode_qkv_post(fake, fake, fake, fake, fake, fake, None, 4, fake, 32, 8, fake, None) == -1
+    assert lib.leankv_batch_qkv_post(fake, 2, fake, fake, None, fake, fake, fake, fake, 4, fake, 32, 8, fake,
+                                     None) == -1                                       # kv_indptr required
+    assert lib.leankv_batch_decode_begin(fake, fake, fake, 4096, 100, 0, fake, fake, 4, fake, fake, fake,
+                                         None) == -1
+    assert lib.leankv_batch_decode_end(fake, 32770, 2, fake, fake, 8, fake, fake, None) == -2   # vocab % 8
+    assert lib.leankv_silu_mul_f16(fake, fake, 2, 1001, None) == -2
+    assert lib.leankv_xchg_advance(None, None) == -1
+    assert lib.leankv_xchg_recv_bytes(4, 64, 4096) == 8 * 64 * 4 * 4096
+    assert lib.leankv_xchg_recv_bytes(0, 64, 4096) == 0
+
+    x = _native.Xchg()
+    x.world, x.rank, x.n_slots, x.max_cols, x.max_wait_iters = 2, 0, 4, 4096, 100
+    x.recv[0], x.recv[1] = fake, fake
+    x.epoch, x.status = fake, fake
+    ws = lib.leankv_sparse_gemv_workspace_bytes(4096, 2048)
+    call = lambda xc, slot, n=4096: lib.leankv_sparse_gemv_allreduce_f16(
+        fake, fake, fake, n, 2048, 0.1, None, fake, ws, None, ctypes.byref(xc), slot, None)
+    assert call(x, 4) == -1                      # slot outside the area
+    x.rank = 2
+    assert call(x, 0) == -1                      # rank outside the world
+    x.rank, x.world = 0, 9
+    assert call(x, 0) == -1                      # more ranks than the struct can hold
+    x.world, x.max_cols = 2, 1000
+    assert call(x, 0) == -1                      # max_cols not a multiple of 256
+    x.max_cols = 2048
+    assert call(x, 0) == -1                      # N does not fit the receive area
+    x.max_cols, x.recv[1] = 4096, None
+    assert call(x, 0) == -1                      # a peer's area is missing
+    x.recv[1], x.max_wait_iters = fake + 4, 100
+    assert call(x, 0) == -1                      # receive area not 8-byte aligned
+    assert lib.leankv_ipc_alloc(0, None, None) == -1 and lib.leankv_ipc_open(None, None) == -1
+    assert lib.leankv_ipc_close(None) == -1 and lib.leankv_ipc_free(None) == -1
