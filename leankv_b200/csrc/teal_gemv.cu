@@ -10,6 +10,11 @@
 // arrive for a column slice sums them in split order, so the result does not depend on
 // arrival order and no floating-point atomics are used.
 //
+// The same kernel also serves: per-segment thresholds (fused q/k/v), bias, residual add, the fused
+// gate/up SwiGLU (template flag), RMSNorm of the input row fused into the prologue, and the
+// tensor-parallel form in which the finishing CTA sums the ranks' partial products over peer
+// memory before it writes y.
+//
 // Arithmetic follows the reference's B=1 path (leankv/teal/kernels/sparse_gemv.py:71-87:
 // fp16 operands widened to fp32, fp32 sums) and the mask of leankv/teal/sparse_fns.py:36
 // (strict '>' against the threshold rounded to fp16).

@@ -15,8 +15,10 @@
 // centroids, scaled by a factor alpha chosen so that all of them are (almost) exactly
 // representable in fp16, live in four registers used as 8-entry byte tables. Scores
 // (16 tokens x 4 query heads) and the value sum (128 coordinates x 4 heads) are
-// m16n8k16 tensor-core MMAs whose eight N columns carry the four GQA heads as fp16
-// hi/lo pairs, so query and probability rounding does not limit accuracy.
+// m16n8k16 tensor-core MMAs whose eight N columns carry the four GQA heads: as fp16
+// hi/lo pairs of the query for the scores (so query rounding does not limit accuracy),
+// and as single fp16 probabilities (lo columns zero) for the value sum, where rounding
+// is independent from token to token and averages out.
 //
 // Split-KV: a CTA (4 warps) covers a range of pages; CTA partials are merged, in chunk
 // order, by the last CTA to arrive for a (sequence, kv head), which also applies the
