@@ -58,6 +58,25 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
     for (int b = blockIdx.y; b < p.B; b += gridDim.y) {
         const int pos = p.pos[b];
         const __half* src = p.qkv + (size_t)b * row + (size_t)head * kDim;
+        // where the new token goes: fetched now so that the page-table round trip (and, for V, the word
+        // shared with the pair token) overlaps the arithmetic instead of trailing it
+        const int which = kind - 1;
+        const int h = which == 0 ? head - p.nq : head - p.nq - p.nkv;
+        const int slot = pos & 15;
+        int page = -1;
+        uint32_t* words = nullptr;
+        uint32_t old_word = 0;
+        if (kind != 0) {
+            const int base = p.kv_indptr != nullptr ? p.kv_indptr[b] : 0;
+            page = p.page_indices[base + (pos >> 4)];
+            if (page >= 0 && page < p.n_pages) {
+                words = reinterpret_cast<uint32_t*>(p.pool + (((size_t)page * 2 + which) * p.nkv + h) * kChunkBytes);
+                if (which == 1 && j < 24) {
+                    const int g = j & 7, kk = j >> 3, pr = slot >> 1;
+                    old_word = words[kk * 64 + (pr < 4 ? 4 * g + pr : 32 + 4 * g + (pr - 4))];
+                }
+            }
+        }
 
         __half xv = src[j];
         if (kind != 2) {
@@ -109,13 +128,8 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
         s_code[j] = (uint8_t)code;
         __syncthreads();
 
-        const int which = kind - 1;
-        const int h = which == 0 ? head - p.nq : head - p.nq - p.nkv;
-        const int base = p.kv_indptr != nullptr ? p.kv_indptr[b] : 0;
-        const int page = p.page_indices[base + (pos >> 4)], slot = pos & 15;
-        if (page < 0 || page >= p.n_pages) continue;
-        uint8_t* chunk = p.pool + (((size_t)page * 2 + which) * p.nkv + h) * kChunkBytes;
-        uint32_t* words = reinterpret_cast<uint32_t*>(chunk);
+        if (words == nullptr) continue;
+        uint8_t* chunk = reinterpret_cast<uint8_t*>(words);
         if (j == 0) reinterpret_cast<__half*>(chunk + kNormOffsetBytes)[slot] = __float2half_rn(norm);
 
         if (which == 0) {
@@ -135,8 +149,7 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
 #pragma unroll 8
                 for (int c = 0; c < 16; ++c) bits |= unit_word_bits(2 * c + par, kk, s_code[16 * g + c]);
                 const uint32_t keep = par ? 0x0F0F0F0Fu : 0xF0F0F0F0u;   // the other token's nibbles
-                const int w = kk * 64 + ui;
-                words[w] = bits | (words[w] & keep);
+                words[kk * 64 + ui] = bits | (old_word & keep);
             }
         }
     }

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
     if (p.norm_w != nullptr) {
         float ss = 0.f;
         const uint4* hv = reinterpret_cast<const uint4*>(p.x);
+#pragma unroll 4
         for (int i = tid; i < (p.Z >> 3); i += kThreads) {
             const uint4 a = hv[i];
             const float2 f0 = h2_to_f2(a.x), f1 = h2_to_f2(a.y), f2 = h2_to_f2(a.z), f3 = h2_to_f2(a.w);
@@ -314,16 +315,33 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
 #pragma unroll
             for (int j = 0; j < 8; ++j) m[j] = m2[j] = 0.f;
             const float* base = p.partials + slice * kColsPerCta + lane * 8;
-#pragma unroll 4
-            for (int k = warp; k < p.k_splits; k += kWarps) {
-                const float* src = base + ((size_t)k * kArrays) * npad;
-                const float4 a = ld_cg_f32x4(src), b = ld_cg_f32x4(src + 4);
-                m[0] += a.x; m[1] += a.y; m[2] += a.z; m[3] += a.w;
-                m[4] += b.x; m[5] += b.y; m[6] += b.z; m[7] += b.w;
-                if (kSwiglu) {
-                    const float4 c = ld_cg_f32x4(src + npad), d = ld_cg_f32x4(src + npad + 4);
-                    m2[0] += c.x; m2[1] += c.y; m2[2] += c.z; m2[3] += c.w;
-                    m2[4] += d.x; m2[5] += d.y; m2[6] += d.z; m2[7] += d.w;
+            // kBatch splits' loads are issued together (one L2 round trip for up to 8 * kBatch splits);
+            // the sums are still taken in ascending split order
+            constexpr int kBatch = kSwiglu ? 2 : 5;
+            for (int k0 = warp; k0 < p.k_splits; k0 += kWarps * kBatch) {
+                float4 a[kBatch], b[kBatch], c[kSwiglu ? kBatch : 1], d[kSwiglu ? kBatch : 1];
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const int k = k0 + i * kWarps;
+                    const float* src = base + ((size_t)k * kArrays) * npad;
+                    const bool ok = k < p.k_splits;
+                    a[i] = ok ? ld_cg_f32x4(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    b[i] = ok ? ld_cg_f32x4(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (kSwiglu) {
+                        c[i] = ok ? ld_cg_f32x4(src + npad) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        d[i] = ok ? ld_cg_f32x4(src + npad + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    if (k0 + i * kWarps < p.k_splits) {
+                        m[0] += a[i].x; m[1] += a[i].y; m[2] += a[i].z; m[3] += a[i].w;
+                        m[4] += b[i].x; m[5] += b[i].y; m[6] += b[i].z; m[7] += b[i].w;
+                        if (kSwiglu) {
+                            m2[0] += c[i].x; m2[1] += c[i].y; m2[2] += c[i].z; m2[3] += c[i].w;
+                            m2[4] += d[i].x; m2[5] += d[i].y; m2[6] += d[i].z; m2[7] += d[i].w;
+                        }
+                    }
                 }
             }
             float4* d = reinterpret_cast<float4*>(&s_red[warp][0][lane * 8]);
