@@ -459,6 +459,10 @@ class DecodeEngine:
             with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
                 self._step_launches()
             # capture does not execute; state is unchanged
+            if self.tp_size > 1:
+                # the in-kernel exchange waits a bounded time for its peers: start the replays together
+                torch.cuda.synchronize()
+                torch.distributed.barrier(group=self.group)
 
     def step(self, use_graph: bool = True) -> None:
         if use_graph:
