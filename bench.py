@@ -147,6 +147,57 @@ def cpu_decode_sample(n_steps: int, warmup: int, threads: int, ctx: int = PROMPT
     return tok_s, sample, t_layer
 
 
+def cpu_kernel_legs(threads: int) -> dict:
+    """The reference's CPU path (oracle port) on configurations 1-3, on the host cores, bounded to a few
+    seconds each: masked fp16 F.linear for the two GEMV configs; quantize + de-quantize + attention
+    over one of config 3's 16 sequences (scaled by 16 in the reported time)."""
+    import torch
+
+    from leankv_b200 import workloads
+    from oracle import teal as oteal, turboquant as otq
+
+    torch.set_num_threads(threads)
+    out = {"cores": threads, "kind": "port"}
+
+    def timeit(fn, reps):
+        fn()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        return (time.perf_counter() - t0) / reps
+
+    with torch.no_grad():
+        c1 = workloads.sparse_gemv_case(device="cpu")
+        out["sparse_gemv_4096x14336_us"] = 1e6 * timeit(lambda: oteal.sparse_linear(c1.x, c1.weight, c1.threshold), 20)
+        del c1
+        c2 = workloads.swiglu_case(device="cpu")
+        out["sparse_swiglu_14336x4096_us"] = 1e6 * timeit(
+            lambda: oteal.swiglu(c2.x, c2.w_gate, c2.w_up, c2.threshold, c2.threshold), 10)
+        del c2
+        gen = torch.Generator().manual_seed(3)
+        H, T = 8, 4096
+        k, v = torch.randn(1, H, T, 128, generator=gen), torch.randn(1, H, T, 128, generator=gen)
+        q = torch.randn(1, 32, 128, generator=gen).half()
+        cb = otq.lloyd_max(128, 3)
+        bounds, cents = torch.tensor(cb["boundaries"][1:-1]), torch.tensor(cb["centroids"])
+        Pk, Pv = otq.rotation_matrix(128, 42), otq.rotation_matrix(128, 43)
+        t0 = time.perf_counter()
+        qk, qv = otq.quantize(k, Pk, bounds, 3)[:2], otq.quantize(v, Pv, bounds, 3)[:2]
+        t_quant = time.perf_counter() - t0
+
+        def attend():
+            k_hat = otq.dequantize(qk[0], qk[1], Pk, cents, 3, 128).half()
+            v_hat = otq.dequantize(qv[0], qv[1], Pv, cents, 3, 128).half()
+            return otq.kv_attention(q, k_hat, v_hat, 128 ** -0.5)
+
+        t_attn = timeit(attend, 2)
+        out["tq_bulk_quantize_append_b16_t4096_us"] = 16e6 * t_quant
+        out["tq_decode_attn_b16_t4096_us"] = 16e6 * t_attn
+        out["sample"] = ("configs 1 and 2 in full (20 / 10 repetitions); config 3 on 1 of its 16 sequences "
+                         "(8 kv heads x 4096 tokens), time x 16")
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -621,7 +672,7 @@ def run_ours(args):
             threads = os.cpu_count() or 1
             tok_s, sample, _ = cpu_decode_sample(8, 2, threads)
             line["cpu_baseline"] = {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
-                                    "sample": sample}
+                                    "sample": sample, "kernels": cpu_kernel_legs(threads)}
     else:
         line["roofline"] = {"bound": "hbm", "kernel": "whole decode step (all kernels)", "achieved": line["step"]["gbs_per_gpu"],
                             "peak": peak_gbs, "unit": "GB/s", "frac": line["step"]["frac_of_peak"], "traffic": None,
