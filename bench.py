@@ -330,6 +330,10 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
     start = torch.zeros(B, dtype=torch.int32, device=dev)
     pools = [torch.zeros(kv.n_pages, 2, H, 800, dtype=torch.uint8, device=dev) for _ in range(4)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    lib.leankv_tq_pool_append(kv.k.data_ptr(), kv.v.data_ptr(), B, H, T, Pk.data_ptr(), Pv.data_ptr(),
+                              bounds_d.data_ptr(), pools[0].data_ptr(), kv.n_pages, indptr.data_ptr(),
+                              flat.data_ptr(), start.data_ptr(), st)          # untimed warm-up launch
+    torch.cuda.synchronize()
     e0.record()
     for p in pools:
         lib.leankv_tq_pool_append(kv.k.data_ptr(), kv.v.data_ptr(), B, H, T, Pk.data_ptr(), Pv.data_ptr(),
