@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
     __shared__ float s_u[kDim];       // what gets rotated: x for q, x / (norm + 1e-10) for k and v
     __shared__ double s_ss[2];
     __shared__ float s_bounds[8];
-    __shared__ uint8_t s_code[kDim];
+    __shared__ __align__(4) uint8_t s_code[kDim];
 
     const int j = threadIdx.x;
     const int head = blockIdx.x;
@@ -132,22 +132,27 @@ __global__ void __launch_bounds__(kDim) decode_qkv_post_kernel(const PostParams 
         uint8_t* chunk = reinterpret_cast<uint8_t*>(words);
         if (j == 0) reinterpret_cast<__half*>(chunk + kNormOffsetBytes)[slot] = __float2half_rn(norm);
 
+        // four codes per 32-bit shared-memory load; pack4 squeezes the low nibbles of 4 bytes into 16 bits
+        auto pack4 = [](uint32_t v) -> uint32_t {
+            const uint32_t t2 = (v | (v >> 4)) & 0x00FF00FFu;
+            return (t2 | (t2 >> 8)) & 0xFFFFu;
+        };
         if (which == 0) {
             if (j < 12) {                      // 4 units (quarters of the vector) x 3 words, this token only
                 const int t4 = j & 3, kk = j >> 2;
-                uint32_t bits = 0;
-#pragma unroll 8
-                for (int e = 0; e < 32; ++e) bits |= unit_word_bits(e, kk, s_code[32 * t4 + e]);
-                words[kk * 64 + slot * 4 + t4] = bits;
+                const uint32_t* c4 = reinterpret_cast<const uint32_t*>(&s_code[32 * t4]);
+                const uint32_t lo = c4[2 * kk] & 0x07070707u, hi = c4[2 * kk + 1] & 0x07070707u;
+                const uint32_t s_lo = ((c4[6] >> kk) & 0x01010101u) << 3, s_hi = ((c4[7] >> kk) & 0x01010101u) << 3;
+                words[kk * 64 + slot * 4 + t4] = pack4(lo) | (pack4(hi) << 16) | pack4(s_lo) | (pack4(s_hi) << 16);
             }
         } else {
             if (j < 24) {                      // 8 units (16-coordinate groups) x 3 words, shared with the pair token
                 const int g = j & 7, kk = j >> 3;
                 const int pr = slot >> 1, par = slot & 1;
                 const int ui = pr < 4 ? 4 * g + pr : 32 + 4 * g + (pr - 4);
-                uint32_t bits = 0;
-#pragma unroll 8
-                for (int c = 0; c < 16; ++c) bits |= unit_word_bits(2 * c + par, kk, s_code[16 * g + c]);
+                const uint32_t* ca = reinterpret_cast<const uint32_t*>(&s_code[16 * g]);
+                const uint32_t a4 = ca[kk] & 0x07070707u, as4 = (ca[3] >> kk) & 0x01010101u;
+                const uint32_t bits = par ? ((a4 << 4) | (as4 << 7)) : (a4 | (as4 << 3));
                 const uint32_t keep = par ? 0x0F0F0F0Fu : 0xF0F0F0F0u;   // the other token's nibbles
                 words[kk * 64 + ui] = bits | (old_word & keep);
             }
