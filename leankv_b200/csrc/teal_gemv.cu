@@ -30,6 +30,7 @@ constexpr int kColsPerCta = 256;       // 32 lanes x 8 fp16
 constexpr int kLaneSlots = 4;          // threshold tests per lane during compaction
 constexpr int kMaxRowsPerSplit = kWarps * 32 * kLaneSlots;  // 1024
 constexpr int kMaxSplits = 128;
+constexpr int kMaxSplitsNarrow = 40;   // = kWarps x the merge's load batch: the last CTA sums a slice in one round trip
 constexpr int kCtasPerSm = 4;
 
 struct GemvParams {
@@ -85,7 +86,10 @@ GemvPlan make_plan(int N, int Z, int arrays) {
     int by_rows = Z / 32;            // keep at least ~32 input channels per split
     if (by_rows < 1) by_rows = 1;
     if (ks > by_rows) ks = by_rows;
-    if (ks > kMaxSplits) ks = kMaxSplits;
+    // Narrow matrices (a tensor-parallel rank's share) would otherwise be cut into ~100 splits of a few
+    // rows each, and the time goes into merging them: measured 8.6 -> 6.8 us for 768 x 4096.
+    const int max_splits = pl.n_slices <= 8 ? kMaxSplitsNarrow : kMaxSplits;
+    if (ks > max_splits) ks = max_splits;
     int rows = (Z + ks - 1) / ks;
     if (rows > kMaxRowsPerSplit) rows = kMaxRowsPerSplit;
     pl.rows_per_split = rows;
