@@ -378,7 +378,13 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
         // meaningless, but no kernel hangs).
         const unsigned int ep = (unsigned int)*reinterpret_cast<const volatile int*>(p.xepoch);
         const unsigned long long word = ((unsigned long long)ep << 32) | (unsigned long long)__float_as_uint(sum);
-        for (int r = 0; r < p.xw; ++r) st_relaxed_sys_u64(p.xrecv[r] + (size_t)p.xrank * npad + col, word);
+        // every rank starts with a different destination so that the ranks' stores do not all converge on
+        // one GPU's links at the same moment
+        for (int i = 0; i < p.xw; ++i) {
+            int r = p.xrank + i;
+            r = r >= p.xw ? r - p.xw : r;
+            st_relaxed_sys_u64(p.xrecv[r] + (size_t)p.xrank * npad + col, word);
+        }
         const bool live = *reinterpret_cast<volatile int*>(p.xstatus) == 0;
         // first look at every source at once (independent loads), then poll whatever is still missing
         unsigned long long v[LEANKV_MAX_RANKS];
