@@ -357,6 +357,17 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
     out["tq_decode_attn_b16_t4096"] = {"us": t * 1e6, "algorithmic_bytes": alg, "gbs": alg / t / 1e9,
                                        "frac": alg / t / 1e9 / peak_gbs, "launches_timed": 2 * iters,
                                        "note": "two launches per call: query rotation + attention"}
+    # the same attention on a query that is already rotated (what the decode loops use: the rotation
+    # happens in the fused post kernel), one launch per call
+    q_rot = (kv.q.float() @ Pk.t()).contiguous()
+    fn4 = lambda i: lib.leankv_tq_decode_attn_rotated(q_rot.data_ptr(), o.data_ptr(), B, 32, H, pools[i].data_ptr(),
+                                                      kv.n_pages, indptr.data_ptr(), flat.data_ptr(),
+                                                      last.data_ptr(), 256, Pv.data_ptr(), cents_h.data_ptr(),
+                                                      1.0 / math.sqrt(128.0), wsa.data_ptr(), wsa.numel(), st)
+    t4 = time_kernel(fn4, len(pools), iters)
+    alg4 = alg + 2 * B * 32 * 128          # fp32 instead of fp16 query
+    out["tq_decode_attn_rotated_b16_t4096"] = {"us": t4 * 1e6, "algorithmic_bytes": alg4, "gbs": alg4 / t4 / 1e9,
+                                               "frac": alg4 / t4 / 1e9 / peak_gbs, "launches_timed": iters}
 
 
 def exchange_leg(dev, world, rank, group, iters=200):
