@@ -27,9 +27,20 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "B=1 decode tok/s (Mistral-7B shape)"
-GEMV_CONFIG1_DRAM_BYTES = 70_497_280 + 1_027_840
 PROMPT_LEN = 512
 SPARSITY = 0.4
+
+
+def _captured_traffic(name: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the ncu capture recorded
+    for kernel ``name`` in profiles/captures.json, with the capture's label; (None, None) if absent."""
+    path = os.path.join(ROOT, "profiles", "captures.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)[name]
+        return int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"]), rec.get("capture")
+    except Exception:
+        return None, None
 
 
 def _peaks():
@@ -90,17 +101,39 @@ class ClockSampler:
 
 # ── CPU baseline: the reference's PyTorch path restated in oracle/, on the host cores ──────────
 
+def _reference_ops():
+    """The reference's own functions for the per-layer CPU arithmetic, from the copy of its package under
+    oracle/_ref (made by oracle/build_ref.py where a reference checkout is present), or None."""
+    try:
+        from oracle import build_ref
+
+        if not build_ref.available():
+            return None
+        build_ref.load()
+        from leankv.teal.sparse_fns import SparsifyFn, compute_threshold_for_sparsity
+        from leankv.turboquant.quantizer import TurboQuantMSE
+
+        return {"SparsifyFn": SparsifyFn, "threshold": compute_threshold_for_sparsity, "TurboQuantMSE": TurboQuantMSE}
+    except Exception:
+        return None
+
+
 def cpu_decode_sample(n_steps: int, warmup: int, threads: int, ctx: int = PROMPT_LEN + 128):
     """Times decode steps of ONE Mistral-7B-shaped layer on the CPU the way the reference runs it:
     TEAL hook (mask, dense fp16 F.linear) on the seven projections, TurboQuant cache update
     (quantize the new token, de-quantize the whole cold cache) and attention. A token costs 32 such
-    layers plus the lm_head GEMV; tok/s is extrapolated from the per-layer time."""
+    layers plus the lm_head GEMV; tok/s is extrapolated from the per-layer time. Where the copy of the
+    reference package is importable its own SparsifyFn / TurboQuantMSE do the arithmetic (kind
+    "reference"), otherwise the restatement in oracle/ (kind "port"). Thresholds are fixed before the
+    timed loop (the reference calibrates them offline)."""
     import torch
     import torch.nn.functional as F
 
     from oracle import teal as oteal, turboquant as otq
 
     torch.set_num_threads(threads)
+    ref = _reference_ops()
+    kind = "reference" if ref is not None else "port"
     gen = torch.Generator().manual_seed(0)
     H, I, nq, nkv, V = 4096, 14336, 32, 8, 32768
     w = {n: (torch.randn(o, i, generator=gen) * 0.02).half()
@@ -108,33 +141,49 @@ def cpu_decode_sample(n_steps: int, warmup: int, threads: int, ctx: int = PROMPT
                                gate=(I, H), up=(I, H), down=(H, I)).items()}
     lm_head = (torch.randn(V, H, generator=gen) * 0.02).half()
     x0 = torch.distributions.Laplace(0.0, 1.0).sample((1, H)).half()
-    cb = otq.lloyd_max(128, 3)
-    bounds = torch.tensor(cb["boundaries"][1:-1])
-    cents = torch.tensor(cb["centroids"])
-    Pi_k, Pi_v = otq.rotation_matrix(128, 42), otq.rotation_matrix(128, 43)
     kv = torch.randn(2, 1, nkv, ctx, 128, generator=gen)
-    cold = [otq.quantize(kv[i], Pi, bounds, 3)[:2] for i, Pi in ((0, Pi_k), (1, Pi_v))]
+    if ref is not None:
+        qk, qv = ref["TurboQuantMSE"](128, 3, "cpu", torch.float32, seed=42), ref["TurboQuantMSE"](128, 3, "cpu", torch.float32, seed=43)
+        cold = [qk.quantize(kv[0]), qv.quantize(kv[1])]
+        quantize = lambda x, which: (qk if which == 0 else qv).quantize(x)
+        dequantize = lambda which: (qk if which == 0 else qv).dequantize(cold[which])
+        sparse_linear = lambda x, wt, t: F.linear(ref["SparsifyFn"](t)(x), wt)
+        thr = ref["threshold"]
+    else:
+        cb = otq.lloyd_max(128, 3)
+        bounds = torch.tensor(cb["boundaries"][1:-1])
+        cents = torch.tensor(cb["centroids"])
+        Pi = (otq.rotation_matrix(128, 42), otq.rotation_matrix(128, 43))
+        cold = [otq.quantize(kv[i], Pi[i], bounds, 3)[:2] for i in (0, 1)]
+        quantize = lambda x, which: otq.quantize(x, Pi[which], bounds, 3)
+        dequantize = lambda which: otq.dequantize(cold[which][0], cold[which][1], Pi[which], cents, 3, 128)
+        sparse_linear = oteal.sparse_linear
+        thr = oteal.threshold_for_sparsity
 
-    def layer_step(x):
-        t = oteal.threshold_for_sparsity(x, SPARSITY)
-        q = oteal.sparse_linear(x, w["q"], t).reshape(1, nq, 128)
-        k = oteal.sparse_linear(x, w["k"], t).reshape(1, nkv, 1, 128)
-        v = oteal.sparse_linear(x, w["v"], t).reshape(1, nkv, 1, 128)
-        otq.quantize(k.float(), Pi_k, bounds, 3)
-        otq.quantize(v.float(), Pi_v, bounds, 3)
-        k_hat = otq.dequantize(cold[0][0], cold[0][1], Pi_k, cents, 3, 128).half()
-        v_hat = otq.dequantize(cold[1][0], cold[1][1], Pi_v, cents, 3, 128).half()
+    def layer_step(x, t):
+        q = sparse_linear(x, w["q"], t["x"]).reshape(1, nq, 128)
+        k = sparse_linear(x, w["k"], t["x"]).reshape(1, nkv, 1, 128)
+        v = sparse_linear(x, w["v"], t["x"]).reshape(1, nkv, 1, 128)
+        quantize(k.float(), 0)
+        quantize(v.float(), 1)
+        k_hat = dequantize(0).half()
+        v_hat = dequantize(1).half()
         a = otq.kv_attention(q, k_hat, v_hat, 128 ** -0.5).half().reshape(1, nq * 128)
-        h = x + oteal.sparse_linear(a, w["o"], oteal.threshold_for_sparsity(a, SPARSITY))
-        m = oteal.swiglu(h, w["gate"], w["up"], t, t)
-        return h + oteal.sparse_linear(m, w["down"], oteal.threshold_for_sparsity(m, SPARSITY))
+        if "a" not in t:
+            t["a"] = thr(a, SPARSITY)
+        h = x + sparse_linear(a, w["o"], t["a"])
+        m = F.silu(sparse_linear(h, w["gate"], t["x"])) * sparse_linear(h, w["up"], t["x"])
+        if "m" not in t:
+            t["m"] = thr(m, SPARSITY)
+        return h + sparse_linear(m, w["down"], t["m"])
 
     with torch.no_grad():
+        t = {"x": thr(x0, SPARSITY)}
         for _ in range(max(warmup, 1)):
-            layer_step(x0)
+            layer_step(x0, t)
         t0 = time.perf_counter()
         for _ in range(n_steps):
-            layer_step(x0)
+            layer_step(x0, t)
         t_layer = (time.perf_counter() - t0) / n_steps
         t1 = time.perf_counter()
         for _ in range(3):
@@ -143,14 +192,48 @@ def cpu_decode_sample(n_steps: int, warmup: int, threads: int, ctx: int = PROMPT
     tok_s = 1.0 / (32 * t_layer + t_head)
     sample = (f"{n_steps} decode steps of 1 of 32 layers at {ctx}-token context (7 masked fp16 F.linear, "
               f"quantize 1 + de-quantize {ctx} tokens x 8 kv heads, attention) + lm_head GEMV; "
-              f"tok/s = 1 / (32 x {t_layer * 1e3:.2f} ms + {t_head * 1e3:.2f} ms)")
-    return tok_s, sample, t_layer
+              f"tok/s = 1 / (32 x {t_layer * 1e3:.2f} ms + {t_head * 1e3:.2f} ms); arithmetic by "
+              + ("the reference's own SparsifyFn / TurboQuantMSE (copy under oracle/_ref)" if ref is not None
+                 else "the oracle restatement (no copy of the reference package on this machine)"))
+    return tok_s, sample, t_layer, kind
 
 
-def cpu_kernel_legs(threads: int) -> dict:
+def check_codes(codes: dict) -> dict:
+    """Checker for the TurboQuant codes the GPU kernels produced for one full config-3 sequence
+    (8 kv heads x 4096 tokens, K and V): every code against the fixed-order oracle (must be equal) and
+    against the reference-order torch quantize (may differ only where the rotated coordinate lies
+    within 4 ulp of a decision boundary: those are the near-ties, counted)."""
+    import numpy as np
+    import torch
+
+    from leankv_b200 import workloads
+    from oracle import tq_exact, turboquant as otq
+
+    kv = workloads.kv_case(device="cpu")
+    cb = otq.lloyd_max(128, 3)
+    bounds = torch.tensor(cb["boundaries"][1:-1], dtype=torch.float32)
+    out = {"coords": 0, "mismatches_vs_exact": 0, "near_ties_vs_reference": 0, "outside_band_vs_reference": 0,
+           "sample": "sequence 0 of config 3: 8 kv heads x 4096 tokens, K and V, pool append and bulk quantize"}
+    for name, x, seed in (("k", kv.k[0], 42), ("v", kv.v[0], 43)):
+        Pi = otq.rotation_matrix(128, seed)
+        ex, _, y, margin = tq_exact.quantize(x.float().numpy().reshape(-1, 128), Pi.numpy(), bounds.numpy())
+        ref = otq.quantize(x.float(), Pi, bounds, 3)[2].numpy().reshape(-1, 128)
+        for got in (codes[name + "_pool"], codes[name + "_bulk"]):
+            out["mismatches_vs_exact"] += int((got.reshape(-1, 128) != ex).sum())
+        got = codes[name + "_pool"].reshape(-1, 128)
+        diff = got != ref
+        band = margin[diff] <= 4 * np.spacing(np.abs(y[diff]).astype(np.float32))
+        out["coords"] += ex.size
+        out["near_ties_vs_reference"] += int(band.sum())
+        out["outside_band_vs_reference"] += int((~band).sum())
+    return out
+
+
+def cpu_kernel_legs(threads: int, codes=None) -> dict:
     """The reference's CPU path (oracle port) on configurations 1-3, on the host cores, bounded to a few
     seconds each: masked fp16 F.linear for the two GEMV configs; quantize + de-quantize + attention
-    over one of config 3's 16 sequences (scaled by 16 in the reported time)."""
+    over one of config 3's 16 sequences (scaled by 16 in the reported time). With ``codes`` (what the GPU
+    kernels wrote for that sequence) the same oracle also checks them."""
     import torch
 
     from leankv_b200 import workloads
@@ -195,6 +278,8 @@ def cpu_kernel_legs(threads: int) -> dict:
         out["tq_decode_attn_b16_t4096_us"] = 16e6 * t_attn
         out["sample"] = ("configs 1 and 2 in full (20 / 10 repetitions); config 3 on 1 of its 16 sequences "
                          "(8 kv heads x 4096 tokens), time x 16")
+        if codes is not None:
+            out["tq_codes"] = check_codes(codes)
     return out
 
 
@@ -204,12 +289,12 @@ def run_reference(args):
         return
     threads = os.cpu_count() or 1
     steps = max(1, min(args.steps, 64))
-    tok_s, sample, t_layer = cpu_decode_sample(steps, max(args.warmup, 1), threads)
+    tok_s, sample, t_layer, kind = cpu_decode_sample(steps, max(args.warmup, 1), threads)
     line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / tok_s,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": _config(args.gpus),
-            "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
+            "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": kind,
                              "sample": sample},
             "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -346,6 +431,27 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
     out["tq_bulk_quantize_append_b16_t4096"] = {"us": t_q * 1e6, "algorithmic_bytes": alg_q,
                                                 "gbs": alg_q / t_q / 1e9, "fp32_gflops": 2 * B * H * T * 2 * 128 * 128 / t_q / 1e9,
                                                 "bound": "fp32 FMA"}
+    # what the kernels wrote for sequence 0 (pool append, and the bulk quantize entry): compared code by code
+    # with the CPU oracle by the baseline leg
+    def nib(t):
+        t = t.cpu().numpy()
+        import numpy as np
+        return np.stack([t & 0xF, t >> 4], axis=-1).reshape(*t.shape[:-1], -1)
+
+    codes = {}
+    pages0 = kv.page_ids[0].contiguous()
+    for which, name, x, Pi in ((0, "k", kv.k[0], Pk), (1, "v", kv.v[0], Pv)):
+        idx = torch.empty(H, T, 64, dtype=torch.uint8, device=dev)
+        nrm = torch.empty(H, T, dtype=torch.float32, device=dev)
+        lib.leankv_tq_pool_unpack(pools[0].data_ptr(), kv.n_pages, H, pages0.data_ptr(), T, which, idx.data_ptr(),
+                                  nrm.data_ptr(), st)
+        codes[name + "_pool"] = nib(idx)
+        xc = x.contiguous()
+        lib.leankv_tq_quantize(xc.data_ptr(), 0, H * T, 128, 3, Pi.data_ptr(), bounds_d.data_ptr(), idx.data_ptr(),
+                               nrm.data_ptr(), st)
+        torch.cuda.synchronize()
+        codes[name + "_bulk"] = nib(idx)
+    out["_codes_for_checker"] = codes
     wsa = torch.zeros(lib.leankv_tq_decode_attn_workspace_bytes(B, 32, H, 256) + 256, dtype=torch.uint8, device=dev)
     o = torch.empty_like(kv.q)
     fn3 = lambda i: lib.leankv_tq_decode_attn(kv.q.data_ptr(), o.data_ptr(), B, 32, H, pools[i].data_ptr(),
@@ -363,11 +469,112 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
     fn4 = lambda i: lib.leankv_tq_decode_attn_rotated(q_rot.data_ptr(), o.data_ptr(), B, 32, H, pools[i].data_ptr(),
                                                       kv.n_pages, indptr.data_ptr(), flat.data_ptr(),
                                                       last.data_ptr(), 256, Pv.data_ptr(), cents_h.data_ptr(),
-                                                      1.0 / math.sqrt(128.0), wsa.data_ptr(), wsa.numel(), st)
+                                                      1.0 / math.sqrt(128.0), wsa.data_ptr(), wsa.numel(), 0, st)
     t4 = time_kernel(fn4, len(pools), iters)
     alg4 = alg + 2 * B * 32 * 128          # fp32 instead of fp16 query
     out["tq_decode_attn_rotated_b16_t4096"] = {"us": t4 * 1e6, "algorithmic_bytes": alg4, "gbs": alg4 / t4 / 1e9,
                                                "frac": alg4 / t4 / 1e9 / peak_gbs, "launches_timed": iters}
+
+
+# ── GPU comparators: the reference's own GPU code and a stock fp16 paged decode, outside the product path ──
+
+def comparator(name: str):
+    """Runs one comparator on cuda:0 and returns its timing dict. These are not part of the library:
+    ``triton_gemv`` JIT-compiles the reference's Triton kernel from the copy of its package under
+    oracle/_ref (config 1), ``reference_cache`` runs the reference's TurboQuantCache.update + SDPA on the
+    GPU at config 3's shape, ``flashinfer`` times FlashInfer's fp16 paged decode at config 3's shape."""
+    import math
+
+    import torch
+
+    from leankv_b200 import workloads
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if name == "triton_gemv":
+        from oracle import build_ref
+
+        build_ref.load()
+        from leankv.teal.kernels.sparse_gemv import prepare_weight_for_sparse_gemv, sparse_gemv
+
+        c = workloads.sparse_gemv_case(device=dev)
+        wts = [prepare_weight_for_sparse_gemv(c.weight.clone()) for _ in range(5)]     # 5 x 117 MB > L2
+        x = c.x.reshape(1, 1, -1).contiguous()
+        y = sparse_gemv(x, wts[0], c.threshold)                                        # autotune + compile
+        want = (c.weight.float() @ (c.x.float() * (c.x.abs() > c.threshold)).reshape(-1)).reshape(-1)
+        err = float((y.float().reshape(-1) - want).norm() / want.norm())
+        t = time_kernel(lambda i: sparse_gemv(x, wts[i], c.threshold), 5, 100)
+        alg = c.n_active * 4096 * 2 + 14336 * 2 + 4096 * 2
+        return {"us": t * 1e6, "gbs": alg / t / 1e9, "rel_l2_vs_fp32": err,
+                "what": "reference Triton _splitk_sparse_gemv_kernel (autotuned, zero-fill pre-hook included), config 1"}
+    kv = workloads.kv_case(device=dev)
+    B, H, T = 16, 8, 4096
+    if name == "reference_cache":
+        import torch.nn.functional as F
+
+        from oracle import build_ref
+
+        build_ref.load()
+        from leankv.turboquant.cache import TurboQuantCache
+
+        cache = TurboQuantCache(bits=3, head_dim=128, num_layers=1, hot_buffer_size=64, device=dev)
+        cache.update(kv.k, kv.v, 0)
+        q = kv.q.unsqueeze(2)
+        knew, vnew = kv.k[:, :, :1].contiguous(), kv.v[:, :, :1].contiguous()
+
+        def step(i):
+            K, V = cache.update(knew, vnew, 0)
+            return F.scaled_dot_product_attention(q, K, V, enable_gqa=True)
+
+        t = time_kernel(step, 1, 10, warmup=2)
+        return {"us": t * 1e6, "what": "reference TurboQuantCache.update (de-quantize the whole cold store) + SDPA "
+                                       "on the GPU, one decode step at config 3's shape"}
+    if name == "flashinfer":
+        import flashinfer
+
+        pages = kv.n_pages
+        cache = torch.empty(pages, 2, 16, H, 128, dtype=torch.float16, device=dev)
+        ids = kv.page_ids.long()
+        cache[ids.reshape(-1), 0] = kv.k.transpose(1, 2).reshape(B * 256, 16, H, 128)
+        cache[ids.reshape(-1), 1] = kv.v.transpose(1, 2).reshape(B * 256, 16, H, 128)
+        caches = [cache] + [cache.clone() for _ in range(1)]                              # 2 x 537 MB > L2
+        ws = torch.empty(128 << 20, dtype=torch.uint8, device=dev)
+        wrapper = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+        indptr = torch.arange(0, (B + 1) * 256, 256, dtype=torch.int32, device=dev)
+        last = torch.full((B,), 16, dtype=torch.int32, device=dev)
+        wrapper.plan(indptr, kv.page_ids.reshape(-1).contiguous(), last, 32, H, 128, 16, q_data_type=torch.float16,
+                     kv_data_type=torch.float16)
+        out = wrapper.run(kv.q, caches[0])
+        kf = kv.k.float().repeat_interleave(4, dim=1)
+        vf = kv.v.float().repeat_interleave(4, dim=1)
+        sc = torch.einsum("bhd,bhtd->bht", kv.q.float(), kf) / math.sqrt(128.0)
+        want = torch.einsum("bht,bhtd->bhd", torch.softmax(sc, dim=-1), vf)
+        err = float((out.float() - want).norm() / want.norm())
+        t = time_kernel(lambda i: wrapper.run(kv.q, caches[i]), len(caches), 50)
+        alg = 2 * B * H * T * 128 * 2
+        return {"us": t * 1e6, "gbs": alg / t / 1e9, "rel_l2_vs_fp32": err, "kv_bytes": alg,
+                "what": "FlashInfer BatchDecodeWithPagedKVCacheWrapper, fp16 pages, config 3's shape (5.1 x the bytes of the 3-bit pool)"}
+    raise ValueError(name)
+
+
+def run_comparators(names=("triton_gemv", "reference_cache", "flashinfer"), timeout_s: int = 240) -> dict:
+    """Each comparator in a child process of its own (own CUDA context, JIT compilation bounded by a
+    time limit); a failure or time-out is reported in place of the numbers."""
+    import subprocess
+
+    out = {}
+    for name in names:
+        try:
+            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--comparator", name],
+                               capture_output=True, text=True, timeout=timeout_s)
+            last = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+            out[name] = json.loads(last[-1]) if r.returncode == 0 and last else {
+                "unavailable": (r.stderr.strip().splitlines() or ["no output"])[-1][:300]}
+        except subprocess.TimeoutExpired:
+            out[name] = {"unavailable": f"did not finish within {timeout_s} s (JIT compilation)"}
+        except Exception as e:   # noqa: BLE001
+            out[name] = {"unavailable": repr(e)[:300]}
+    return out
 
 
 def exchange_leg(dev, world, rank, group, iters=200):
@@ -451,7 +658,7 @@ def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
     total, ctx = (BATCH_TOTAL, BATCH_CTX) if not small else (16, 256)
     mine = partition_batch(total, world, rank)
     B = len(mine)
-    eng = BatchDecodeEngine.random_init(cfg, dev, B, seed=0, max_seq_len=ctx + 2 * (W + K) + 32)
+    eng = BatchDecodeEngine.random_init(cfg, dev, B, seed=0, max_seq_len=ctx + 2 * (W + K) + 48)
     gen = torch.Generator().manual_seed(4321)
     prompts = torch.randint(0, cfg.vocab_size, (total, ctx), generator=gen)[mine.start:mine.stop]
 
@@ -472,6 +679,14 @@ def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
     torch.cuda.synchronize()
     prefill_s = reduce_max(time.perf_counter() - t0)
     eng.capture()
+    # the first steps of two of this rank's sequences, kept for the parity check below
+    n_par, par_steps = min(2, B), 4
+    par_tokens, par_logits = [], []
+    for _ in range(par_steps):
+        par_tokens.append(eng.tokens[:n_par].clone())
+        eng.graph.replay()
+        par_logits.append(eng.logits[:n_par].float().clone())
+    torch.cuda.synchronize()
     pin_in = torch.zeros(B, dtype=torch.int64).pin_memory()
     pin_out = torch.zeros(B, dtype=torch.int64).pin_memory()
 
@@ -499,8 +714,30 @@ def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
         return reduce_max(wall if host_io else e0.elapsed_time(e1) * 1e-3)
 
     sec = timed(False)
+    eng.check_status()
     sec_e2e = timed(True)
-    ctx_mid = ctx + W + K // 2
+    eng.check_status()
+    ctx_mid = ctx + par_steps + W + K // 2
+
+    # parity: the same sequences served alone by a 2-sequence engine on the same weights, teacher-forced on
+    # the batch's tokens (library GEMMs may pick another kernel at another batch size, so logits agree to
+    # rounding and an argmax near-tie may differ)
+    small_eng = BatchDecodeEngine(cfg, eng.w, dev, n_par, max_seq_len=ctx + par_steps + 32)
+    small_eng.prefill(prompts[:n_par])
+    errs, same = [], 0
+    for i in range(par_steps):
+        small_eng.tokens.copy_(par_tokens[i])
+        small_eng.step()
+        torch.cuda.synchronize()
+        got = small_eng.logits.float()
+        errs.append(float((par_logits[i] - got).norm() / got.norm()))
+        same += int((par_logits[i].argmax(-1) == got.argmax(-1)).sum())
+    small_eng.check_status()
+    parity = {"sequences": n_par, "steps": par_steps, "max_rel_l2": max(errs), "bound": 2e-2,
+              "argmax_equal": f"{same} of {n_par * par_steps}"}
+    del small_eng
+    if parity["max_rel_l2"] > parity["bound"]:
+        raise RuntimeError(f"batched decode does not match the same sequences served alone: {parity}")
 
     # the attention launch of one layer alone, rotating over the layers' pools (each larger than L2)
     st = torch.cuda.current_stream().cuda_stream
@@ -514,7 +751,7 @@ def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
                                           eng.pools[l].data_ptr(), eng.max_pages, eng.kv_indptr.data_ptr(),
                                           eng.kv_page_indices.data_ptr(), eng.kv_last.data_ptr(), eng.pps,
                                           eng.Pi_v[l].data_ptr(), eng.centroids_host.data_ptr(),
-                                          1.0 / math.sqrt(128.0), eng.ws_attn.data_ptr(), eng.ws_attn.numel(), st)
+                                          1.0 / math.sqrt(128.0), eng.ws_attn.data_ptr(), eng.ws_attn.numel(), 0, st)
     t_attn = time_kernel(attn, n_l, attn_iters)
     n_tok = int(eng.pos[0].item())
     alg_attn = 2 * B * eng.nkv * n_tok * 50 + B * eng.nq * 128 * (4 + 2) + 4 * (B * ((n_tok + 15) // 16) + 2 * B + 1)
@@ -528,6 +765,7 @@ def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
                                 "d2h_bytes_per_step": 8 * B},
         "kv_bytes_per_sequence": eng.kv_bytes_per_sequence(ctx),
         "kv_bytes_per_sequence_fp16": 2 * cfg.num_layers * cfg.num_kv_heads * 128 * 2 * ctx,
+        "parity_vs_sequences_served_alone": parity,
         "prefill_s": prefill_s, "gpu_launches": eng.launches_per_step * K, "library_gemms": eng.gemms_per_step * K,
         "bytes_per_step_per_gpu": {"weights": weight_bytes, "kv": kv_step},
         "step_gbs_per_gpu": (weight_bytes + kv_step) / (sec / K) / 1e9,
@@ -536,6 +774,69 @@ def batched_decode_leg(dev, world, rank, K, W, small=False, attn_iters=20):
     }
     del eng
     torch.cuda.empty_cache()
+    return out
+
+
+# ── what the timed decode steps computed ──────────────────────────────────────────────────────
+
+def decode_parity(eng, prompt, cfg, dev, world, rank, group, history, tp_steps: int = 8):
+    """Checks on the results of the configuration that is being timed, at its full shape.
+
+    * every N: logits of the first decode step (sparse GEMVs, append, paged attention) against the dense
+      library-GEMM prompt pass of the same weights extended by that one token (rel-L2);
+    * N > 1: (a) every rank's token history of the timed run is identical; (b) on rank 0 a single-GPU
+      engine with the same seeded weights and thresholds is teacher-forced on the tensor-parallel run's
+      tokens for ``tp_steps`` steps and the logits are compared step by step (rel-L2, bound 2e-2: fp16
+      partial sums in another order, threshold near-ties)."""
+    import torch
+    import torch.distributed as dist
+
+    from leankv_b200.engine import DecodeEngine
+
+    def rel(a, b):
+        a, b = a.double().flatten(), b.double().flatten()
+        return float((a - b).norm() / b.norm())
+
+    out = {}
+    first = eng.prefill(prompt)
+    tp_tokens, tp_logits = [], []
+    for i in range(tp_steps):
+        tp_tokens.append(int(eng.token.item()))
+        eng.step()
+        torch.cuda.synchronize()
+        tp_logits.append(eng.logits.float().clone())
+    eng.check_status()
+    with torch.no_grad():
+        ids = torch.tensor(list(prompt) + [first], device=dev)
+        x = eng._dense_forward(ids, write_cache=False)
+        want = (x @ eng.w["lm_head_t"]).float()
+    out["first_step_vs_dense_prompt_pass_rel_l2"] = rel(tp_logits[0], want)
+    if world > 1:
+        gathered = [torch.empty_like(history) for _ in range(world)]
+        dist.all_gather(gathered, history, group=group)
+        identical = all(torch.equal(gathered[0], g) for g in gathered[1:])
+        tp = {"ranks_identical": bool(identical), "tokens_compared": int(history.numel()),
+              "timed_out": False, "steps": tp_steps, "bound": 2e-2}
+        if rank == 0:
+            single = DecodeEngine.random_init(cfg, dev, seed=0, max_seq_len=eng.max_seq_len)
+            single.set_thresholds({l: dict(t) for l, t in enumerate(eng.thresholds)})
+            single.prefill(prompt)
+            errs = []
+            for i in range(tp_steps):
+                single.token.fill_(tp_tokens[i])
+                single.step()
+                torch.cuda.synchronize()
+                errs.append(rel(tp_logits[i], single.logits.float()))
+            single.check_status()
+            tp["per_step_rel_l2"] = errs
+            tp["max_rel_l2"] = max(errs)
+            tp["first_token_equal"] = bool(int(single.history[0].item()) == first)
+            del single
+            torch.cuda.empty_cache()
+        dist.barrier(group=group)
+        out["tp"] = tp
+        if rank == 0 and (not identical or tp["max_rel_l2"] > tp["bound"]):
+            raise RuntimeError(f"tensor-parallel results do not match the single-GPU engine: {tp}")
     return out
 
 
@@ -620,8 +921,10 @@ def run_ours(args):
         return sec, sampler.summary()
 
     sec, clocks = timed_steps(host_io=False)
+    eng.check_status()          # a failed wait inside a kernel would make the steps fast and wrong: stop here
     streamed = eng.bytes_streamed()
     launches = eng.launches_per_step * K
+    history = eng.history[:1 + W + K].clone()
     if args.quick:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": K / sec, "unit": "tok/s", "n_gpus": world, "steps": K,
@@ -631,11 +934,14 @@ def run_ours(args):
             dist.destroy_process_group()
         return
     sec_e2e, _ = timed_steps(host_io=True)
+    eng.check_status()
+    parity = decode_parity(eng, prompt, cfg, dev, world, rank, group, history)
 
     # the same engine with TEAL off (every weight column streamed): the dense-fp16 comparison point
     sparse_thresholds = [dict(t) for t in eng.thresholds]
     eng.set_thresholds(None)
     sec_dense, _ = timed_steps(host_io=False)
+    eng.check_status()
     dense_streamed = eng.bytes_streamed()
     eng.set_thresholds({l: t for l, t in enumerate(sparse_thresholds)})
 
@@ -665,8 +971,11 @@ def run_ours(args):
                  "launches_per_step": launches_per_step,
                  "dense_same_engine_tok_s": K / sec_dense,
                  "dense_weight_bytes_per_step_per_gpu": dense_streamed / K,
-                 "speedup_vs_dense_same_engine": sec_dense / sec},
+                 "speedup_vs_dense_same_engine": sec_dense / sec,
+                 "parity_rel_l2": parity["first_step_vs_dense_prompt_pass_rel_l2"]},
     }
+    if world > 1:
+        line["tp_parity"] = parity["tp"]
     if exchange is not None:
         line["tp_exchange"] = exchange
     if batched is not None:
@@ -675,19 +984,25 @@ def run_ours(args):
         line["batched_decode"] = batched
     if world == 1 and not args.small:
         legs = kernel_legs(dev, peak_gbs)
+        codes_for_checker = legs.pop("_codes_for_checker", None)
         g = legs["sparse_gemv_4096x14336"]
         line["roofline"] = {"bound": "hbm", "kernel": "sparse_gemv_kernel<false> (config 1: 4096 x 14336, 40 % sparse)",
                             "achieved": g["gbs"], "peak": peak_gbs, "unit": "GB/s", "frac": g["frac"],
-                            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this same leg
-                            # (ncu capture summarised in profiles/sparse_gemv_config1.md)
-                            "traffic": GEMV_CONFIG1_DRAM_BYTES, "peak_source": peak_src,
+                            "traffic": _captured_traffic("sparse_gemv_config1")[0],
+                            "traffic_source": _captured_traffic("sparse_gemv_config1")[1], "peak_source": peak_src,
                             "algorithmic_bytes_per_launch": g["algorithmic_bytes"], "us_per_launch": g["us"]}
         line["kernels"] = legs
+        if not args.no_comparators:
+            torch.cuda.empty_cache()
+            line["gpu_comparators"] = run_comparators()
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            tok_s, sample, _ = cpu_decode_sample(8, 2, threads)
-            line["cpu_baseline"] = {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
-                                    "sample": sample, "kernels": cpu_kernel_legs(threads)}
+            tok_s, sample, _, kind = cpu_decode_sample(8, 2, threads)
+            cpu_legs = cpu_kernel_legs(threads, codes_for_checker)
+            if "tq_codes" in cpu_legs:
+                legs["tq_codes"] = cpu_legs.pop("tq_codes")
+            line["cpu_baseline"] = {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": kind,
+                                    "sample": sample, "kernels": cpu_legs}
     else:
         line["roofline"] = {"bound": "hbm", "kernel": "whole decode step (all kernels)", "achieved": line["step"]["gbs_per_gpu"],
                             "peak": peak_gbs, "unit": "GB/s", "frac": line["step"]["frac_of_peak"], "traffic": None,
@@ -752,6 +1067,11 @@ def main():
     ap.add_argument("--only-legs", default="",
                     help="comma list of gemv,swiglu,attn: run just those kernel legs and print their JSON")
     ap.add_argument("--leg-iters", type=int, default=200)
+    ap.add_argument("--check-codes", action="store_true",
+                    help="with --only-legs attn: also run the CPU oracle's code-by-code check of the pool")
+    ap.add_argument("--comparator", default="", help="run one GPU comparator (triton_gemv, reference_cache, "
+                                                     "flashinfer) and print its JSON")
+    ap.add_argument("--no-comparators", action="store_true", help="skip the GPU comparator legs of the default run")
     ap.add_argument("--only-exchange", action="store_true",
                     help="under torchrun: time the GEMV + all-reduce leg alone and print its JSON")
     ap.add_argument("--workload", choices=["decode", "batched"], default="decode",
@@ -765,6 +1085,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.comparator:
+        print(json.dumps(comparator(args.comparator)))
     elif args.only_exchange:
         import datetime
 
@@ -788,8 +1110,11 @@ def main():
 
         _native.lib()
         torch.cuda.set_device(0)
-        print(json.dumps(kernel_legs(torch.device("cuda", 0), _peaks()[0], tuple(args.only_legs.split(",")),
-                                     args.leg_iters)))
+        legs = kernel_legs(torch.device("cuda", 0), _peaks()[0], tuple(args.only_legs.split(",")), args.leg_iters)
+        codes = legs.pop("_codes_for_checker", None)
+        if codes is not None and args.check_codes:
+            legs["tq_codes"] = check_codes(codes)
+        print(json.dumps(legs))
     else:
         run_ours(args)
 

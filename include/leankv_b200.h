@@ -82,8 +82,9 @@ int leankv_sparse_gemv_seg_f16(const void* Wt, const void* x, void* y, int N, in
 /* The two kernels above with the block's RMSNorm fused in front (no reference counterpart: HF runs
  * MistralRMSNorm as separate ops before the patched projections): h is the un-normalised row and
  *   x[z] = norm_weight[z] * fp16( h[z] * rsqrt(mean(h^2) + eps) )
- * is formed on the fly by every CTA (Z % 8 == 0, h 16-byte aligned). With residual == y == h the
- * GEMV updates the residual stream in place (each output element is read and written by one thread). */
+ * is formed on the fly by every CTA (Z % 8 == 0, h 16-byte aligned). Every CTA reads all of h while
+ * others may already be writing y, so y must not overlap h (LEANKV_EINVAL otherwise); residual may
+ * equal y (each output element is read and written by one thread). */
 int leankv_sparse_gemv_rmsnorm_f16(const void* Wt, const void* h, const void* norm_weight, float eps,
                                    void* y, int N, int Z, const leankv_segments_t* segs /* host */,
                                    const void* residual, void* workspace, size_t workspace_bytes,
@@ -184,9 +185,9 @@ int leankv_tq_pool_unpack(const void* pool, int n_pages, int n_kv_heads,
  * cache.py:169-189 would materialise; they are never formed: the query is rotated once,
  * scores and the value sum are taken in rotated space on tensor cores, and the output is
  * rotated back once. q, out: fp16 [B][n_q_heads][128]. n_q_heads / n_kv_heads must be 4
- * (GQA-4) in this version. kv_last_page_len[b] in 1..16; a sequence with
- * kv_indptr[b+1] == kv_indptr[b] yields zeros. max_pages_per_seq bounds the split-KV
- * grid (host value, >= the longest sequence's page count). centroids is read on the
+ * (GQA-4) in this version. kv_indptr is a prefix sum (non-decreasing); kv_last_page_len[b] in
+ * 1..16; a sequence with kv_indptr[b+1] == kv_indptr[b] yields zeros. max_pages_per_seq sizes
+ * the grid and the workspace (host value, >= the longest sequence's page count). centroids is read on the
  * host (the codebook is a compile-time-like constant of the cache): it is turned into
  * register look-up tables that travel as kernel arguments. The first 4 bytes of the
  * workspace are a status word (see leankv_tq_decode_attn_status). */
@@ -203,18 +204,21 @@ int leankv_tq_decode_attn(const void* q, void* out, int B, int n_q_heads, int n_
 /* Same attention for a caller that already holds the rotated query q_rot = Pi_k q
  * (fp32 [B][n_q_heads][128], e.g. from leankv_decode_qkv_post): skips the query-rotation
  * launch. Everything else as leankv_tq_decode_attn.
- * Stream-ordering note: the kernel starts fetching the page table and every page except each
- * sequence's last one while the launch queued directly before it may still be running (programmatic
- * dependent launch). That launch may therefore write only q_rot and the last page of each sequence,
- * which is what leankv_decode_qkv_post / leankv_batch_qkv_post do; a multi-page
- * leankv_tq_pool_append must not be the launch directly before this call (leankv_tq_decode_attn
- * is safe after it: its query-rotation launch sits in between). */
+ * flags: 0, or LEANKV_ATTN_EARLY_FETCH. With the flag the kernel starts reading the page table
+ * and fetching every page except each sequence's last one while the launch queued directly
+ * before it may still be running (programmatic dependent launch); q_rot and the last pages are
+ * read only after that launch has completed. The flag is therefore only correct when the
+ * preceding launch writes nothing but q_rot and the last page of each sequence, which is what
+ * leankv_decode_qkv_post / leankv_batch_qkv_post do (the decode loops pass the flag). Without
+ * it the call has plain stream-order semantics after any launch, e.g. a multi-page
+ * leankv_tq_pool_append. */
+#define LEANKV_ATTN_EARLY_FETCH 1
 int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int B, int n_q_heads, int n_kv_heads,
                                   const void* pool, int n_pages,
                                   const int32_t* kv_indptr, const int32_t* kv_page_indices,
                                   const int32_t* kv_last_page_len, int max_pages_per_seq,
                                   const float* Pi_v, const float* centroids /* host, 8 */, float scale,
-                                  void* workspace, size_t workspace_bytes, void* stream);
+                                  void* workspace, size_t workspace_bytes, int flags, void* stream);
 
 /* Device status word of the bounded waits inside the attention kernel (0 = no wait
  * ever gave up). Copied to *status with a synchronous 4-byte copy from `workspace`. */

@@ -18,6 +18,7 @@ MAX_SEGMENTS = 4
 TQ_PAGE_TOKENS = 16
 TQ_DIM = 128
 TQ_CHUNK_BYTES = 800
+ATTN_EARLY_FETCH = 1
 
 
 class Segments(Structure):
@@ -84,7 +85,7 @@ SIGNATURES = {
                                       c_void_p, c_float, c_void_p, c_size_t, c_void_p]),
     "leankv_tq_decode_attn_rotated": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                              c_float, c_void_p, c_size_t, c_void_p]),
+                                              c_float, c_void_p, c_size_t, c_int, c_void_p]),
     "leankv_decode_qkv_post": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "leankv_tq_decode_attn_status": (c_int, [c_void_p, POINTER(c_int)]),

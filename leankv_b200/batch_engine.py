@@ -38,6 +38,7 @@ class BatchDecodeEngine(DecodeEngine):
 
         self.cfg, self.dev = cfg, torch.device(device)
         self.tp_rank, self.tp_size, self.group = 0, 1, None
+        self.xchg = None
         self.lib = _native.lib()
         self.nq, self.nkv, self.inter = cfg.num_q_heads, cfg.num_kv_heads, cfg.intermediate_size
         self.n_qkv = (self.nq + 2 * self.nkv) * 128
@@ -128,7 +129,8 @@ class BatchDecodeEngine(DecodeEngine):
                 self.q_rot.data_ptr(), self.attn.data_ptr(), B, self.nq, self.nkv, self.pools[l].data_ptr(),
                 self.max_pages, self.kv_indptr.data_ptr(), self.kv_page_indices.data_ptr(),
                 self.kv_last.data_ptr(), self.pps, self.Pi_v[l].data_ptr(), self.centroids_host.data_ptr(),
-                1.0 / math.sqrt(128.0), self.ws_attn.data_ptr(), self.ws_attn.numel(), st()), "decode_attn_rotated")
+                1.0 / math.sqrt(128.0), self.ws_attn.data_ptr(), self.ws_attn.numel(), _native.ATTN_EARLY_FETCH,
+                st()), "decode_attn_rotated")
             self.launches_per_step += 2
             self._mm(self.attn, lw["wo_t"], self.o)
             self._norm_rows(self.o, lw["ln2"])                       # h += o ; x = norm(h)
@@ -201,6 +203,7 @@ class BatchDecodeEngine(DecodeEngine):
         with torch.cuda.device(self.dev):
             for _ in range(n_steps):
                 self.step()
+            self.check_status()
         return self.history[:, :1 + n_steps].clone()
 
     def kv_bytes_per_sequence(self, n_tokens: int) -> int:

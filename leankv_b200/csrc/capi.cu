@@ -57,7 +57,7 @@ extern "C" const char* leankv_strerror(int code) {
     }
 }
 
-extern "C" int leankv_abi_version(void) { return 1; }
+extern "C" int leankv_abi_version(void) { return 2; }
 
 extern "C" const char* leankv_last_cuda_error(void) { return leankv::g_last_cuda_error; }
 

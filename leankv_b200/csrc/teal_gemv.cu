@@ -439,9 +439,14 @@ int check_common(const void* Wt, const void* x, const void* y, int N, int Z) {
     return LEANKV_OK;
 }
 
-int check_norm(const void* x, const void* norm_w, int Z) {
+// With the RMSNorm fused in, every CTA reads the whole input row for the norm while the finishing CTAs
+// of other column slices are already writing y: the output must not overlap the input row.
+int check_norm(const void* x, const void* norm_w, int Z, const void* y, int N) {
     if (norm_w == nullptr) return LEANKV_OK;
     if (Z % 8 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(norm_w) & 1u) != 0) return LEANKV_EALIGN;
+    const uintptr_t x0 = reinterpret_cast<uintptr_t>(x), x1 = x0 + 2 * (uintptr_t)Z;
+    const uintptr_t y0 = reinterpret_cast<uintptr_t>(y), y1 = y0 + 2 * (uintptr_t)N;
+    if (y0 < x1 && x0 < y1) return LEANKV_EINVAL;
     return LEANKV_OK;
 }
 
@@ -451,7 +456,7 @@ int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const lean
                 const leankv_xchg_t* xchg = nullptr, int slot = 0) {
     int rc = check_common(Wt, x, y, N, Z);
     if (rc != LEANKV_OK) return rc;
-    rc = check_norm(x, norm_w, Z);
+    rc = check_norm(x, norm_w, Z, y, N);
     if (rc != LEANKV_OK) return rc;
     if (segs == nullptr || segs->n_segments < 1 || segs->n_segments > LEANKV_MAX_SEGMENTS)
         return LEANKV_EINVAL;
@@ -588,7 +593,7 @@ static int launch_swiglu(const void* Wt_gate, const void* Wt_up, const void* x, 
                          unsigned long long* active_elems, void* stream, const void* norm_w, float norm_eps) {
     int rc = check_common(Wt_gate, x, y, N, Z);
     if (rc != LEANKV_OK) return rc;
-    rc = check_norm(x, norm_w, Z);
+    rc = check_norm(x, norm_w, Z, y, N);
     if (rc != LEANKV_OK) return rc;
     if (Wt_up == nullptr) return LEANKV_EINVAL;
     if (!aligned16(Wt_up)) return LEANKV_EALIGN;
@@ -672,6 +677,8 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 // Device address of g_static_scratch per device ordinal. In host code the symbol's name is only a
 // handle for the runtime, never a pointer a kernel could use; the address has to be asked for.
+// The table is filled without a lock: threads that race on a device's first call all store the same
+// address (a pointer-sized store), so the worst case is a repeated look-up.
 constexpr int kStaticMaxDevices = 64;
 void* g_static_scratch_addr[kStaticMaxDevices] = {nullptr};
 

@@ -11,20 +11,28 @@
 //
 // One warp owns one page (16 tokens) at a time. Its K and V chunks (800 bytes each) are
 // brought into a per-warp shared-memory ring by bulk async copies that complete on an
-// mbarrier. Codes become fp16 MMA operands with byte-permute look-ups: the eight
-// centroids, scaled by a factor alpha chosen so that all of them are (almost) exactly
-// representable in fp16, live in four registers used as 8-entry byte tables. Scores
-// (16 tokens x 4 query heads) and the value sum (128 coordinates x 4 heads) are
-// m16n8k16 tensor-core MMAs whose eight N columns carry the four GQA heads: as fp16
-// hi/lo pairs of the query for the scores (so query rounding does not limit accuracy),
-// and as single fp16 probabilities (lo columns zero) for the value sum, where rounding
-// is independent from token to token and averages out.
+// mbarrier. Codes become tensor-core operands with byte-permute look-ups in 8-entry byte
+// tables held in registers (one look-up yields four codes' bytes).
+//  * Scores are integer MMAs (m16n8k32, s8): the centroids and the rotated query are 16-bit
+//    fixed-point numbers split into a high and a low signed byte. The MMA's K dimension
+//    carries 16 coordinates x {high, low} centroid byte, its rows the four GQA heads twice
+//    (high x high, and high x low + low x high), its columns eight tokens; the low x low term
+//    (2^-16 relative) is dropped. Integer sums are exact, so the only rounding on the key side is
+//    the 16-bit representation of the query (per head, relative to its largest coordinate) and of
+//    the centroids.
+//  * The value sum is an fp16 MMA (m16n8k16): rows = coordinates, K = tokens, columns = heads.
+//    The centroids enter scaled by a factor alpha chosen so that all eight are (almost) exactly
+//    representable in fp16; probabilities times value norms are rounded to fp16, which is
+//    independent from token to token and averages out over the sum. The score MMA's output
+//    layout (heads in rows, tokens in columns) is exactly the value MMA's B operand layout, so
+//    probabilities never move between lanes.
 //
-// Split-KV: a CTA (4 warps) covers a range of pages; CTA partials are merged, in chunk
-// order, by the last CTA to arrive for a (sequence, kv head), which also applies the
-// inverse value rotation.
+// Work is split over one wave of CTAs as equal shares of the flat list of all pages (see
+// tq_attn_kernel.cuh); partial results of a (sequence, kv head) pair are merged, in CTA order, by
+// the last CTA to arrive for it, which also applies the inverse value rotation.
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -39,7 +47,18 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kStages = 4;
 constexpr int kGroup = 4;                     // query heads per kv head
 constexpr int kPartialFloats = kGroup * kDim + 2 * kGroup;
-constexpr int kMaxChunks = 128;
+// Resident CTAs per SM: 5 (96 registers per thread, a few spilled bytes) by default; LEANKV_ATTN_OCC=4
+// selects the 128-register build of the same kernel.
+int attn_occupancy() {
+    static int occ = 0;
+    if (occ == 0) {
+        const char* e = std::getenv("LEANKV_ATTN_OCC");
+        occ = (e != nullptr && e[0] == '4') ? 4 : 5;
+    }
+    return occ;
+}
+constexpr int kMinPagesPerCta = 4;            // short inputs use fewer CTAs rather than sub-page shares
+constexpr float kFixedMax = 32512.0f;         // largest |value| of the 16-bit fixed-point operands (127 * 256)
 constexpr int kSpinLimit = 1 << 20;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -49,15 +68,17 @@ constexpr int kStatusBadPage = 2;
 
 struct AttnParams {
     const float* qprime;      // [B][Hq][128] rotated query Pi_k q
-    float qscale;             // softmax scale * log2(e) / alpha, applied when the query fragments are built
+    float qscale;             // softmax scale * log2(e)
     __half* out;              // [B][Hq][128]
     const uint8_t* pool;
     int n_pages, H, B;
     const int32_t* indptr;
     const int32_t* indices;
     const int32_t* last_len;
-    int pages_per_cta, n_chunks;
+    int flags;
     const float* Pi_v;
+    uint32_t kh0, kh1, kl0, kl1;   // byte tables: high / low signed byte of round(c[0..7] / c_unit)
+    float c_unit;                  // centroid value of one fixed-point unit
     uint32_t tl0, tl1, th0, th1;   // byte tables: low / high bytes of fp16(alpha * c[0..7])
     float inv_alpha;
     float* partials;
@@ -108,14 +129,18 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
-}
-// fp16 "hi" part of x, or the fp16 remainder x - hi ("lo" part).
-__device__ __forceinline__ float split_part(float x, int part) {
-    const float hi = __half2float(__float2half_rn(x));
-    return part ? x - hi : hi;
 }
 
 struct Unit {
@@ -163,7 +188,7 @@ __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const flo
 
 // ---- host side ---------------------------------------------------------------
 struct AttnPlan {
-    int pages_per_cta, n_chunks;
+    int n_ctas;
     size_t off_counters, off_qprime, off_partials, total;
 };
 
@@ -171,33 +196,17 @@ AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     AttnPlan pl;
     if (max_pages < 1) max_pages = 1;
     const long long pairs = (long long)B * Hkv;
-    // Chunks per (sequence, kv head). A warp tracks at most 32 pages, which sets the minimum. When the
-    // whole grid fits on the GPU at once (6 CTAs per SM) use as many chunks as still fit, so that no
-    // SM idles waiting for a second round. Otherwise pick, among the next few chunk counts, the one
-    // whose last round of CTAs is fullest.
-    const long long slots = (long long)sm_count() * 6;
-    const long long np = pairs > 0 ? pairs : 1;
-    const long long nc_min = (max_pages + 32 * kAttnWarps - 1) / (32 * kAttnWarps);
-    long long nc = slots / np;
-    if (nc < nc_min) {
-        double best = -1.0;
-        for (long long c = nc_min; c < nc_min + 8 && c <= kMaxChunks; ++c) {
-            const long long ctas = np * c, rounds = (ctas + slots - 1) / slots;
-            const double eff = (double)ctas / (double)(rounds * slots);
-            if (eff > best + 0.02) { best = eff; nc = c; }
-        }
-    }
-    if (nc < 1) nc = 1;
-    long long ppw = (max_pages + nc * kAttnWarps - 1) / (nc * kAttnWarps);
-    if (ppw < 1) ppw = 1;
-    while ((max_pages + ppw * kAttnWarps - 1) / (ppw * kAttnWarps) > kMaxChunks) ++ppw;
-    pl.pages_per_cta = (int)(ppw * kAttnWarps);
-    pl.n_chunks = (max_pages + pl.pages_per_cta - 1) / pl.pages_per_cta;
+    // One wave of resident CTAs; inputs too short to give every CTA kMinPagesPerCta pages get fewer
+    // (the kernel applies the same rule to the page count it finds on the device).
+    const long long slots = (long long)sm_count() * attn_occupancy();
+    long long want = (pairs * max_pages + kMinPagesPerCta - 1) / kMinPagesPerCta;
+    if (want < 1) want = 1;
+    pl.n_ctas = (int)(want < slots ? want : slots);
     pl.off_counters = 256;
     pl.off_qprime = pl.off_counters + round_up(sizeof(int) * (size_t)pairs, 256);
     pl.off_partials = pl.off_qprime + round_up(sizeof(float) * (size_t)B * Hq * kDim, 256);
-    pl.total = pl.off_partials +
-               (pl.n_chunks > 1 ? sizeof(float) * (size_t)pairs * pl.n_chunks * kPartialFloats : 0);
+    // two partial results per CTA: the pair its share starts inside and the pair it ends inside
+    pl.total = pl.off_partials + sizeof(float) * (size_t)pl.n_ctas * 2 * kPartialFloats;
     return pl;
 }
 
@@ -218,6 +227,8 @@ struct Lut {
     float centroids[8];
     uint32_t tl0, tl1, th0, th1;
     float alpha;
+    uint32_t kh0, kh1, kl0, kl1;
+    float c_unit;
     bool valid;
 };
 
@@ -250,6 +261,20 @@ void build_lut(const float* c, Lut* lut) {
     std::memcpy(lut->centroids, c, sizeof(float) * 8);
     lut->tl0 = lo[0]; lut->tl1 = lo[1]; lut->th0 = hi[0]; lut->th1 = hi[1];
     lut->alpha = best_alpha;
+    // key side: 16-bit fixed point, split into a balanced low byte in [-128, 127] and a high byte
+    float cmax = 0.f;
+    for (int k = 0; k < 8; ++k) cmax = std::fmax(cmax, std::fabs(c[k]));
+    const float unit = cmax > 0.f ? cmax / kFixedMax : 1.0f;
+    uint32_t kh[2] = {0, 0}, kl[2] = {0, 0};
+    for (int k = 0; k < 8; ++k) {
+        const int ci = (int)std::lrintf(c[k] / unit);
+        const int l8 = ((ci + 128) & 255) - 128;
+        const int h8 = (ci - l8) / 256;
+        kh[k >> 2] |= (uint32_t)(h8 & 255) << (8 * (k & 3));
+        kl[k >> 2] |= (uint32_t)(l8 & 255) << (8 * (k & 3));
+    }
+    lut->kh0 = kh[0]; lut->kh1 = kh[1]; lut->kl0 = kl[0]; lut->kl1 = kl[1];
+    lut->c_unit = unit;
     lut->valid = true;
 }
 
@@ -275,7 +300,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
                        const void* pool, int n_pages, const int32_t* kv_indptr,
                        const int32_t* kv_page_indices, const int32_t* kv_last_page_len,
                        int max_pages_per_seq, const float* Pi_k, const float* Pi_v, const float* centroids,
-                       float scale, void* workspace, size_t workspace_bytes, void* stream) {
+                       float scale, void* workspace, size_t workspace_bytes, int flags, void* stream) {
     if (B < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_pages <= 0 || max_pages_per_seq < 0)
         return LEANKV_EINVAL;
     if (B == 0) return LEANKV_OK;
@@ -287,8 +312,8 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
         (q && !aligned16(Pi_k)) || !aligned16(Pi_v) || !aligned16(workspace))
         return LEANKV_EALIGN;
     if (B > 65535 || n_kv_heads > 65535) return LEANKV_ELIMIT;
+    if ((flags & ~LEANKV_ATTN_EARLY_FETCH) != 0) return LEANKV_EINVAL;
     const AttnPlan pl = make_plan(B, n_q_heads, n_kv_heads, max_pages_per_seq);
-    if (pl.pages_per_cta > 32 * kAttnWarps) return LEANKV_ELIMIT;   // a warp tracks at most 32 pages
     if (workspace_bytes < pl.total) return LEANKV_EWORKSPACE;
     const Lut& lut = get_lut(centroids);
 
@@ -304,7 +329,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
 
     AttnParams p{};
     p.qprime = qprime;
-    p.qscale = scale * kLog2e / lut.alpha;
+    p.qscale = scale * kLog2e;
     p.out = static_cast<__half*>(out);
     p.pool = static_cast<const uint8_t*>(pool);
     p.n_pages = n_pages;
@@ -313,16 +338,19 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.indptr = kv_indptr;
     p.indices = kv_page_indices;
     p.last_len = kv_last_page_len;
-    p.pages_per_cta = pl.pages_per_cta;
-    p.n_chunks = pl.n_chunks;
+    p.flags = flags;
     p.Pi_v = Pi_v;
+    p.kh0 = lut.kh0; p.kh1 = lut.kh1; p.kl0 = lut.kl0; p.kl1 = lut.kl1;
+    p.c_unit = lut.c_unit;
     p.tl0 = lut.tl0; p.tl1 = lut.tl1; p.th0 = lut.th0; p.th1 = lut.th1;
     p.inv_alpha = 1.0f / lut.alpha;
     p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
-    dim3 grid(pl.n_chunks, n_kv_heads, B);
-    LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel, grid, dim3(kAttnThreads), 0, st, p));
+    if (attn_occupancy() == 4)
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
+    else
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     return LEANKV_OK;
 }
 
@@ -335,7 +363,7 @@ extern "C" int leankv_tq_decode_attn(const void* q, void* out, int B, int n_q_he
     if (!q) return LEANKV_EINVAL;
     return attn_launch(q, nullptr, out, B, n_q_heads, n_kv_heads, pool, n_pages, kv_indptr, kv_page_indices,
                        kv_last_page_len, max_pages_per_seq, Pi_k, Pi_v, centroids, scale, workspace,
-                       workspace_bytes, stream);
+                       workspace_bytes, 0, stream);
 }
 
 extern "C" int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int B, int n_q_heads,
@@ -343,11 +371,12 @@ extern "C" int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int 
                                              const int32_t* kv_indptr, const int32_t* kv_page_indices,
                                              const int32_t* kv_last_page_len, int max_pages_per_seq,
                                              const float* Pi_v, const float* centroids, float scale,
-                                             void* workspace, size_t workspace_bytes, void* stream) {
+                                             void* workspace, size_t workspace_bytes, int flags,
+                                             void* stream) {
     if (!q_rot) return LEANKV_EINVAL;
     return attn_launch(nullptr, q_rot, out, B, n_q_heads, n_kv_heads, pool, n_pages, kv_indptr,
                        kv_page_indices, kv_last_page_len, max_pages_per_seq, nullptr, Pi_v, centroids, scale,
-                       workspace, workspace_bytes, stream);
+                       workspace, workspace_bytes, flags, stream);
 }
 
 extern "C" int leankv_tq_decode_attn_status(const void* workspace, int* status) {

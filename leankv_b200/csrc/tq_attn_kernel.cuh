@@ -1,9 +1,13 @@
 // Main kernel of the paged TurboQuant decode attention (included by tq_attn.cu, inside
 // namespace leankv::{anonymous}; see the header comment there for the algorithm).
 //
-// Grid (chunk, kv head, sequence); a CTA of 4 warps covers `pages_per_cta` consecutive pages
-// of one (sequence, kv head); warp w takes a contiguous quarter of them, one page (16 tokens)
-// per iteration.
+// Work split. All pages of all (sequence, kv head) pairs form one flat list, ordered by sequence,
+// then kv head, then page. The grid is one wave of resident CTAs and CTA c takes the c-th equal
+// share of that list (shares differ by at most one page), whatever the sequence lengths are. A
+// share is cut at pair boundaries into segments; the CTA's four warps split each segment's pages,
+// their results are merged in shared memory, and a segment that is not a whole pair leaves a
+// partial result in the workspace. The last CTA to arrive for a pair merges the partials in CTA
+// order and applies the inverse value rotation.
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -16,57 +20,35 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // are taken relative to the (stale) reference and stay below 2^kRescaleSlack.
 constexpr float kRescaleSlack = 5.0f;
 
-__global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const AttnParams p) {
-    // per-warp ring of kStages x (K chunk + V chunk); after its last page a warp reuses its ring
-    // for its partial result, and the CTA reuses warp 0's ring for the merged output
+// Integer MMA accumulators start from the bit pattern of 1.5 * 2^23: adding an integer |n| < 2^22 to
+// that pattern gives the bit pattern of the float 1.5 * 2^23 + n, so the sums come out of the tensor
+// core as floats without a conversion instruction.
+constexpr int kBiasBits = 0x4B400000;
+constexpr float kBiasF = 12582912.0f;
+
+template <int kOcc>   // resident CTAs per SM the register allocation is held to
+__global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(const AttnParams p) {
+    // per-warp ring of kStages x (K chunk + V chunk)
     __shared__ __align__(128) uint8_t s_ring[kAttnWarps][kStages][2][kChunkBytes];
     __shared__ __align__(8) uint64_t s_bar[kAttnWarps][kStages];
+    __shared__ __align__(16) float s_res[kAttnWarps][kGroup][kDim];   // warp results, later scratch of the merge
     __shared__ float s_m[kAttnWarps][kGroup], s_l[kAttnWarps][kGroup];
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int H = p.H, Hq = H * kGroup;
+    const bool early = (p.flags & LEANKV_ATTN_EARLY_FETCH) != 0;
+    bool waited = false;
+    if (!early) {
+        pdl_begin();
+        waited = true;
+    }
     // Pull the inverse rotation (a constant, 64 KB) towards L2 early: whichever CTA ends up merging
-    // the chunks needs it at the very end of the critical path.
-    if (chunk == 0 && kvh == 0 && b == 0)
+    // needs it at the very end of the critical path.
+    if (blockIdx.x == 0)
         for (int i = tid; i < kDim * kDim / 32; i += kAttnThreads)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Pi_v + i * 32));
-    // Everything up to pdl_begin() may run while the launch before this one is still executing. It
-    // reads only what older launches produced: the page table and every page except each sequence's
-    // last one (the page the preceding append / post kernel is writing the new token into).
-    const int Hq = p.H * kGroup;
-
-    const int seq_pg0 = p.indptr[b];
-    const int n_pages_b = p.indptr[b + 1] - seq_pg0;
-    const int P = p.pages_per_cta;
-    const int n_chunks_b = (n_pages_b + P - 1) / P;
-    __half* out_base = p.out + ((size_t)b * Hq + (size_t)kvh * kGroup) * kDim;
-
-    if (n_pages_b <= 0) {
-        pdl_begin();
-        if (chunk == 0)
-            for (int i = tid; i < kGroup * kDim; i += kAttnThreads) out_base[i] = __float2half_rn(0.f);
-        return;
-    }
-    if (chunk >= n_chunks_b) return;
-
-    int last_len = p.last_len[b];
-    last_len = last_len < 1 ? 1 : (last_len > 16 ? 16 : last_len);
-    const int cta_pg1 = min(n_pages_b, chunk * P + P);
-    const int ppw = (P + kAttnWarps - 1) / kAttnWarps;          // <= 32 (host guarantees it)
-    const int w_pg0 = chunk * P + warp * ppw;
-    const int n_my = max(0, min(cta_pg1, w_pg0 + ppw) - w_pg0);
-
-    // lane i keeps the page id of this warp's i-th page; out-of-range ids are flagged once here
-    int my_page = 0;
-    if (lane < n_my) {
-        my_page = p.indices[seq_pg0 + w_pg0 + lane];
-        if (my_page < 0 || my_page >= p.n_pages) {
-            my_page = -1;
-            atomicOr(p.status, kStatusBadPage);
-        }
-    }
 
     const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
     const uint32_t ring0 = smem_u32(&s_ring[warp][0][0][0]);
@@ -77,272 +59,439 @@ __global__ void __launch_bounds__(kAttnThreads, 6) tq_decode_attn_kernel(const A
     }
     __syncwarp();
 
-    const uint8_t* pool_kvh = p.pool + (size_t)kvh * kChunkBytes;
-    const size_t page_stride = (size_t)2 * p.H * kChunkBytes;       // K chunk of a page -> next page
-    const size_t kv_stride = (size_t)p.H * kChunkBytes;             // K chunk -> V chunk of that page
-    auto issue = [&](int s, int page) {                             // lane 0 only
-        const uint8_t* src = pool_kvh + (size_t)(page < 0 ? 0 : page) * page_stride;
-        mbar_expect_tx(bar0 + 8 * s, 2 * kChunkBytes);
-        bulk_g2s(ring0 + s * 2 * kChunkBytes, src, kChunkBytes, bar0 + 8 * s);
-        bulk_g2s(ring0 + s * 2 * kChunkBytes + kChunkBytes, src + kv_stride, kChunkBytes, bar0 + 8 * s);
-    };
-    // first copies: all but the sequence's last page start now, that one after the wait
-    const int i_seq_last = n_pages_b - 1 - w_pg0;                   // index of the last page in this warp, if it has it
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-        const int pg = __shfl_sync(0xffffffffu, my_page, s);
-        if (lane == 0 && s < n_my && s != i_seq_last) issue(s, pg);
+    // ---- this CTA's share of the flat page list ----
+    // With early fetch everything up to the first pdl_begin() below runs while the launch before this
+    // one may still be executing; it reads only the page table and pages that older launches wrote.
+    const int ip0 = p.indptr[0];
+    const long long F = (long long)H * (p.indptr[p.B] - ip0);
+    // sequences without pages produce zeros; CTAs share them out
+    for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
+        if (p.indptr[b + 1] - p.indptr[b] <= 0) {
+            if (!waited) { pdl_begin(); waited = true; }
+            __half* o = p.out + (size_t)b * Hq * kDim;
+            for (int i = tid; i < Hq * kDim; i += kAttnThreads) o[i] = __float2half_rn(0.f);
+        }
     }
-
-    pdl_begin();
-    if (i_seq_last >= 0 && i_seq_last < kStages && i_seq_last < n_my) {
-        const int pg = __shfl_sync(0xffffffffu, my_page, i_seq_last);
-        if (lane == 0) issue(i_seq_last, pg);
-    }
-
-    // Query as the B operand of the score MMA: column n = g is (head g/2, hi|lo part g%2);
-    // k-step s covers rotated coordinates 32t + 4s .. +3.
-    const int head = g >> 1, part = g & 1;
-    uint32_t qf[8][2];
+    long long C = gridDim.x;
     {
-        const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const float4 v = *reinterpret_cast<const float4*>(qp + 4 * s);
-            qf[s][0] = pack_h2(split_part(v.x * p.qscale, part), split_part(v.y * p.qscale, part));
-            qf[s][1] = pack_h2(split_part(v.z * p.qscale, part), split_part(v.w * p.qscale, part));
+        long long cap = F / kMinPagesPerCta;
+        if (cap < 1) cap = 1;
+        if (C > cap) C = cap;
+    }
+    if (F <= 0 || (long long)blockIdx.x >= C) {
+        if (!waited) pdl_begin();
+        return;
+    }
+    const long long f_lo = (long long)blockIdx.x * F / C, f_hi = ((long long)blockIdx.x + 1) * F / C;
+
+    // sequence that holds flat page f_lo: the last b with H * (indptr[b] - indptr[0]) <= f_lo
+    int b;
+    {
+        int lo = 0, hi = p.B;
+        while (hi - lo > 1) {
+            const int step = (hi - lo + kAttnThreads - 1) / kAttnThreads;
+            const long long idx = (long long)lo + (long long)(tid + 1) * step;
+            const bool pred = idx < hi && (long long)H * (p.indptr[idx] - ip0) <= f_lo;
+            const int cnt = __syncthreads_count(pred);
+            lo += cnt * step;
+            hi = min(hi, lo + step);
         }
+        b = lo;
+    }
+    int seq_pg0 = p.indptr[b];
+    int n_b = p.indptr[b + 1] - seq_pg0;
+    int kvh, pg;
+    {
+        const long long r = f_lo - (long long)H * (seq_pg0 - ip0);
+        kvh = (int)(r / n_b);
+        pg = (int)(r - (long long)kvh * n_b);
     }
 
-    float m_ref = -INFINITY, l_run = 0.f;     // m_ref: reference value of the exponentials (per head t)
-    float acc[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const uint8_t* pool_base = p.pool;
+    const size_t page_stride = (size_t)2 * H * kChunkBytes;       // K chunk of a page -> next page
+    const size_t kv_stride = (size_t)H * kChunkBytes;             // K chunk -> V chunk of that page
+    unsigned it = 0;                 // pages this warp has put through its ring so far
+    bool failed = false;             // a bounded wait gave up: the warp stops using its ring
 
-    int n_done = 0;
-    bool failed = false;
-    for (int i = 0; i < n_my; ++i) {
-        const int s = i & (kStages - 1);
-        // the verdict is made warp-uniform so that no lane is left behind at a shuffle
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (i / kStages) & 1))) {
-            failed = true;
-            break;
-        }
-        n_done = i + 1;
-        const int page = __shfl_sync(0xffffffffu, my_page, i);
-        const int next_page = __shfl_sync(0xffffffffu, my_page, (i + kStages) & 31);
-        const int n_valid = page < 0 ? 0 : ((w_pg0 + i == n_pages_b - 1) ? last_len : 16);
-
-        const uint8_t* stage = &s_ring[warp][s][0][0];
-        const uint32_t* kw = reinterpret_cast<const uint32_t*>(stage);
-        const __half* kn = reinterpret_cast<const __half*>(stage + kNormOffsetBytes);
-        const uint32_t* vw = reinterpret_cast<const uint32_t*>(stage + kChunkBytes);
-        const __half* vn = reinterpret_cast<const __half*>(stage + kChunkBytes + kNormOffsetBytes);
-
-        // ---- scores: D[16 tokens][8 = 4 heads x (hi,lo)] ----
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-        {
-            float d2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: halves the dependent MMA chain
-            const Unit ua = load_unit(kw, lane), ub = load_unit(kw, 32 + lane);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const uint32_t sa = ua.s[q >> 1] >> (16 * (q & 1));
-                const uint32_t sb = ub.s[q >> 1] >> (16 * (q & 1));
-                const uint32_t la = __byte_perm(p.tl0, p.tl1, sa), ha = __byte_perm(p.th0, p.th1, sa);
-                const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb), hb = __byte_perm(p.th0, p.th1, sb);
-                mma_16816((q & 1) ? d2 : d, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
-                          __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), qf[q][0], qf[q][1]);
+    for (long long f = f_lo; f < f_hi;) {
+        const int seg_len = (int)min((long long)(n_b - pg), f_hi - f);
+        if (seg_len <= 0) break;         // cannot happen for a consistent page table; never loop on an inconsistent one
+        const bool whole = seg_len == n_b;
+        // ---- this warp's pages of the segment ----
+        const int w_lo = pg + (int)(((long long)seg_len * warp) / kAttnWarps);
+        const int w_hi = pg + (int)(((long long)seg_len * (warp + 1)) / kAttnWarps);
+        const int n_my = failed ? 0 : w_hi - w_lo;
+        const uint8_t* pool_kvh = pool_base + (size_t)kvh * kChunkBytes;
+        auto issue = [&](unsigned itn, int page) {                     // lane 0 only
+            const uint32_t s = itn & (kStages - 1);
+            const uint8_t* src = pool_kvh + (size_t)(page < 0 ? 0 : page) * page_stride;
+            mbar_expect_tx(bar0 + 8 * s, 2 * kChunkBytes);
+            bulk_g2s(ring0 + s * 2 * kChunkBytes, src, kChunkBytes, bar0 + 8 * s);
+            bulk_g2s(ring0 + s * 2 * kChunkBytes + kChunkBytes, src + kv_stride, kChunkBytes, bar0 + 8 * s);
+        };
+        // lane i keeps the page id of the warp's (32 * batch + i)-th page; the next batch is fetched a
+        // batch ahead. Out-of-range ids are flagged once and read as a page without valid tokens.
+        auto load_ids = [&](int first) -> int {
+            int id = 0;
+            if (first + lane < n_my) {
+                id = p.indices[seq_pg0 + w_lo + first + lane];
+                if (id < 0 || id >= p.n_pages) {
+                    id = -1;
+                    atomicOr(p.status, kStatusBadPage);
+                }
             }
-            d[0] += d2[0]; d[1] += d2[1]; d[2] += d2[2]; d[3] += d2[3];
+            return id;
+        };
+        int ids_cur = load_ids(0), ids_nxt = load_ids(32);
+        // first copies; before the dependency wait the sequence's last page (the one the preceding
+        // launch may be writing the new token into) is left out and issued right after the wait
+        const int i_seq_last = n_b - 1 - w_lo;
+        bool held_back = false;
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+            const int pgid = __shfl_sync(0xffffffffu, ids_cur, s);
+            if (s < n_my) {
+                if (!waited && s == i_seq_last) held_back = true;
+                else if (lane == 0) issue(it + s, pgid);
+            }
         }
-        float sa = (d[0] + d[1]) * __half2float(kn[g]);
-        float sb = (d[2] + d[3]) * __half2float(kn[g + 8]);
-        float na = __half2float(vn[g]), nb = __half2float(vn[g + 8]);
-        if (n_valid < 16) {                      // last page of a sequence (or a rejected page)
-            if (g >= n_valid) { sa = -INFINITY; na = 0.f; }
-            if (g + 8 >= n_valid) { sb = -INFINITY; nb = 0.f; }
+        if (!waited) {
+            pdl_begin();
+            waited = true;
+            if (held_back) {
+                const int pgid = __shfl_sync(0xffffffffu, ids_cur, i_seq_last);
+                if (lane == 0) issue(it + i_seq_last, pgid);
+            }
         }
 
-        // ---- online softmax (log2 domain; the query carries scale * log2 e) ----
-        float mt = fmaxf(sa, sb);
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
-        if (__any_sync(0xffffffffu, mt > m_ref + kRescaleSlack)) {
-            if (mt > m_ref + kRescaleSlack) {         // this lane's head moves its reference value
-                const float f = ex2_approx(m_ref - mt);   // 0 on the first page (m_ref = -inf)
-                l_run *= f;
+        // ---- query as the A operand of the integer score MMA ----
+        // Rows 0..3 of the 16 x 32 tile are the four heads' high digits against the centroids' high
+        // digits; rows 8..11 pair the low digits of one side with the high digits of the other; the
+        // rest is zero. Lane (g, t) with g < 4 holds head g, rotated coordinates 32t .. 32t+31;
+        // k-step s covers coordinates 32t + 4s .. +3.
+        uint32_t qh[8], ql[8];
+        float kscale = 0.f;      // score per integer unit of (256 * HH + MID), before the key norm
+        {
+            const int head = g & 3;
+            const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
+            float4 v[8];
+            float amax = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                v[s] = *reinterpret_cast<const float4*>(qp + 4 * s);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[s].x), fabsf(v[s].y)), fmaxf(fabsf(v[s].z), fabsf(v[s].w))));
+            }
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const float uq = amax > 0.f ? amax * (1.0f / kFixedMax) : 1.0f;
+            const float inv = 1.0f / uq;
+            kscale = 256.0f * uq * p.c_unit * p.qscale;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const float e[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+                uint32_t hi = 0, lo = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int qi = __float2int_rn(e[i] * inv);
+                    const int l8 = ((qi + 128) & 255) - 128;         // balanced low digit in [-128, 127]
+                    const int h8 = (qi - l8) >> 8;                    // |qi| <= 32512 keeps this in [-127, 127]
+                    hi |= (uint32_t)(h8 & 255) << (8 * i);
+                    lo |= (uint32_t)(l8 & 255) << (8 * i);
+                }
+                qh[s] = g < 4 ? hi : 0u;
+                ql[s] = g < 4 ? lo : 0u;
+            }
+        }
+
+        float m_ref = -INFINITY, l_run = 0.f;     // lanes g < 4: head g, this lane's four tokens per page
+        float acc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+        int n_done = 0;
+        for (int i = 0; i < n_my; ++i) {
+            const unsigned itn = it + i;
+            const int s = itn & (kStages - 1);
+            if ((i & 31) == 0 && i > 0) {
+                ids_cur = ids_nxt;
+                ids_nxt = load_ids(i + 32);
+            }
+            // the verdict is made warp-uniform so that no lane is left behind at a shuffle
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (itn / kStages) & 1))) {
+                failed = true;
+                break;
+            }
+            n_done = i + 1;
+            const int page = __shfl_sync(0xffffffffu, ids_cur, i & 31);
+            const int i_next = i + kStages;
+            const int next_page = __shfl_sync(0xffffffffu, (i_next >> 5) == (i >> 5) ? ids_cur : ids_nxt, i_next & 31);
+            const int n_valid = page < 0 ? 0 : ((w_lo + i == n_b - 1) ? min(max(p.last_len[b], 1), 16) : 16);
+
+            const uint8_t* stage = &s_ring[warp][s][0][0];
+            const uint32_t* kw = reinterpret_cast<const uint32_t*>(stage);
+            const uint32_t* kn2 = reinterpret_cast<const uint32_t*>(stage + kNormOffsetBytes);
+            const uint32_t* vw = reinterpret_cast<const uint32_t*>(stage + kChunkBytes);
+            const uint32_t* vn2 = reinterpret_cast<const uint32_t*>(stage + kChunkBytes + kNormOffsetBytes);
+
+            // ---- scores: D[row][token], tokens 0..7 in tile 0 and 8..15 in tile 1 ----
+            int d0[4] = {kBiasBits, kBiasBits, kBiasBits, kBiasBits};
+            int d1[4] = {kBiasBits, kBiasBits, kBiasBits, kBiasBits};
+            {
+                const Unit ua = load_unit(kw, lane), ub = load_unit(kw, 32 + lane);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const uint32_t sa = ua.s[q >> 1] >> (16 * (q & 1));
+                    const uint32_t sb = ub.s[q >> 1] >> (16 * (q & 1));
+                    mma_s8_16832(d0, qh[q], ql[q], 0u, qh[q], __byte_perm(p.kh0, p.kh1, sa), __byte_perm(p.kl0, p.kl1, sa));
+                    mma_s8_16832(d1, qh[q], ql[q], 0u, qh[q], __byte_perm(p.kh0, p.kh1, sb), __byte_perm(p.kl0, p.kl1, sb));
+                }
+            }
+            // tokens of this lane: 2t, 2t+1 (tile 0) and 8+2t, 9+2t (tile 1); norms as fp16 pairs
+            const float2 kna = h2_to_f2(kn2[t]), knb = h2_to_f2(kn2[4 + t]);
+            float2 vna = h2_to_f2(vn2[t]), vnb = h2_to_f2(vn2[4 + t]);
+            float sc[4];
+            sc[0] = fmaf(__int_as_float(d0[0]) - kBiasF, 256.f, __int_as_float(d0[2]) - kBiasF) * (kscale * kna.x);
+            sc[1] = fmaf(__int_as_float(d0[1]) - kBiasF, 256.f, __int_as_float(d0[3]) - kBiasF) * (kscale * kna.y);
+            sc[2] = fmaf(__int_as_float(d1[0]) - kBiasF, 256.f, __int_as_float(d1[2]) - kBiasF) * (kscale * knb.x);
+            sc[3] = fmaf(__int_as_float(d1[1]) - kBiasF, 256.f, __int_as_float(d1[3]) - kBiasF) * (kscale * knb.y);
+            if (n_valid < 16) {                      // last page of a sequence (or a rejected page)
+                if (2 * t >= n_valid) { sc[0] = -INFINITY; vna.x = 0.f; }
+                if (2 * t + 1 >= n_valid) { sc[1] = -INFINITY; vna.y = 0.f; }
+                if (8 + 2 * t >= n_valid) { sc[2] = -INFINITY; vnb.x = 0.f; }
+                if (9 + 2 * t >= n_valid) { sc[3] = -INFINITY; vnb.y = 0.f; }
+            }
+
+            // ---- online softmax (log2 domain; the scores carry scale * log2 e) ----
+            const float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+            if (__any_sync(0xffffffffu, g < 4 && mx > m_ref + kRescaleSlack)) {
+                // some head's reference value moves: its four lanes agree on the new one, and every
+                // lane rescales the accumulator columns of the heads it holds
+                float mh = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, 2));
+                float fsc = 1.0f;
+                if (mh > m_ref + kRescaleSlack) {
+                    fsc = ex2_approx(m_ref - mh);          // 0 on the first page (m_ref = -inf)
+                    l_run *= fsc;
+                    m_ref = mh;
+                }
+                const float fa = __shfl_sync(0xffffffffu, fsc, ((2 * t) & 3) * 4);
+                const float fb = __shfl_sync(0xffffffffu, fsc, ((2 * t + 1) & 3) * 4);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    acc[j][0] *= f; acc[j][1] *= f; acc[j][2] *= f; acc[j][3] *= f;
+                    acc[j][0] *= fa; acc[j][2] *= fa;
+                    acc[j][1] *= fb; acc[j][3] *= fb;
                 }
-                m_ref = mt;
             }
+            const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;    // only while nothing valid was seen
+            const float p0 = ex2_approx(sc[0] - m_safe), p1 = ex2_approx(sc[1] - m_safe);
+            const float p2 = ex2_approx(sc[2] - m_safe), p3 = ex2_approx(sc[3] - m_safe);
+            l_run += (p0 + p1) + (p2 + p3);
+            // Probabilities (times value norms) are already where the value MMA wants its B operand:
+            // rows = tokens 2t, 2t+1, 2t+8, 2t+9, column g = head g (columns 4..7 stay zero). fp16 rounding
+            // of the probabilities is independent from token to token and averages out over the sum.
+            const uint32_t b0 = g < 4 ? pack_h2(p0 * vna.x, p1 * vna.y) : 0u;
+            const uint32_t b1 = g < 4 ? pack_h2(p2 * vnb.x, p3 * vnb.y) : 0u;
+            {
+                const Unit ua = load_unit(vw, lane), ub = load_unit(vw, 32 + lane);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t sa2 = ua.s[j >> 1] >> (16 * (j & 1));
+                    const uint32_t sb2 = ub.s[j >> 1] >> (16 * (j & 1));
+                    const uint32_t la = __byte_perm(p.tl0, p.tl1, sa2), ha = __byte_perm(p.th0, p.th1, sa2);
+                    const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb2), hb = __byte_perm(p.th0, p.th1, sb2);
+                    mma_16816(acc[j], __byte_perm(la, ha, 0x5140), __byte_perm(la, ha, 0x7362),
+                              __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362), b0, b1);
+                }
+            }
+            __syncwarp();   // every lane has finished reading this stage
+            if (lane == 0 && i_next < n_my) issue(itn + kStages, next_page);
         }
-        const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;    // only while nothing valid was seen
-        const float pa = ex2_approx(sa - m_safe), pb = ex2_approx(sb - m_safe);
-        l_run += pa + pb;
-        const float wa = pa * na, wb = pb * nb;
+        if (failed && n_my > 0) {
+            // Give the copies still in flight a bounded chance to land before the CTA can exit.
+            if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+            const int issued = min(n_my, n_done + kStages);
+            for (int i = n_done; i < issued; ++i)
+                mbar_wait_bounded(bar0 + 8 * ((it + i) & (kStages - 1)), ((it + i) / kStages) & 1);
+        }
+        it += n_my;
 
-        // Probabilities (times value norms) as the B operand of the value MMA: rows = tokens,
-        // column n = g is (head g/2, hi|lo part g%2).
-        const int src0 = (2 * t) * 4 + head, src1 = src0 + 4;
-        const float x0 = __shfl_sync(0xffffffffu, wa, src0), x1 = __shfl_sync(0xffffffffu, wa, src1);
-        const float x2 = __shfl_sync(0xffffffffu, wb, src0), x3 = __shfl_sync(0xffffffffu, wb, src1);
-        // fp16 rounding of the probabilities is independent from token to token and averages out over
-        // the sum, unlike rounding of the query or of the centroids: no hi/lo split here, the "lo"
-        // columns of the value MMA are fed zeros
-        const uint32_t b0 = part ? 0u : pack_h2(x0, x1);
-        const uint32_t b1 = part ? 0u : pack_h2(x2, x3);
-        {
-            const Unit ua = load_unit(vw, lane), ub = load_unit(vw, 32 + lane);
+        // ---- warp result -> shared memory ----
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        if (g < 4 && t == 0) {
+            s_m[warp][g] = m_ref;
+            s_l[warp][g] = l_run;
+        }
+        if (t < 2) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const uint32_t sa2 = ua.s[j >> 1] >> (16 * (j & 1));
-                const uint32_t sb2 = ub.s[j >> 1] >> (16 * (j & 1));
-                const uint32_t la = __byte_perm(p.tl0, p.tl1, sa2), ha = __byte_perm(p.th0, p.th1, sa2);
-                const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb2), hb = __byte_perm(p.th0, p.th1, sb2);
-                mma_16816(acc[j], __byte_perm(la, ha, 0x5140), __byte_perm(la, ha, 0x7362),
-                          __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362), b0, b1);
+                // rows g / g+8 of m-tile j are rotated coordinates 16g+2j / 16g+2j+1; columns 2t, 2t+1
+                // are heads 2t and 2t+1.
+                *reinterpret_cast<float2*>(&s_res[warp][2 * t][16 * g + 2 * j]) = make_float2(acc[j][0], acc[j][2]);
+                *reinterpret_cast<float2*>(&s_res[warp][2 * t + 1][16 * g + 2 * j]) = make_float2(acc[j][1], acc[j][3]);
             }
         }
-        __syncwarp();   // every lane has finished reading this stage
-        if (lane == 0 && i + kStages < n_my) issue(s, next_page);
-    }
-    if (failed) {
-        // Give the copies still in flight a bounded chance to land before the CTA can exit.
-        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
-        const int issued = min(n_my, n_done + kStages);
-        for (int i = n_done; i < issued; ++i) mbar_wait_bounded(bar0 + 8 * (i & (kStages - 1)), (i / kStages) & 1);
-    }
-
-    // ---- warp result -> shared memory (the warp's own ring is free now) ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
-    if (g == 0) {
-        s_m[warp][t] = m_ref;
-        s_l[warp][t] = l_run;
-    }
-    __syncwarp();
-    float* w_acc = reinterpret_cast<float*>(&s_ring[warp][0][0][0]);      // [kGroup][kDim] floats = 2 KB
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        // rows g / g+8 of m-tile j are rotated coordinates 16g+2j / 16g+2j+1; columns 2t, 2t+1
-        // are the hi and lo parts of head t.
-        *reinterpret_cast<float2*>(&w_acc[t * kDim + 16 * g + 2 * j]) =
-            make_float2(acc[j][0] + acc[j][1], acc[j][2] + acc[j][3]);
-    }
-    __syncthreads();
-
-    // ---- CTA merge over its 4 warps: thread = rotated coordinate ----
-    float* ring_f = reinterpret_cast<float*>(&s_ring[0][0][0][0]);
-    constexpr int kWarpRingFloats = kStages * 2 * kChunkBytes / 4;
-    float o[kGroup], mh[kGroup], lh[kGroup];
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-        float m = s_m[0][h];
-#pragma unroll
-        for (int w = 1; w < kAttnWarps; ++w) m = fmaxf(m, s_m[w][h]);
-        float ov = 0.f, lv = 0.f;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
-            const float mw = s_m[w][h];
-            const float f = mw == -INFINITY ? 0.f : ex2_approx(mw - m);
-            ov = fmaf(f, ring_f[w * kWarpRingFloats + h * kDim + tid], ov);
-            lv = fmaf(f, s_l[w][h], lv);
-        }
-        o[h] = ov; mh[h] = m; lh[h] = lv;
-    }
-
-    if (n_chunks_b > 1) {
-        float* mine = p.partials + (((size_t)b * p.H + kvh) * p.n_chunks + chunk) * kPartialFloats;
-#pragma unroll
-        for (int h = 0; h < kGroup; ++h) mine[h * kDim + tid] = o[h];
-        if (tid < kGroup) {
-            mine[kGroup * kDim + tid] = mh[tid];
-            mine[kGroup * kDim + kGroup + tid] = lh[tid];
-        }
-        __threadfence();
         __syncthreads();
-        if (tid == 0) {
-            const int prev = atomicAdd(&p.counters[b * p.H + kvh], 1);
-            s_last = (prev == n_chunks_b - 1);
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        // last CTA of this (sequence, kv head): merge the chunk partials in chunk order.
-        // All maxima / sums first (one round trip, staged in the now idle ring), then the value rows
-        // with the loads of several chunks and all four heads in flight together.
-        const float* base = p.partials + (((size_t)b * p.H + kvh) * p.n_chunks) * kPartialFloats;
-        float* s_ml = ring_f;                                     // [n_chunks_b][2 * kGroup]: m then l
-        for (int i = tid; i < n_chunks_b * 2 * kGroup; i += kAttnThreads)
-            s_ml[i] = ld_cg_f32(base + (size_t)(i >> 3) * kPartialFloats + kGroup * kDim + (i & 7));
-        __syncthreads();
-        float mg[kGroup];
+
+        // ---- CTA merge over its 4 warps: thread = rotated coordinate ----
+        float o[kGroup], mh[kGroup], lh[kGroup];
 #pragma unroll
         for (int h = 0; h < kGroup; ++h) {
-            float m = -INFINITY;
-            for (int c = 0; c < n_chunks_b; ++c) m = fmaxf(m, s_ml[c * 2 * kGroup + h]);
-            mg[h] = m;
-            o[h] = 0.f;
-            lh[h] = 0.f;
-        }
-#pragma unroll 4
-        for (int c = 0; c < n_chunks_b; ++c) {
-            const float* pc = base + (size_t)c * kPartialFloats + tid;
-            float ov[kGroup];
+            float m = s_m[0][h];
 #pragma unroll
-            for (int h = 0; h < kGroup; ++h) ov[h] = ld_cg_f32(pc + h * kDim);
+            for (int w = 1; w < kAttnWarps; ++w) m = fmaxf(m, s_m[w][h]);
+            float ov = 0.f, lv = 0.f;
 #pragma unroll
-            for (int h = 0; h < kGroup; ++h) {
-                const float mc = s_ml[c * 2 * kGroup + h];
-                const float f = mc == -INFINITY ? 0.f : ex2_approx(mc - mg[h]);
-                o[h] = fmaf(f, ov[h], o[h]);
-                lh[h] = fmaf(f, s_ml[c * 2 * kGroup + kGroup + h], lh[h]);
+            for (int w = 0; w < kAttnWarps; ++w) {
+                const float mw = s_m[w][h];
+                const float fw = mw == -INFINITY ? 0.f : ex2_approx(mw - m);
+                ov = fmaf(fw, s_res[w][h][tid], ov);
+                lv = fmaf(fw, s_l[w][h], lv);
             }
+            o[h] = ov; mh[h] = m; lh[h] = lv;
         }
-        __syncthreads();                                          // s_ml is overwritten below (s_o / s_part)
-        if (tid == 0) p.counters[b * p.H + kvh] = 0;
-    }
+        __syncthreads();                       // s_res / s_m / s_l may be overwritten from here on
 
-    // ---- normalise, undo the centroid scale, rotate back: out = o @ Pi_v ----
-    float* s_o = ring_f + 512;               // [kGroup][kDim], behind warp 0's partial
-    float* s_part = ring_f + 1024;           // [kAttnWarps][kGroup][kDim]
+        bool finish = whole;
+        if (!whole) {
+            // partial slot: 1 if this pair started in an earlier part of this CTA's share (it is then
+            // the CTA's last segment), 0 if the CTA's share starts inside or at the start of the pair
+            const long long o_p = (long long)H * (seq_pg0 - ip0) + (long long)kvh * n_b;
+            const int slot = f_lo < o_p ? 1 : 0;
+            float* mine = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPartialFloats;
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) s_o[h * kDim + tid] = lh[h] > 0.f ? o[h] * (p.inv_alpha / lh[h]) : 0.f;
-    __syncthreads();
-    {
-        // warp w sums rows 32w .. 32w+31 of Pi_v for 4 output columns per lane (coalesced 16-byte loads)
-        float r[kGroup][4];
+            for (int h = 0; h < kGroup; ++h) mine[h * kDim + tid] = o[h];
+            if (tid < kGroup) {
+                mine[kGroup * kDim + tid] = mh[tid];
+                mine[kGroup * kDim + kGroup + tid] = lh[tid];
+            }
+            __threadfence();
+            __syncthreads();
+            const long long e_p = o_p + n_b - 1;
+            const int c_first = (int)(((o_p + 1) * C + F - 1) / F) - 1;
+            const int c_last = (int)(((e_p + 1) * C + F - 1) / F) - 1;
+            const int n_seg = c_last - c_first + 1;
+            if (tid == 0) {
+                const int prev = atomicAdd(&p.counters[b * H + kvh], 1);
+                s_last = (prev == n_seg - 1);
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                // last CTA of this (sequence, kv head): merge the partials in CTA order. All maxima / sums
+                // first (one round trip), then the value rows with several CTAs' loads in flight together.
+                float* s_ml = &s_res[0][0][0];                            // [n_seg][2 * kGroup]: m then l
+                auto part_of = [&](int k) -> const float* {
+                    const int c = c_first + k;
+                    const int sl = (k == 0 && ((long long)c * F / C) < o_p) ? 1 : 0;
+                    return p.partials + ((size_t)c * 2 + sl) * kPartialFloats;
+                };
+                // a pair cut into more pieces than the staging area holds (one very long sequence among
+                // short ones) reads its maxima / sums from the workspace directly
+                const bool staged = n_seg * 2 * kGroup <= kAttnWarps * kGroup * kDim;
+                auto ml = [&](int k, int j) -> float {
+                    return staged ? s_ml[k * 2 * kGroup + j] : ld_cg_f32(part_of(k) + kGroup * kDim + j);
+                };
+                if (staged)
+                    for (int i = tid; i < n_seg * 2 * kGroup; i += kAttnThreads)
+                        s_ml[i] = ld_cg_f32(part_of(i >> 3) + kGroup * kDim + (i & 7));
+                __syncthreads();
+                float mg[kGroup];
 #pragma unroll
-        for (int h = 0; h < kGroup; ++h) r[h][0] = r[h][1] = r[h][2] = r[h][3] = 0.f;
-        const float4* pv = reinterpret_cast<const float4*>(p.Pi_v) + (size_t)(32 * warp) * (kDim / 4) + lane;
+                for (int h = 0; h < kGroup; ++h) {
+                    float m = -INFINITY;
+                    for (int k = 0; k < n_seg; ++k) m = fmaxf(m, ml(k, h));
+                    mg[h] = m;
+                    o[h] = 0.f;
+                    lh[h] = 0.f;
+                }
+#pragma unroll 4
+                for (int k = 0; k < n_seg; ++k) {
+                    const float* pc = part_of(k) + tid;
+                    float ov[kGroup];
 #pragma unroll
-        for (int ii = 0; ii < 32; ++ii) {
-            const float4 w4 = __ldg(pv + (size_t)ii * (kDim / 4));
-            const int i = 32 * warp + ii;
+                    for (int h = 0; h < kGroup; ++h) ov[h] = ld_cg_f32(pc + h * kDim);
 #pragma unroll
-            for (int h = 0; h < kGroup; ++h) {
-                const float sv = s_o[h * kDim + i];
-                r[h][0] = fmaf(sv, w4.x, r[h][0]);
-                r[h][1] = fmaf(sv, w4.y, r[h][1]);
-                r[h][2] = fmaf(sv, w4.z, r[h][2]);
-                r[h][3] = fmaf(sv, w4.w, r[h][3]);
+                    for (int h = 0; h < kGroup; ++h) {
+                        const float mc = ml(k, h);
+                        const float fc = mc == -INFINITY ? 0.f : ex2_approx(mc - mg[h]);
+                        o[h] = fmaf(fc, ov[h], o[h]);
+                        lh[h] = fmaf(fc, ml(k, kGroup + h), lh[h]);
+                    }
+                }
+                __syncthreads();                                          // s_ml is overwritten below
+                if (tid == 0) p.counters[b * H + kvh] = 0;
+                finish = true;
             }
         }
+
+        if (finish) {
+            // ---- normalise, undo the centroid scale, rotate back: out = o @ Pi_v ----
+            float* s_o = &s_res[0][0][0];                                 // [kGroup][kDim]
+            float* s_part = &s_res[1][0][0];                              // [kAttnWarps - 1][kGroup][kDim]
 #pragma unroll
-        for (int h = 0; h < kGroup; ++h)
-            *reinterpret_cast<float4*>(&s_part[(warp * kGroup + h) * kDim + 4 * lane]) =
-                make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);
-    }
-    __syncthreads();
+            for (int h = 0; h < kGroup; ++h) s_o[h * kDim + tid] = lh[h] > 0.f ? o[h] * (p.inv_alpha / lh[h]) : 0.f;
+            __syncthreads();
+            // warp w sums rows 32w .. 32w+31 of Pi_v for 4 output columns per lane (coalesced 16-byte loads)
+            float r[kGroup][4];
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-        float v = 0.f;
+            for (int h = 0; h < kGroup; ++h) r[h][0] = r[h][1] = r[h][2] = r[h][3] = 0.f;
+            const float4* pv = reinterpret_cast<const float4*>(p.Pi_v) + (size_t)(32 * warp) * (kDim / 4) + lane;
+#pragma unroll 8
+            for (int ii = 0; ii < 32; ++ii) {
+                const float4 w4 = __ldg(pv + (size_t)ii * (kDim / 4));
+                const int i = 32 * warp + ii;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) v += s_part[(w * kGroup + h) * kDim + tid];
-        out_base[h * kDim + tid] = __float2half_rn(v);
+                for (int h = 0; h < kGroup; ++h) {
+                    const float sv = s_o[h * kDim + i];
+                    r[h][0] = fmaf(sv, w4.x, r[h][0]);
+                    r[h][1] = fmaf(sv, w4.y, r[h][1]);
+                    r[h][2] = fmaf(sv, w4.z, r[h][2]);
+                    r[h][3] = fmaf(sv, w4.w, r[h][3]);
+                }
+            }
+            __syncthreads();                                              // everyone has read s_o
+            // cross-warp sum in two rounds through the three free warp slots of s_res
+            if (warp > 0) {
+#pragma unroll
+                for (int h = 0; h < kGroup; ++h)
+                    *reinterpret_cast<float4*>(&s_part[((warp - 1) * kGroup + h) * kDim + 4 * lane]) =
+                        make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);
+            }
+            __syncthreads();
+            if (warp == 0) {
+                __half* out_base = p.out + ((size_t)b * Hq + (size_t)kvh * kGroup) * kDim;
+#pragma unroll
+                for (int h = 0; h < kGroup; ++h) {
+                    float4 v = make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);
+#pragma unroll
+                    for (int w = 0; w < kAttnWarps - 1; ++w) {
+                        const float4 a = *reinterpret_cast<const float4*>(&s_part[(w * kGroup + h) * kDim + 4 * lane]);
+                        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    }
+                    const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&h01);
+                    pk.y = *reinterpret_cast<const uint32_t*>(&h23);
+                    *reinterpret_cast<uint2*>(out_base + h * kDim + 4 * lane) = pk;
+                }
+            }
+            __syncthreads();                                              // s_res is free for the next segment
+        }
+
+        // ---- advance to the next pair ----
+        f += seg_len;
+        pg += seg_len;
+        if (pg >= n_b && f < f_hi) {
+            pg = 0;
+            if (++kvh == H) {
+                kvh = 0;
+                do {
+                    ++b;
+                    seq_pg0 = p.indptr[b];
+                    n_b = p.indptr[b + 1] - seq_pg0;
+                } while (n_b <= 0 && b + 1 < p.B);
+            }
+        }
     }
 }

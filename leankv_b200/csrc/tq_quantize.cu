@@ -369,6 +369,12 @@ __global__ void tq_pool_unpack_kernel(const UnpackParams p) {
         const long long ht = i >> 6;
         const int tok = (int)(ht % p.n_tokens), h = (int)(ht / p.n_tokens);
         const int page = p.page_indices[tok >> 4], slot = tok & 15;
+        if (page < 0 || page >= p.n_pages) {
+            // a stale or foreign page id: nothing is read from the pool; the token reads as code 0, norm 0
+            p.indices[i] = 0;
+            if (byte == 0) p.norms[ht] = 0.f;
+            continue;
+        }
         const uint8_t* chunk = p.pool + (((size_t)page * 2 + p.which) * p.H + h) * kChunkBytes;
         const uint32_t* words = reinterpret_cast<const uint32_t*>(chunk);
         const int c0 = 2 * byte, c1 = c0 + 1;
@@ -389,12 +395,18 @@ int check_tq_common(long long n_vec, int dim, int bits) {
 
 template <bool kQuantize>
 int launch_tile(const TileParams& p, void* stream) {
-    static bool attr_done[2] = {false, false};
-    if (!attr_done[kQuantize]) {
+    // The opt-in to 128 KiB of dynamic shared memory belongs to a device's copy of the function, so it is
+    // remembered per device ordinal (a process may quantize on several GPUs). Racing first calls all
+    // store the same value.
+    constexpr int kMaxDevices = 64;
+    static bool attr_done[kMaxDevices][2] = {};
+    int dev = 0;
+    LEANKV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices || !attr_done[dev][kQuantize]) {
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_tile_kernel<kQuantize>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kTileSmemBytes));
-        attr_done[kQuantize] = true;
+        if (dev >= 0 && dev < kMaxDevices) attr_done[dev][kQuantize] = true;
     }
     const long long n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
     const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());

@@ -7,8 +7,9 @@ structure directly: every projection is a sparse GEMV launch (q/k/v fused into o
 gate/up fused with SiLU), K/V are rotated+quantized+packed on append, attention runs on the
 packed pages, and one whole step — including position / page-table bookkeeping and the
 greedy argmax — is captured in a CUDA graph and replayed per token. Tensor parallelism
-splits q/k/v/gate/up by output columns and o/down by input rows with one NCCL all-reduce
-after o_proj and one after down_proj.
+splits q/k/v/gate/up by output columns and o/down by input rows; the two sums per block are taken
+inside the row-parallel GEMV kernels over peer memory (``LEANKV_TP_EXCHANGE=nccl`` selects a separate
+NCCL all-reduce launch after o_proj and down_proj instead).
 
 Prefill (prompt processing) is dense, like the reference's kernel mode
 (``leankv/teal/patching.py:178-180``): library GEMMs + SDPA over the de-quantized pages.
@@ -154,6 +155,7 @@ class DecodeEngine:
         self.graph = None
         self.launches_per_step = 0
         self._pinned_token = torch.zeros(1, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else None
+        self._pinned_status = torch.zeros(2, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
 
     # ── construction helpers ─────────────────────────────────────────────
 
@@ -342,7 +344,7 @@ class DecodeEngine:
                 self.q_rot.data_ptr(), self.attn.data_ptr(), 1, self.nq, self.nkv, self.pools[l].data_ptr(),
                 self.max_pages, sp + 8, self.page_indices.data_ptr(), sp + 16, self.max_pages,
                 self.Pi_v[l].data_ptr(), self.centroids_host.data_ptr(), 1.0 / math.sqrt(128.0),
-                self.ws_attn.data_ptr(), self.ws_attn.numel(), st()), "decode_attn_rotated")
+                self.ws_attn.data_ptr(), self.ws_attn.numel(), _native.ATTN_EARLY_FETCH, st()), "decode_attn_rotated")
             self.launches_per_step += 2
         else:
             _native.check(lib.leankv_rope_f16(self.qkv.data_ptr(), self.inv_freq.data_ptr(), sp,
@@ -463,6 +465,24 @@ class DecodeEngine:
                 # the in-kernel exchange waits a bounded time for its peers: start the replays together
                 torch.cuda.synchronize()
                 torch.distributed.barrier(group=self.group)
+
+    def status_words(self) -> tuple[int, int]:
+        """(exchange status, attention status) read from the device: non-zero once a bounded wait inside
+        the in-kernel all-reduce / the attention kernel's page copies has given up, or a page id was out
+        of range. Synchronises the device."""
+        ex = int(self.xchg.status.item()) if self.xchg is not None else 0
+        at = int(self.ws_attn[:4].view(torch.int32).item())
+        return ex, at
+
+    def check_status(self) -> None:
+        """Raise if any kernel of this engine has reported a failed wait or a bad page id. The exchange
+        status is sticky and switches later polls off, so results computed after it was set are
+        meaningless: callers must not use them."""
+        ex, at = self.status_words()
+        if ex or at:
+            raise RuntimeError(f"decode kernels reported a failure: exchange status {ex} "
+                               f"(1 = a peer's partial sum never arrived), attention status {at} "
+                               f"(1 = page copy wait gave up, 2 = page id out of range)")
 
     def step(self, use_graph: bool = True) -> None:
         if use_graph:
@@ -627,10 +647,16 @@ class DecodeEngine:
                 self.graph.replay()
                 if stream_to_host:
                     self._pinned_token.copy_(self.token, non_blocking=True)
+                    self._pinned_status[0:1].copy_(self.ws_attn[:4].view(torch.int32), non_blocking=True)
+                    if self.xchg is not None:
+                        self._pinned_status[1:2].copy_(self.xchg.status, non_blocking=True)
                     torch.cuda.current_stream().synchronize()
+                    if int(self._pinned_status[0]) or int(self._pinned_status[1]):
+                        self.check_status()
                     out.append(int(self._pinned_token[0]))
             if not stream_to_host:
                 out = self.history[:1 + max(n_steps, 0)].tolist()
+            self.check_status()
         return out
 
     def bytes_streamed(self) -> int:

@@ -36,9 +36,24 @@ def paged_attention_forward(module, query, key, value, attention_mask, dropout: 
         d = query.shape[-1]
         if scaling is not None and abs(float(scaling) * d ** 0.5 - 1.0) > 1e-6:
             raise RuntimeError("the paged decode kernel uses scale = head_dim ** -0.5")
+        if attention_mask is not None and getattr(module, "layer_idx", 0) == 0 and _masks_something(attention_mask):
+            # The fused kernel attends to every cached token of a sequence. A mask that hides cached
+            # positions (left-padded prompts of unequal length in one batch, a sliding window) would be
+            # ignored silently, so it is refused; checked once per step, on the first layer.
+            raise RuntimeError(
+                "the paged decode kernel cannot apply an attention mask that hides cached positions "
+                "(padded batches of unequal prompt length, sliding-window attention): run such inputs "
+                "with disable_paged_attention(model), which takes the dense SDPA route")
         out = cache.decode_attention(module.layer_idx, query[:, :, 0, :])        # [B, Hq, D]
         return out.unsqueeze(1), None
     return _sdpa(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling, **kwargs)
+
+
+def _masks_something(mask: torch.Tensor) -> bool:
+    """True if a boolean (False = hidden) or additive (negative = hidden) mask hides any position."""
+    if mask.dtype == torch.bool:
+        return not bool(mask.all())
+    return bool((mask < 0).any())
 
 
 def register() -> None:

@@ -257,3 +257,135 @@ def test_paged_cache_api():
         big = torch.zeros(3, 2, 200, 128, dtype=torch.float16, device=dev)
         cache.update(big, big, 0)
     cache.print_memory_report()
+
+
+def count_code_parity(k, v, dev):
+    """Quantize one full sequence [Hkv, T, 128] (fp16 K and V) both ways the library offers — bulk
+    ``leankv_tq_quantize`` and ``leankv_tq_pool_append`` into pages — and compare every code with the
+    fixed-order oracle (must be identical) and with the reference-order torch quantize of
+    ``oracle/turboquant.py`` (may differ only inside the 4-ulp band around a decision boundary)."""
+    H, T, _ = k.shape
+    rp = RawPool((T + 15) // 16, H, dev)
+    pages = torch.randperm(rp.n_pages, generator=torch.Generator().manual_seed(11)).tolist()
+    rp.append(k.unsqueeze(0), v.unsqueeze(0), [0, len(pages)], pages, [0])
+    counts = {"coords": 0, "mismatches_vs_exact": 0, "near_ties_vs_reference": 0, "outside_band_vs_reference": 0}
+    for which, x, Pi, seed in ((0, k, rp.Pi_k, 42), (1, v, rp.Pi_v, 43)):
+        ex_codes, ex_norms, y, margin = tq_exact.quantize(x.float().cpu().numpy().reshape(-1, 128),
+                                                          Pi.cpu().numpy(), rp.bounds.cpu().numpy())
+        idx, norms = rp.unpack(pages, T, which)
+        pool_codes = pool_layout.nibbles_to_codes(idx).reshape(-1, 128)
+        quant = TurboQuantMSE(128, 3, dev, torch.float32, seed=seed)
+        q = quant.quantize(x)
+        bulk_codes = pool_layout.nibbles_to_codes(q.indices.cpu().numpy()).reshape(-1, 128)
+        counts["coords"] += ex_codes.size
+        counts["mismatches_vs_exact"] += int((pool_codes != ex_codes).sum()) + int((bulk_codes != ex_codes).sum())
+        assert np.array_equal(norms.reshape(-1), ex_norms.astype(np.float16).astype(np.float32))
+        ref_codes = otq.quantize(x.float().cpu(), Pi.cpu(), rp.bounds.cpu(), 3)[2].numpy().reshape(-1, 128)
+        diff = pool_codes != ref_codes
+        in_band = margin[diff] <= 4 * np.spacing(np.abs(y[diff]).astype(np.float32))
+        counts["near_ties_vs_reference"] += int(in_band.sum())
+        counts["outside_band_vs_reference"] += int((~in_band).sum())
+    return counts
+
+
+def test_quantize_full_config3_sequence_vs_both_oracles():
+    """8 kv heads x 4096 tokens, K and V: 8.4 M coordinates, the scale at which order-dependent
+    near-ties start to show up against the reference's BLAS."""
+    dev = _dev()
+    kv = workloads.kv_case(batch=1, context=4096, seed=3, device=dev)
+    counts = count_code_parity(kv.k[0], kv.v[0], dev)
+    print("config-3 sequence code parity:", counts)
+    assert counts["coords"] == 2 * 8 * 4096 * 128
+    assert counts["mismatches_vs_exact"] == 0
+    assert counts["outside_band_vs_reference"] == 0
+    assert counts["near_ties_vs_reference"] <= 64
+
+
+def test_decode_attention_ragged_batch_vs_oracle():
+    """Sequences of very different lengths (empty ones included) in one launch: the kernel cuts the flat
+    page list into equal shares regardless of where sequences begin and end."""
+    dev = _dev()
+    lens = [0, 1, 15, 16, 17, 100, 700, 33, 0, 2500, 64, 5]
+    B, H = len(lens), 2
+    gen = torch.Generator().manual_seed(21)
+    n_pages = sum((n + 15) // 16 for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=gen).tolist()
+    rp = RawPool(n_pages, H, dev)
+    q = torch.randn(B, 4 * H, 128, generator=gen).half().to(dev)
+    indptr, flat, last, pages = [0], [], [], []
+    for b, n in enumerate(lens):
+        np_b = (n + 15) // 16
+        mine = [perm.pop() for _ in range(np_b)]
+        pages.append(mine)
+        flat += mine
+        indptr.append(indptr[-1] + np_b)
+        last.append(16 if n == 0 else (n - 1) % 16 + 1)
+        if n:
+            k = (torch.randn(1, H, n, 128, generator=gen) * (1 + b % 3)).half().to(dev)
+            v = torch.randn(1, H, n, 128, generator=gen).half().to(dev)
+            rp.append(k, v, [0, np_b], mine, [0])
+    for max_pages in (157, 400):
+        out = rp.attention(q, indptr, flat, last, max_pages=max_pages)
+        assert rp.status() == 0
+        want = oracle_attention_from_pool(rp, q, pages, lens)
+        for b, n in enumerate(lens):
+            if n == 0:
+                assert torch.count_nonzero(out[b]) == 0
+            else:
+                assert rel_l2(out[b].cpu(), want[b]) < ATTN_TOL, (b, n)
+
+
+def test_rotated_attention_plain_call_directly_after_a_multi_page_append():
+    """Without LEANKV_ATTN_EARLY_FETCH the pre-rotated entry has plain stream-order semantics: queued
+    directly behind an append that fills many pages (no synchronisation in between) it must see all of
+    them. With the flag it may not be used there, which is why the flag is opt-in."""
+    import ctypes
+    import math
+
+    dev = _dev()
+    kv = workloads.kv_case(batch=4, n_q_heads=8, n_kv_heads=2, context=900, seed=13, device=dev)
+    B, H, T = 4, 2, 900
+    pps = (T + 15) // 16
+    rp = RawPool(B * pps, H, dev)
+    lib = rp.lib
+    flat = kv.page_ids.reshape(-1).contiguous()
+    indptr = torch.arange(0, (B + 1) * pps, pps, dtype=torch.int32, device=dev)
+    last = torch.full((B,), (T - 1) % 16 + 1, dtype=torch.int32, device=dev)
+    start = torch.zeros(B, dtype=torch.int32, device=dev)
+    q_rot = (kv.q.float() @ rp.Pi_k.t()).contiguous()
+    ws = torch.zeros(lib.leankv_tq_decode_attn_workspace_bytes(B, 8, H, pps), dtype=torch.uint8, device=dev)
+    out = torch.empty_like(kv.q)
+    st = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    for _ in range(3):                                   # back to back, nothing in between
+        rp.pool.zero_()
+        _native_check(lib.leankv_tq_pool_append(kv.k.data_ptr(), kv.v.data_ptr(), B, H, T, rp.Pi_k.data_ptr(),
+                                                rp.Pi_v.data_ptr(), rp.bounds.data_ptr(), rp.pool.data_ptr(),
+                                                rp.n_pages, indptr.data_ptr(), flat.data_ptr(), start.data_ptr(), st))
+        _native_check(lib.leankv_tq_decode_attn_rotated(q_rot.data_ptr(), out.data_ptr(), B, 8, H, rp.pool.data_ptr(),
+                                                        rp.n_pages, indptr.data_ptr(), flat.data_ptr(),
+                                                        last.data_ptr(), pps, rp.Pi_v.data_ptr(),
+                                                        rp.centroids_host.data_ptr(), 1.0 / math.sqrt(128.0),
+                                                        ws.data_ptr(), ws.numel(), 0, st))
+    torch.cuda.synchronize()
+    settled = rp.attention(kv.q, indptr.tolist(), flat.tolist(), last.tolist(), max_pages=pps)
+    assert rel_l2(out.cpu(), settled.cpu()) < 1e-4       # same pages, same kernel; only the query rotation's summation order differs
+    want = oracle_attention_from_pool(rp, kv.q, kv.page_ids.cpu().tolist(), [T] * B)
+    assert rel_l2(out.cpu(), want) < ATTN_TOL
+
+
+def _native_check(rc):
+    from leankv_b200 import _native
+
+    _native.check(rc, "C-ABI call")
+
+
+def test_pool_unpack_skips_page_ids_outside_the_pool():
+    dev = _dev()
+    kv = _small_kv(dev)
+    rp = RawPool(6, 2, dev)
+    rp.append(kv.k[:1, :, :40], kv.v[:1, :, :40], [0, 3], [4, 1, 2], [0])
+    good_idx, good_norms = rp.unpack([4, 1, 2], 40, 0)
+    idx, norms = rp.unpack([4, 99, -3], 40, 0)            # stale / foreign ids in the table
+    assert np.array_equal(idx[:, :16], good_idx[:, :16]) and np.array_equal(norms[:, :16], good_norms[:, :16])
+    assert not idx[:, 16:].any() and not norms[:, 16:].any()

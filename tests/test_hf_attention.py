@@ -124,3 +124,24 @@ def test_other_scale_is_refused():
     M._leankv_paged_cache.fused_decode = True
     with pytest.raises(RuntimeError):
         hf_attention.paged_attention_forward(M(), q, q, q, None, scaling=0.5)
+
+
+def test_mask_that_hides_cached_positions_is_refused():
+    """A padded batch or a sliding window would be ignored by the fused kernel: refuse instead."""
+    q = torch.zeros(2, 4, 1, 128)
+
+    class M:
+        layer_idx = 0
+        _leankv_paged_cache = StandInCache(1)
+
+    M._leankv_paged_cache.fused_decode = True
+    hidden = torch.ones(2, 1, 1, 5, dtype=torch.bool)
+    hidden[1, 0, 0, 0] = False
+    with pytest.raises(RuntimeError, match="attention mask"):
+        hf_attention.paged_attention_forward(M(), q, q, q, hidden)
+    additive = torch.zeros(2, 1, 1, 5)
+    additive[0, 0, 0, 2] = float("-inf")
+    with pytest.raises(RuntimeError, match="attention mask"):
+        hf_attention.paged_attention_forward(M(), q, q, q, additive)
+    assert not hf_attention._masks_something(torch.ones(2, 1, 1, 5, dtype=torch.bool))
+    assert not hf_attention._masks_something(torch.zeros(2, 1, 1, 5))

@@ -31,11 +31,22 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
         assert name in _native.SIGNATURES, f"{name} has no ctypes signature"
     assert sorted(_native.SIGNATURES) == names
-    assert lib.leankv_abi_version() == 1
+    assert lib.leankv_abi_version() == 2
     assert b"workspace" in lib.leankv_strerror(-3)
 
 
+def _no_device_for_made_up_pointers():
+    """The validation tests pass made-up addresses and rely on every call being refused before a
+    launch. Where a GPU is visible a regression of a check would launch a kernel on those addresses,
+    so the tests only run on machines without one (the build container)."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("made-up pointers are only passed where no kernel could be launched")
+
+
 def test_argument_validation_returns_codes_before_any_launch():
+    _no_device_for_made_up_pointers()
     lib = _native.lib()
     fake = 0x10000   # never dereferenced: validation fails first
     # N not a multiple of 8
@@ -72,6 +83,16 @@ def test_argument_validation_returns_codes_before_any_launch():
                                      fake, 0.1, fake, 16, None) == -3
     assert lib.leankv_tq_decode_attn(fake, fake, 0, 32, 8, fake, 4, fake, fake, fake, 4, fake, fake,
                                      fake, 0.1, fake, 16, None) == 0    # empty batch
+    # unknown flag bits of the pre-rotated entry are refused
+    assert lib.leankv_tq_decode_attn_rotated(fake, fake, 1, 32, 8, fake, 4, fake, fake, fake, 4, fake, fake, 0.1,
+                                             fake, 1 << 30, 2, None) == -1
+    # RMSNorm fused in: the output may not overlap the input row (other CTAs still read it)
+    segs1 = _native.Segments()
+    segs1.n_segments, segs1.seg_end[0], segs1.threshold[0] = 1, 4096, 0.1
+    assert lib.leankv_sparse_gemv_rmsnorm_f16(fake * 16, fake, fake * 2, 1e-5, fake, 4096, 4096, ctypes.byref(segs1),
+                                              None, fake * 4, 1 << 30, None, None) == -1
+    assert lib.leankv_sparse_swiglu_rmsnorm_f16(fake * 16, fake * 32, fake, fake * 2, 1e-5, fake + 4096, 4096, 4096,
+                                                0.1, 0.1, fake * 4, 1 << 30, None, None) == -1
 
 
 def test_workspace_sizes_are_modest():
@@ -240,6 +261,7 @@ def test_threshold_files_round_trip_in_the_reference_format(tmp_path, capsys):
 def test_argument_validation_of_the_decode_and_exchange_entry_points():
     """Glue kernels, batched glue kernels and the GEMV + all-reduce entry reject bad arguments with a
     status code before anything is launched (so this runs without a GPU)."""
+    _no_device_for_made_up_pointers()
     lib = _native.lib()
     fake, odd = 0x10000, 0x10002
     assert lib.leankv_rmsnorm_f16(None, None, fake, fake, 4096, 1e-5, None) == -1
