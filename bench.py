@@ -428,9 +428,16 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
     torch.cuda.synchronize()
     t_q = e0.elapsed_time(e1) * 1e-3 / len(pools)
     alg_q = 2 * B * H * T * (256 + 50)
-    out["tq_bulk_quantize_append_b16_t4096"] = {"us": t_q * 1e6, "algorithmic_bytes": alg_q,
-                                                "gbs": alg_q / t_q / 1e9, "fp32_gflops": 2 * B * H * T * 2 * 128 * 128 / t_q / 1e9,
-                                                "bound": "fp32 FMA"}
+    import ctypes
+
+    stats = (ctypes.c_ulonglong * 2)()
+    lib.leankv_tq_band_stats(stats, 1)
+    out["tq_bulk_quantize_append_b16_t4096"] = {
+        "us": t_q * 1e6, "algorithmic_bytes": alg_q, "gbs": alg_q / t_q / 1e9,
+        "rotation_gflops": 2 * B * H * T * 2 * 128 * 128 / t_q / 1e9,
+        "bound": "tensor (fp16 hi/lo split, three products) + exact fp32 chain inside the 1e-4 band" if stats[1]
+                 else "fp32 FMA",
+        "band_hit_fraction": (stats[0] / stats[1]) if stats[1] else None}
     # what the kernels wrote for sequence 0 (pool append, and the bulk quantize entry): compared code by code
     # with the CPU oracle by the baseline leg
     def nib(t):

@@ -171,6 +171,14 @@ int leankv_tq_pool_append(const void* k, const void* v, int B, int n_kv_heads, i
                           const int32_t* kv_indptr, const int32_t* kv_page_indices,
                           const int32_t* start_pos, void* stream);
 
+/* Appends of 16 or more tokens per sequence (prompt processing, where the reference quantizes the
+ * flushed tokens with one dense fp32 matmul, cache.py:136-142 / quantizer.py:119-129) run the
+ * rotation on tensor cores and re-derive every coordinate that lands within 1e-4 of a decision
+ * boundary with the sequential fp32 chain, so the codes are those of the definition above.
+ * stats[0] = coordinates re-derived, stats[1] = coordinates quantized on the current device since
+ * the last reset (synchronous copy; reset != 0 clears the counters). */
+int leankv_tq_band_stats(unsigned long long* stats /* host, 2 */, int reset);
+
 /* Pool -> reference format for pages of one sequence: codes as nibble-packed uint8
  * [n_kv_heads][n_tokens][64] and norms fp32 [n_kv_heads][n_tokens] (the fp16 pool
  * norm widened), for K (which = 0) or V (which = 1). */

@@ -77,6 +77,7 @@ SIGNATURES = {
     "leankv_tq_pool_append": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p]),
+    "leankv_tq_band_stats": (c_int, [POINTER(c_ulonglong), c_int]),
     "leankv_tq_pool_unpack": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p]),
     "leankv_tq_decode_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),

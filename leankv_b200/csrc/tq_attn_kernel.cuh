@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     __shared__ __align__(8) uint64_t s_bar[kAttnWarps][kStages];
     __shared__ __align__(16) float s_res[kAttnWarps][kGroup][kDim];   // warp results, later scratch of the merge
     __shared__ float s_m[kAttnWarps][kGroup], s_l[kAttnWarps][kGroup];
+    __shared__ int s_ip[kAttnThreads];                                // kv_indptr of a small batch
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -62,11 +63,19 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     // ---- this CTA's share of the flat page list ----
     // With early fetch everything up to the first pdl_begin() below runs while the launch before this
     // one may still be executing; it reads only the page table and pages that older launches wrote.
-    const int ip0 = p.indptr[0];
-    const long long F = (long long)H * (p.indptr[p.B] - ip0);
+    // A batch of fewer than 128 sequences has its whole indptr fetched in one go (one memory round trip
+    // before the page ids can be asked for); larger batches read it from global memory as needed.
+    const bool small_b = p.B < kAttnThreads;
+    if (small_b) {
+        if (tid <= p.B) s_ip[tid] = p.indptr[tid];
+        __syncthreads();
+    }
+    auto ip = [&](int i) -> int { return small_b ? s_ip[i] : p.indptr[i]; };
+    const int ip0 = ip(0);
+    const long long F = (long long)H * (ip(p.B) - ip0);
     // sequences without pages produce zeros; CTAs share them out
     for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
-        if (p.indptr[b + 1] - p.indptr[b] <= 0) {
+        if (ip(b + 1) - ip(b) <= 0) {
             if (!waited) { pdl_begin(); waited = true; }
             __half* o = p.out + (size_t)b * Hq * kDim;
             for (int i = tid; i < Hq * kDim; i += kAttnThreads) o[i] = __float2half_rn(0.f);
@@ -91,15 +100,15 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         while (hi - lo > 1) {
             const int step = (hi - lo + kAttnThreads - 1) / kAttnThreads;
             const long long idx = (long long)lo + (long long)(tid + 1) * step;
-            const bool pred = idx < hi && (long long)H * (p.indptr[idx] - ip0) <= f_lo;
+            const bool pred = idx < hi && (long long)H * (ip((int)idx) - ip0) <= f_lo;
             const int cnt = __syncthreads_count(pred);
             lo += cnt * step;
             hi = min(hi, lo + step);
         }
         b = lo;
     }
-    int seq_pg0 = p.indptr[b];
-    int n_b = p.indptr[b + 1] - seq_pg0;
+    int seq_pg0 = ip(b);
+    int n_b = ip(b + 1) - seq_pg0;
     int kvh, pg;
     {
         const long long r = f_lo - (long long)H * (seq_pg0 - ip0);
@@ -165,12 +174,13 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         }
 
         // ---- query as the A operand of the integer score MMA ----
-        // Rows 0..3 of the 16 x 32 tile are the four heads' high digits against the centroids' high
-        // digits; rows 8..11 pair the low digits of one side with the high digits of the other; the
-        // rest is zero. Lane (g, t) with g < 4 holds head g, rotated coordinates 32t .. 32t+31;
-        // k-step s covers coordinates 32t + 4s .. +3.
-        uint32_t qh[8], ql[8];
-        float kscale = 0.f;      // score per integer unit of (256 * HH + MID), before the key norm
+        // One m16n8k32 step covers 32 coordinates: rows 0..7 hold the high digit of the query, rows 8..15
+        // its low digit (heads 0..3, repeated in rows 4..7 so that all lanes do the same work). Multiplied
+        // with the centroids' high digits that gives HH (rows 0..7) and q_lo x c_hi (rows 8..15); with the
+        // centroids' low digits q_hi x c_lo and q_lo x c_lo. Lane (g, t) holds head g & 3, rotated
+        // coordinates 32t .. 32t+31; k-block kb covers coordinates 32t + 8kb .. +7.
+        uint32_t qa[4][4];
+        float kscale;            // score per integer unit of (256 * HH + MID), before the key norm
         {
             const int head = g & 3;
             const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
@@ -186,75 +196,79 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             const float uq = amax > 0.f ? amax * (1.0f / kFixedMax) : 1.0f;
             const float inv = 1.0f / uq;
             kscale = 256.0f * uq * p.c_unit * p.qscale;
+            auto digits = [&](float x, int sh, uint32_t& hi, uint32_t& lo) {
+                const int qi = __float2int_rn(x * inv);
+                const int l8 = ((qi + 128) & 255) - 128;             // balanced low digit in [-128, 127]
+                const int h8 = (qi - l8) >> 8;                        // |qi| <= 32512 keeps this in [-127, 127]
+                hi |= (uint32_t)(h8 & 255) << sh;
+                lo |= (uint32_t)(l8 & 255) << sh;
+            };
 #pragma unroll
             for (int s = 0; s < 8; ++s) {
-                const float e[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
                 uint32_t hi = 0, lo = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int qi = __float2int_rn(e[i] * inv);
-                    const int l8 = ((qi + 128) & 255) - 128;         // balanced low digit in [-128, 127]
-                    const int h8 = (qi - l8) >> 8;                    // |qi| <= 32512 keeps this in [-127, 127]
-                    hi |= (uint32_t)(h8 & 255) << (8 * i);
-                    lo |= (uint32_t)(l8 & 255) << (8 * i);
-                }
-                qh[s] = g < 4 ? hi : 0u;
-                ql[s] = g < 4 ? lo : 0u;
+                digits(v[s].x, 0, hi, lo);
+                digits(v[s].y, 8, hi, lo);
+                digits(v[s].z, 16, hi, lo);
+                digits(v[s].w, 24, hi, lo);
+                qa[s >> 1][2 * (s & 1)] = hi;          // a0 / a2: rows 0..7, k 0..15 / 16..31
+                qa[s >> 1][2 * (s & 1) + 1] = lo;      // a1 / a3: rows 8..15
             }
         }
 
-        float m_ref = -INFINITY, l_run = 0.f;     // lanes g < 4: head g, this lane's four tokens per page
+        float m_ref = -INFINITY, l_run = 0.f;     // head g & 3, this lane's four tokens per page
         float acc[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        const int last_len = min(max(p.last_len[b], 1), 16);
 
-        int n_done = 0;
-        for (int i = 0; i < n_my; ++i) {
-            const unsigned itn = it + i;
-            const int s = itn & (kStages - 1);
-            if ((i & 31) == 0 && i > 0) {
-                ids_cur = ids_nxt;
-                ids_nxt = load_ids(i + 32);
-            }
-            // the verdict is made warp-uniform so that no lane is left behind at a shuffle
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (itn / kStages) & 1))) {
-                failed = true;
-                break;
-            }
-            n_done = i + 1;
-            const int page = __shfl_sync(0xffffffffu, ids_cur, i & 31);
-            const int i_next = i + kStages;
-            const int next_page = __shfl_sync(0xffffffffu, (i_next >> 5) == (i >> 5) ? ids_cur : ids_nxt, i_next & 31);
-            const int n_valid = page < 0 ? 0 : ((w_lo + i == n_b - 1) ? min(max(p.last_len[b], 1), 16) : 16);
-
-            const uint8_t* stage = &s_ring[warp][s][0][0];
+        // One page. kMasked: the page may hold fewer than 16 valid tokens (a sequence's last page, or a page
+        // id that was rejected); the common case carries no masking code.
+        auto do_page = [&](const uint8_t* stage, int n_valid, auto masked_tag) {
+            constexpr bool kMasked = decltype(masked_tag)::value;
             const uint32_t* kw = reinterpret_cast<const uint32_t*>(stage);
             const uint32_t* kn2 = reinterpret_cast<const uint32_t*>(stage + kNormOffsetBytes);
             const uint32_t* vw = reinterpret_cast<const uint32_t*>(stage + kChunkBytes);
             const uint32_t* vn2 = reinterpret_cast<const uint32_t*>(stage + kChunkBytes + kNormOffsetBytes);
 
             // ---- scores: D[row][token], tokens 0..7 in tile 0 and 8..15 in tile 1 ----
-            int d0[4] = {kBiasBits, kBiasBits, kBiasBits, kBiasBits};
-            int d1[4] = {kBiasBits, kBiasBits, kBiasBits, kBiasBits};
+            int dh0[4], dl0[4], dh1[4], dl1[4];       // centroid high / low digits, tile 0 / 1
             {
                 const Unit ua = load_unit(kw, lane), ub = load_unit(kw, 32 + lane);
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const uint32_t sa = ua.s[q >> 1] >> (16 * (q & 1));
-                    const uint32_t sb = ub.s[q >> 1] >> (16 * (q & 1));
-                    mma_s8_16832(d0, qh[q], ql[q], 0u, qh[q], __byte_perm(p.kh0, p.kh1, sa), __byte_perm(p.kl0, p.kl1, sa));
-                    mma_s8_16832(d1, qh[q], ql[q], 0u, qh[q], __byte_perm(p.kh0, p.kh1, sb), __byte_perm(p.kl0, p.kl1, sb));
+                for (int kb = 0; kb < 4; ++kb) {
+                    const uint32_t sa = ua.s[kb], sa2 = sa >> 16, sb = ub.s[kb], sb2 = sb >> 16;
+                    const uint32_t ah0 = __byte_perm(p.kh0, p.kh1, sa), ah1 = __byte_perm(p.kh0, p.kh1, sa2);
+                    const uint32_t al0 = __byte_perm(p.kl0, p.kl1, sa), al1 = __byte_perm(p.kl0, p.kl1, sa2);
+                    const uint32_t bh0 = __byte_perm(p.kh0, p.kh1, sb), bh1 = __byte_perm(p.kh0, p.kh1, sb2);
+                    const uint32_t bl0 = __byte_perm(p.kl0, p.kl1, sb), bl1 = __byte_perm(p.kl0, p.kl1, sb2);
+                    if (kb == 0) {
+                        mma_s8_16832_bias(dh0, qa[kb], ah0, ah1);
+                        mma_s8_16832_bias(dl0, qa[kb], al0, al1);
+                        mma_s8_16832_bias(dh1, qa[kb], bh0, bh1);
+                        mma_s8_16832_bias(dl1, qa[kb], bl0, bl1);
+                    } else {
+                        mma_s8_16832(dh0, qa[kb], ah0, ah1);
+                        mma_s8_16832(dl0, qa[kb], al0, al1);
+                        mma_s8_16832(dh1, qa[kb], bh0, bh1);
+                        mma_s8_16832(dl1, qa[kb], bl0, bl1);
+                    }
                 }
             }
             // tokens of this lane: 2t, 2t+1 (tile 0) and 8+2t, 9+2t (tile 1); norms as fp16 pairs
             const float2 kna = h2_to_f2(kn2[t]), knb = h2_to_f2(kn2[4 + t]);
             float2 vna = h2_to_f2(vn2[t]), vnb = h2_to_f2(vn2[4 + t]);
+            // 256 * HH + (q_lo c_hi + q_hi c_lo): c0/c1 of the high-digit tile are HH, its c2/c3 and the
+            // low-digit tile's c0/c1 are the two mixed sums (each sum carries the accumulator bias)
+            auto val = [](const int (&dh)[4], const int (&dl)[4], int c) -> float {
+                const float mid = (__int_as_float(dh[2 + c]) - kBiasF) + (__int_as_float(dl[c]) - kBiasF);
+                return fmaf(__int_as_float(dh[c]) - kBiasF, 256.f, mid);
+            };
             float sc[4];
-            sc[0] = fmaf(__int_as_float(d0[0]) - kBiasF, 256.f, __int_as_float(d0[2]) - kBiasF) * (kscale * kna.x);
-            sc[1] = fmaf(__int_as_float(d0[1]) - kBiasF, 256.f, __int_as_float(d0[3]) - kBiasF) * (kscale * kna.y);
-            sc[2] = fmaf(__int_as_float(d1[0]) - kBiasF, 256.f, __int_as_float(d1[2]) - kBiasF) * (kscale * knb.x);
-            sc[3] = fmaf(__int_as_float(d1[1]) - kBiasF, 256.f, __int_as_float(d1[3]) - kBiasF) * (kscale * knb.y);
-            if (n_valid < 16) {                      // last page of a sequence (or a rejected page)
+            sc[0] = val(dh0, dl0, 0) * (kscale * kna.x);
+            sc[1] = val(dh0, dl0, 1) * (kscale * kna.y);
+            sc[2] = val(dh1, dl1, 0) * (kscale * knb.x);
+            sc[3] = val(dh1, dl1, 1) * (kscale * knb.y);
+            if (kMasked) {
                 if (2 * t >= n_valid) { sc[0] = -INFINITY; vna.x = 0.f; }
                 if (2 * t + 1 >= n_valid) { sc[1] = -INFINITY; vna.y = 0.f; }
                 if (8 + 2 * t >= n_valid) { sc[2] = -INFINITY; vnb.x = 0.f; }
@@ -263,9 +277,9 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
 
             // ---- online softmax (log2 domain; the scores carry scale * log2 e) ----
             const float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-            if (__any_sync(0xffffffffu, g < 4 && mx > m_ref + kRescaleSlack)) {
-                // some head's reference value moves: its four lanes agree on the new one, and every
-                // lane rescales the accumulator columns of the heads it holds
+            if (__any_sync(0xffffffffu, mx > m_ref + kRescaleSlack)) {
+                // some head's reference value moves: its lanes agree on the new one, and every lane
+                // rescales the accumulator columns of the heads it holds
                 float mh = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, 2));
                 float fsc = 1.0f;
@@ -287,10 +301,11 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             const float p2 = ex2_approx(sc[2] - m_safe), p3 = ex2_approx(sc[3] - m_safe);
             l_run += (p0 + p1) + (p2 + p3);
             // Probabilities (times value norms) are already where the value MMA wants its B operand:
-            // rows = tokens 2t, 2t+1, 2t+8, 2t+9, column g = head g (columns 4..7 stay zero). fp16 rounding
-            // of the probabilities is independent from token to token and averages out over the sum.
-            const uint32_t b0 = g < 4 ? pack_h2(p0 * vna.x, p1 * vna.y) : 0u;
-            const uint32_t b1 = g < 4 ? pack_h2(p2 * vnb.x, p3 * vnb.y) : 0u;
+            // rows = tokens 2t, 2t+1, 2t+8, 2t+9, column g = head g & 3 (columns 4..7 repeat 0..3 and are
+            // never stored). fp16 rounding of the probabilities is independent from token to token and
+            // averages out over the sum.
+            const uint32_t b0 = pack_h2(p0 * vna.x, p1 * vna.y);
+            const uint32_t b1 = pack_h2(p2 * vnb.x, p3 * vnb.y);
             {
                 const Unit ua = load_unit(vw, lane), ub = load_unit(vw, 32 + lane);
 #pragma unroll
@@ -303,6 +318,30 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                               __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362), b0, b1);
                 }
             }
+        };
+
+        int n_done = 0;
+        for (int i = 0; i < n_my; ++i) {
+            const unsigned itn = it + i;
+            const int s = itn & (kStages - 1);
+            if ((i & 31) == 0 && i > 0) {
+                ids_cur = ids_nxt;
+                ids_nxt = load_ids(i + 32);
+            }
+            // the verdict is made warp-uniform so that no lane is left behind at a shuffle
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (itn / kStages) & 1))) {
+                failed = true;
+                break;
+            }
+            n_done = i + 1;
+            const int page = __shfl_sync(0xffffffffu, ids_cur, i & 31);
+            const int i_next = i + kStages;
+            const int next_page = __shfl_sync(0xffffffffu, (i_next >> 5) == (i >> 5) ? ids_cur : ids_nxt, i_next & 31);
+            const uint8_t* stage = &s_ring[warp][s][0][0];
+            if (page < 0 || w_lo + i == n_b - 1)
+                do_page(stage, page < 0 ? 0 : last_len, std::true_type{});
+            else
+                do_page(stage, 16, std::false_type{});
             __syncwarp();   // every lane has finished reading this stage
             if (lane == 0 && i_next < n_my) issue(itn + kStages, next_page);
         }
@@ -318,7 +357,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         // ---- warp result -> shared memory ----
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-        if (g < 4 && t == 0) {
+        if (g < 4 && t == 0) {                     // lanes g >= 4 hold copies of heads 0..3
             s_m[warp][g] = m_ref;
             s_l[warp][g] = l_run;
         }
@@ -395,6 +434,15 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 if (staged)
                     for (int i = tid; i < n_seg * 2 * kGroup; i += kAttnThreads)
                         s_ml[i] = ld_cg_f32(part_of(i >> 3) + kGroup * kDim + (i & 7));
+                // the value rows of the first kMergeBatch pieces travel in the same round trip
+                constexpr int kMergeBatch = 8;
+                float ov0[kMergeBatch][kGroup];
+#pragma unroll
+                for (int k = 0; k < kMergeBatch; ++k) {
+                    const float* pc = part_of(k < n_seg ? k : 0) + tid;
+#pragma unroll
+                    for (int h = 0; h < kGroup; ++h) ov0[k][h] = k < n_seg ? ld_cg_f32(pc + h * kDim) : 0.f;
+                }
                 __syncthreads();
                 float mg[kGroup];
 #pragma unroll
@@ -405,8 +453,20 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                     o[h] = 0.f;
                     lh[h] = 0.f;
                 }
+#pragma unroll
+                for (int k = 0; k < kMergeBatch; ++k) {
+                    if (k < n_seg) {
+#pragma unroll
+                        for (int h = 0; h < kGroup; ++h) {
+                            const float mc = ml(k, h);
+                            const float fc = mc == -INFINITY ? 0.f : ex2_approx(mc - mg[h]);
+                            o[h] = fmaf(fc, ov0[k][h], o[h]);
+                            lh[h] = fmaf(fc, ml(k, kGroup + h), lh[h]);
+                        }
+                    }
+                }
 #pragma unroll 4
-                for (int k = 0; k < n_seg; ++k) {
+                for (int k = kMergeBatch; k < n_seg; ++k) {
                     const float* pc = part_of(k) + tid;
                     float ov[kGroup];
 #pragma unroll
@@ -488,8 +548,8 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 kvh = 0;
                 do {
                     ++b;
-                    seq_pg0 = p.indptr[b];
-                    n_b = p.indptr[b + 1] - seq_pg0;
+                    seq_pg0 = ip(b);
+                    n_b = ip(b + 1) - seq_pg0;
                 } while (n_b <= 0 && b + 1 < p.B);
             }
         }

@@ -12,6 +12,8 @@
 // order to its BLAS, so a code can differ from it only where y lies within rounding
 // distance of a decision boundary.
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tq_layout.cuh"
 
@@ -352,6 +354,12 @@ __global__ void __launch_bounds__(128) tq_pool_append_kernel(const AppendParams 
     }
 }
 
+#include "tq_append_tc.cuh"
+
+// Coordinates decided by the exact chain / coordinates quantized by the tensor-core append, per device,
+// since the last reset (read by leankv_tq_band_stats).
+__device__ unsigned long long g_band_stats[2];
+
 struct UnpackParams {
     const uint8_t* pool;
     int n_pages, H;
@@ -384,6 +392,17 @@ __global__ void tq_pool_unpack_kernel(const UnpackParams p) {
         if (byte == 0)
             p.norms[ht] = __half2float(reinterpret_cast<const __half*>(chunk + kNormOffsetBytes)[slot]);
     }
+}
+
+// LEANKV_TQ_APPEND=fp32 keeps multi-token appends on the fp32 kernel (the definition the tensor-core
+// path is tested against).
+bool tc_append_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char* e = std::getenv("LEANKV_TQ_APPEND");
+        state = (e != nullptr && e[0] == 'f') ? 0 : 1;
+    }
+    return state == 1;
 }
 
 int check_tq_common(long long n_vec, int dim, int bits) {
@@ -502,6 +521,30 @@ extern "C" int leankv_tq_pool_append(const void* k, const void* v, int B, int n_
     p.start_pos = start_pos;
     // T_new tokens starting anywhere inside a page touch at most (T_new + 14) / 16 + 1 pages.
     const int groups = (T_new + 14) / 16 + 1;
+    if (T_new >= 16 && tc_append_enabled()) {
+        // prompt-sized appends: rotation on tensor cores, codes identical to the fp32 kernels
+        AppendTcParams tp{};
+        tp.a = p;
+        tp.groups = (groups + 3) / 4;
+        tp.n_tiles = 2LL * B * n_kv_heads * tp.groups;
+        void* stats = nullptr;
+        LEANKV_CUDA_TRY(cudaGetSymbolAddress(&stats, g_band_stats));
+        tp.stats = static_cast<unsigned long long*>(stats);
+        int dev = 0;
+        LEANKV_CUDA_TRY(cudaGetDevice(&dev));
+        constexpr int kMaxDevices = 64;
+        static bool attr_done[kMaxDevices] = {};
+        if (dev < 0 || dev >= kMaxDevices || !attr_done[dev]) {
+            LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_pool_append_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)kTcSmemBytes));
+            if (dev >= 0 && dev < kMaxDevices) attr_done[dev] = true;
+        }
+        const long long slots = 2LL * sm_count();
+        const int grid_tc = (int)(tp.n_tiles < slots ? tp.n_tiles : slots);
+        LEANKV_CUDA_TRY(launch_kernel(tq_pool_append_tc_kernel, dim3(grid_tc), dim3(kTcThreads), kTcSmemBytes,
+                                      static_cast<cudaStream_t>(stream), tp));
+        return LEANKV_OK;
+    }
     if (groups > 65535) return LEANKV_ELIMIT;
     dim3 grid(B * n_kv_heads, groups, 2);
     if (T_new == 1)
@@ -532,5 +575,15 @@ extern "C" int leankv_tq_pool_unpack(const void* pool, int n_pages, int n_kv_hea
     if (blocks > sm_count() * 16LL) blocks = sm_count() * 16LL;
     tq_pool_unpack_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_tq_band_stats(unsigned long long* stats /* host, 2 */, int reset) {
+    if (!stats) return LEANKV_EINVAL;
+    LEANKV_CUDA_TRY(cudaMemcpyFromSymbol(stats, g_band_stats, sizeof(unsigned long long) * 2));
+    if (reset) {
+        const unsigned long long zero[2] = {0ull, 0ull};
+        LEANKV_CUDA_TRY(cudaMemcpyToSymbol(g_band_stats, zero, sizeof(zero)));
+    }
     return LEANKV_OK;
 }

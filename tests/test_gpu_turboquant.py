@@ -389,3 +389,57 @@ def test_pool_unpack_skips_page_ids_outside_the_pool():
     idx, norms = rp.unpack([4, 99, -3], 40, 0)            # stale / foreign ids in the table
     assert np.array_equal(idx[:, :16], good_idx[:, :16]) and np.array_equal(norms[:, :16], good_norms[:, :16])
     assert not idx[:, 16:].any() and not norms[:, 16:].any()
+
+
+_POOL_HASH_SNIPPET = r"""
+import ctypes, hashlib, sys, torch
+sys.path.insert(0, %(root)r)
+from leankv_b200 import _native, workloads
+from leankv_b200.turboquant import codebook, rotation
+dev = torch.device("cuda:0")
+lib = _native.lib()
+kv = workloads.kv_case(device=dev)
+B, H, T = 16, 8, 4096
+Pk = rotation.generate_rotation_matrix(128, dev, torch.float32, 42).contiguous()
+Pv = rotation.generate_rotation_matrix(128, dev, torch.float32, 43).contiguous()
+bounds = codebook.get_codebook_tensors(128, 3, "cpu")[1][1:-1].float().contiguous().to(dev)
+indptr = torch.arange(0, (B + 1) * 256, 256, dtype=torch.int32, device=dev)
+flat = kv.page_ids.reshape(-1).contiguous()
+pool = torch.zeros(kv.n_pages, 2, H, 800, dtype=torch.uint8, device=dev)
+# two launches: 1000 tokens first, the rest from position 1000 (a start inside a page, odd pairs for V)
+for t0, t1 in ((0, 1000), (1000, T)):
+    k, v = kv.k[:, :, t0:t1].contiguous(), kv.v[:, :, t0:t1].contiguous()
+    start = torch.full((B,), t0, dtype=torch.int32, device=dev)
+    _native.check(lib.leankv_tq_pool_append(k.data_ptr(), v.data_ptr(), B, H, t1 - t0, Pk.data_ptr(), Pv.data_ptr(),
+                                            bounds.data_ptr(), pool.data_ptr(), kv.n_pages, indptr.data_ptr(),
+                                            flat.data_ptr(), start.data_ptr(), None), "append")
+torch.cuda.synchronize()
+stats = (ctypes.c_ulonglong * 2)()
+lib.leankv_tq_band_stats(stats, 0)
+print("POOL", hashlib.sha256(pool.cpu().numpy().tobytes()).hexdigest(), stats[0], stats[1])
+"""
+
+
+def test_tensor_core_append_writes_the_same_pool_as_the_fp32_kernel_on_all_of_config3():
+    """All 16 sequences x 8 heads x 4096 tokens, K and V (134 M coordinates), appended in two launches:
+    the pool written with the rotation on tensor cores must equal, byte for byte, the pool written by the
+    sequential-fma fp32 kernel that defines the codes. Each path runs in a process of its own (the path is
+    chosen once per process by LEANKV_TQ_APPEND)."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    out = {}
+    for mode in ("tc", "fp32"):
+        env = dict(os.environ, LEANKV_TQ_APPEND=mode)
+        r = subprocess.run([sys.executable, "-c", _POOL_HASH_SNIPPET % {"root": ROOT}], env=env,
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        line = [ln for ln in r.stdout.splitlines() if ln.startswith("POOL")][-1].split()
+        out[mode] = (line[1], int(line[2]), int(line[3]))
+    print("tensor-core append: coordinates re-derived exactly / quantized:", out["tc"][1], "/", out["tc"][2])
+    assert out["tc"][0] == out["fp32"][0]
+    assert out["tc"][2] == 2 * 16 * 8 * 4096 * 128 and out["fp32"][2] == 0
+    assert 0 < out["tc"][1] < 0.02 * out["tc"][2]
