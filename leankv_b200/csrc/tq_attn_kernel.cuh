@@ -7,7 +7,9 @@
 // share is cut at pair boundaries into segments; the CTA's four warps split each segment's pages,
 // their results are merged in shared memory, and a segment that is not a whole pair leaves a
 // partial result in the workspace. The last CTA to arrive for a pair merges the partials in CTA
-// order and applies the inverse value rotation.
+// order and applies the inverse value rotation. When there are at least as many CTAs as pairs the
+// CTA count is rounded down to a multiple of the pair count, so that for sequences of equal length
+// (a single sequence in particular) no share crosses a pair boundary.
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -19,11 +21,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // maximum exceeds the reference value by more than this many log2 units; until then probabilities
 // are taken relative to the (stale) reference and stay below 2^kRescaleSlack.
 constexpr float kRescaleSlack = 5.0f;
+// Reference value before any valid token has been seen: finite, so that no special case is needed
+// (any real score exceeds it by more than the slack, and 2^(kNoRef - m) is 0).
+constexpr float kNoRef = -1.0e30f;
 
 // Integer MMA accumulators start from the bit pattern of 1.5 * 2^23: adding an integer |n| < 2^22 to
 // that pattern gives the bit pattern of the float 1.5 * 2^23 + n, so the sums come out of the tensor
 // core as floats without a conversion instruction.
-constexpr int kBiasBits = 0x4B400000;
 constexpr float kBiasF = 12582912.0f;
 
 template <int kOcc>   // resident CTAs per SM the register allocation is held to
@@ -35,16 +39,13 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     __shared__ float s_m[kAttnWarps][kGroup], s_l[kAttnWarps][kGroup];
     __shared__ int s_ip[kAttnThreads];                                // kv_indptr of a small batch
     __shared__ int s_last;
+    static_assert(kStages == 4, "the page loop is unrolled over a 4-slot ring");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int H = p.H, Hq = H * kGroup;
-    const bool early = (p.flags & LEANKV_ATTN_EARLY_FETCH) != 0;
-    bool waited = false;
-    if (!early) {
-        pdl_begin();
-        waited = true;
-    }
+    bool waited = (p.flags & LEANKV_ATTN_EARLY_FETCH) == 0;
+    if (waited) pdl_begin();
     // Pull the inverse rotation (a constant, 64 KB) towards L2 early: whichever CTA ends up merging
     // needs it at the very end of the critical path.
     if (blockIdx.x == 0)
@@ -86,12 +87,23 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         long long cap = F / kMinPagesPerCta;
         if (cap < 1) cap = 1;
         if (C > cap) C = cap;
+        const long long pairs = (long long)p.B * H;
+        if (C >= pairs) C -= C % pairs;
     }
     if (F <= 0 || (long long)blockIdx.x >= C) {
         if (!waited) pdl_begin();
         return;
     }
-    const long long f_lo = (long long)blockIdx.x * F / C, f_hi = ((long long)blockIdx.x + 1) * F / C;
+    // floor(c * F / C) and its inverse; 32-bit arithmetic when the products fit (the usual case)
+    const bool fits32 = (F + 1) * C + F < (1ll << 32);
+    auto share_start = [&](long long c) -> long long {
+        return fits32 ? (long long)((unsigned)c * (unsigned)F / (unsigned)C) : c * F / C;
+    };
+    auto cta_of = [&](long long f) -> int {        // the CTA whose share holds flat page f
+        return fits32 ? (int)(((unsigned)(f + 1) * (unsigned)C + (unsigned)F - 1u) / (unsigned)F) - 1
+                      : (int)(((f + 1) * C + F - 1) / F) - 1;
+    };
+    const long long f_lo = share_start(blockIdx.x), f_hi = share_start((long long)blockIdx.x + 1);
 
     // sequence that holds flat page f_lo: the last b with H * (indptr[b] - indptr[0]) <= f_lo
     int b;
@@ -111,15 +123,16 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     int n_b = ip(b + 1) - seq_pg0;
     int kvh, pg;
     {
-        const long long r = f_lo - (long long)H * (seq_pg0 - ip0);
-        kvh = (int)(r / n_b);
+        const long long r = f_lo - (long long)H * (seq_pg0 - ip0);    // < H * n_b
+        kvh = fits32 ? (int)((unsigned)r / (unsigned)n_b) : (int)(r / n_b);
         pg = (int)(r - (long long)kvh * n_b);
     }
 
-    const uint8_t* pool_base = p.pool;
     const size_t page_stride = (size_t)2 * H * kChunkBytes;       // K chunk of a page -> next page
     const size_t kv_stride = (size_t)H * kChunkBytes;             // K chunk -> V chunk of that page
-    unsigned it = 0;                 // pages this warp has put through its ring so far
+    const int l4 = lane & 3;
+    unsigned phase = 0;              // bit s: parity the next wait on ring slot s looks for
+    unsigned inflight = 0;           // bit s: a copy into ring slot s has been issued and not yet waited for
     bool failed = false;             // a bounded wait gave up: the warp stops using its ring
 
     for (long long f = f_lo; f < f_hi;) {
@@ -130,47 +143,43 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         const int w_lo = pg + (int)(((long long)seg_len * warp) / kAttnWarps);
         const int w_hi = pg + (int)(((long long)seg_len * (warp + 1)) / kAttnWarps);
         const int n_my = failed ? 0 : w_hi - w_lo;
-        const uint8_t* pool_kvh = pool_base + (size_t)kvh * kChunkBytes;
-        auto issue = [&](unsigned itn, int page) {                     // lane 0 only
-            const uint32_t s = itn & (kStages - 1);
+        const uint8_t* pool_kvh = p.pool + (size_t)kvh * kChunkBytes;
+        // lane s (s < 4) feeds ring slot s
+        auto issue = [&](int page) {
             const uint8_t* src = pool_kvh + (size_t)(page < 0 ? 0 : page) * page_stride;
-            mbar_expect_tx(bar0 + 8 * s, 2 * kChunkBytes);
-            bulk_g2s(ring0 + s * 2 * kChunkBytes, src, kChunkBytes, bar0 + 8 * s);
-            bulk_g2s(ring0 + s * 2 * kChunkBytes + kChunkBytes, src + kv_stride, kChunkBytes, bar0 + 8 * s);
+            const uint32_t bar = bar0 + 8 * l4, dst = ring0 + l4 * 2 * kChunkBytes;
+            mbar_expect_tx(bar, 2 * kChunkBytes);
+            bulk_g2s(dst, src, kChunkBytes, bar);
+            bulk_g2s(dst + kChunkBytes, src + kv_stride, kChunkBytes, bar);
         };
-        // lane i keeps the page id of the warp's (32 * batch + i)-th page; the next batch is fetched a
-        // batch ahead. Out-of-range ids are flagged once and read as a page without valid tokens.
-        auto load_ids = [&](int first) -> int {
+        // Page ids travel in groups of four: lane (any g, l4) holds the id of page base + l4 (lanes with
+        // equal l4 read the same word). Ids outside the pool are flagged once and read as pages without
+        // valid tokens.
+        auto fetch = [&](int base) -> int {
             int id = 0;
-            if (first + lane < n_my) {
-                id = p.indices[seq_pg0 + w_lo + first + lane];
+            if (base + l4 < n_my) {
+                id = p.indices[seq_pg0 + w_lo + base + l4];
                 if (id < 0 || id >= p.n_pages) {
                     id = -1;
-                    atomicOr(p.status, kStatusBadPage);
+                    if (lane < 4) atomicOr(p.status, kStatusBadPage);
                 }
             }
             return id;
         };
-        int ids_cur = load_ids(0), ids_nxt = load_ids(32);
+        int id_cur = fetch(0), id_nxt = fetch(kStages);
         // first copies; before the dependency wait the sequence's last page (the one the preceding
         // launch may be writing the new token into) is left out and issued right after the wait
-        const int i_seq_last = n_b - 1 - w_lo;
-        bool held_back = false;
-#pragma unroll
-        for (int s = 0; s < kStages; ++s) {
-            const int pgid = __shfl_sync(0xffffffffu, ids_cur, s);
-            if (s < n_my) {
-                if (!waited && s == i_seq_last) held_back = true;
-                else if (lane == 0) issue(it + s, pgid);
+        {
+            const int i_seq_last = n_b - 1 - w_lo;
+            const bool mine0 = lane < kStages && lane < n_my;
+            const bool hold = !waited && lane == i_seq_last;
+            if (mine0 && !hold) issue(id_cur);
+            if (!waited) {
+                pdl_begin();
+                waited = true;
+                if (mine0 && hold) issue(id_cur);
             }
-        }
-        if (!waited) {
-            pdl_begin();
-            waited = true;
-            if (held_back) {
-                const int pgid = __shfl_sync(0xffffffffu, ids_cur, i_seq_last);
-                if (lane == 0) issue(it + i_seq_last, pgid);
-            }
+            inflight |= (1u << min(n_my, kStages)) - 1u;
         }
 
         // ---- query as the A operand of the integer score MMA ----
@@ -215,7 +224,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             }
         }
 
-        float m_ref = -INFINITY, l_run = 0.f;     // head g & 3, this lane's four tokens per page
+        float m_ref = kNoRef, l_run = 0.f;        // head g & 3, this lane's four tokens per page
         float acc[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
@@ -258,35 +267,43 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             const float2 kna = h2_to_f2(kn2[t]), knb = h2_to_f2(kn2[4 + t]);
             float2 vna = h2_to_f2(vn2[t]), vnb = h2_to_f2(vn2[4 + t]);
             // 256 * HH + (q_lo c_hi + q_hi c_lo): c0/c1 of the high-digit tile are HH, its c2/c3 and the
-            // low-digit tile's c0/c1 are the two mixed sums (each sum carries the accumulator bias)
+            // low-digit tile's c0/c1 are the two mixed sums. Every sum carries the accumulator bias; all
+            // three subtractions are exact.
             auto val = [](const int (&dh)[4], const int (&dl)[4], int c) -> float {
-                const float mid = (__int_as_float(dh[2 + c]) - kBiasF) + (__int_as_float(dl[c]) - kBiasF);
+                const float mid = (__int_as_float(dh[2 + c]) - 2.f * kBiasF) + __int_as_float(dl[c]);
                 return fmaf(__int_as_float(dh[c]) - kBiasF, 256.f, mid);
             };
-            float sc[4];
-            sc[0] = val(dh0, dl0, 0) * (kscale * kna.x);
-            sc[1] = val(dh0, dl0, 1) * (kscale * kna.y);
-            sc[2] = val(dh1, dl1, 0) * (kscale * knb.x);
-            sc[3] = val(dh1, dl1, 1) * (kscale * knb.y);
+            const float v0 = val(dh0, dl0, 0), v1 = val(dh0, dl0, 1), v2 = val(dh1, dl1, 0), v3 = val(dh1, dl1, 1);
+            const float k0 = kscale * kna.x, k1 = kscale * kna.y, k2 = kscale * knb.x, k3 = kscale * knb.y;
+            // scores relative to the reference value (log2 domain; the scale carries log2 e)
+            float s0 = fmaf(v0, k0, -m_ref), s1 = fmaf(v1, k1, -m_ref), s2 = fmaf(v2, k2, -m_ref),
+                  s3 = fmaf(v3, k3, -m_ref);
+            bool x0 = false, x1 = false, x2 = false, x3 = false;      // token masked out
             if (kMasked) {
-                if (2 * t >= n_valid) { sc[0] = -INFINITY; vna.x = 0.f; }
-                if (2 * t + 1 >= n_valid) { sc[1] = -INFINITY; vna.y = 0.f; }
-                if (8 + 2 * t >= n_valid) { sc[2] = -INFINITY; vnb.x = 0.f; }
-                if (9 + 2 * t >= n_valid) { sc[3] = -INFINITY; vnb.y = 0.f; }
+                x0 = 2 * t >= n_valid; x1 = 2 * t + 1 >= n_valid; x2 = 8 + 2 * t >= n_valid; x3 = 9 + 2 * t >= n_valid;
+                if (x0) { s0 = -INFINITY; vna.x = 0.f; }
+                if (x1) { s1 = -INFINITY; vna.y = 0.f; }
+                if (x2) { s2 = -INFINITY; vnb.x = 0.f; }
+                if (x3) { s3 = -INFINITY; vnb.y = 0.f; }
             }
-
-            // ---- online softmax (log2 domain; the scores carry scale * log2 e) ----
-            const float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-            if (__any_sync(0xffffffffu, mx > m_ref + kRescaleSlack)) {
-                // some head's reference value moves: its lanes agree on the new one, and every lane
-                // rescales the accumulator columns of the heads it holds
+            // ---- online softmax ----
+            const float mx = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
+            if (__any_sync(0xffffffffu, mx > kRescaleSlack)) {
+                // some head's reference value moves: its lanes agree on the page's true maximum as the new
+                // one, and every lane rescales the accumulator columns of the heads it holds
                 float mh = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, 2));
+                const float r0 = x0 ? -INFINITY : v0 * k0, r1 = x1 ? -INFINITY : v1 * k1;
+                const float r2 = x2 ? -INFINITY : v2 * k2, r3 = x3 ? -INFINITY : v3 * k3;
+                float tm = fmaxf(fmaxf(r0, r1), fmaxf(r2, r3));
+                tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+                tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
                 float fsc = 1.0f;
-                if (mh > m_ref + kRescaleSlack) {
-                    fsc = ex2_approx(m_ref - mh);          // 0 on the first page (m_ref = -inf)
+                if (mh > kRescaleSlack) {
+                    fsc = ex2_approx(m_ref - tm);          // 0 on the first page (m_ref = kNoRef)
                     l_run *= fsc;
-                    m_ref = mh;
+                    m_ref = tm;
+                    s0 = r0 - tm; s1 = r1 - tm; s2 = r2 - tm; s3 = r3 - tm;
                 }
                 const float fa = __shfl_sync(0xffffffffu, fsc, ((2 * t) & 3) * 4);
                 const float fb = __shfl_sync(0xffffffffu, fsc, ((2 * t + 1) & 3) * 4);
@@ -296,9 +313,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                     acc[j][1] *= fb; acc[j][3] *= fb;
                 }
             }
-            const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;    // only while nothing valid was seen
-            const float p0 = ex2_approx(sc[0] - m_safe), p1 = ex2_approx(sc[1] - m_safe);
-            const float p2 = ex2_approx(sc[2] - m_safe), p3 = ex2_approx(sc[3] - m_safe);
+            const float p0 = ex2_approx(s0), p1 = ex2_approx(s1), p2 = ex2_approx(s2), p3 = ex2_approx(s3);
             l_run += (p0 + p1) + (p2 + p3);
             // Probabilities (times value norms) are already where the value MMA wants its B operand:
             // rows = tokens 2t, 2t+1, 2t+8, 2t+9, column g = head g & 3 (columns 4..7 repeat 0..3 and are
@@ -320,39 +335,44 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             }
         };
 
-        int n_done = 0;
-        for (int i = 0; i < n_my; ++i) {
-            const unsigned itn = it + i;
-            const int s = itn & (kStages - 1);
-            if ((i & 31) == 0 && i > 0) {
-                ids_cur = ids_nxt;
-                ids_nxt = load_ids(i + 32);
+        for (int base = 0; base < n_my && !failed; base += kStages) {
+            const int id_nn = fetch(base + 2 * kStages);     // in flight while this group is processed
+            const unsigned bad = __ballot_sync(0xffffffffu, id_cur < 0) & 0xFu;
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) {
+                const int i = base + s;
+                if (i < n_my && !failed) {                   // warp-uniform
+                    // the verdict is made warp-uniform so that no lane is left behind at a shuffle
+                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (phase >> s) & 1u))) {
+                        failed = true;
+                    } else {
+                        phase ^= 1u << s;
+                        inflight &= ~(1u << s);
+                        const uint8_t* stage = &s_ring[warp][s][0][0];
+                        const bool is_bad = (bad >> s) & 1u;
+                        if (is_bad || w_lo + i == n_b - 1)
+                            do_page(stage, is_bad ? 0 : last_len, std::true_type{});
+                        else
+                            do_page(stage, 16, std::false_type{});
+                        __syncwarp();   // every lane has finished reading this slot
+                        if (i + kStages < n_my) {
+                            if (lane == s) issue(id_nxt);
+                            inflight |= 1u << s;
+                        }
+                    }
+                }
             }
-            // the verdict is made warp-uniform so that no lane is left behind at a shuffle
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (itn / kStages) & 1))) {
-                failed = true;
-                break;
-            }
-            n_done = i + 1;
-            const int page = __shfl_sync(0xffffffffu, ids_cur, i & 31);
-            const int i_next = i + kStages;
-            const int next_page = __shfl_sync(0xffffffffu, (i_next >> 5) == (i >> 5) ? ids_cur : ids_nxt, i_next & 31);
-            const uint8_t* stage = &s_ring[warp][s][0][0];
-            if (page < 0 || w_lo + i == n_b - 1)
-                do_page(stage, page < 0 ? 0 : last_len, std::true_type{});
-            else
-                do_page(stage, 16, std::false_type{});
-            __syncwarp();   // every lane has finished reading this stage
-            if (lane == 0 && i_next < n_my) issue(itn + kStages, next_page);
+            id_cur = id_nxt;
+            id_nxt = id_nn;
         }
-        if (failed && n_my > 0) {
+        if (failed && inflight != 0) {
             // Give the copies still in flight a bounded chance to land before the CTA can exit.
             if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
-            const int issued = min(n_my, n_done + kStages);
-            for (int i = n_done; i < issued; ++i)
-                mbar_wait_bounded(bar0 + 8 * ((it + i) & (kStages - 1)), ((it + i) / kStages) & 1);
+#pragma unroll
+            for (int s = 0; s < kStages; ++s)
+                if ((inflight >> s) & 1u) mbar_wait_bounded(bar0 + 8 * s, (phase >> s) & 1u);
+            inflight = 0;
         }
-        it += n_my;
 
         // ---- warp result -> shared memory ----
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -382,8 +402,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             float ov = 0.f, lv = 0.f;
 #pragma unroll
             for (int w = 0; w < kAttnWarps; ++w) {
-                const float mw = s_m[w][h];
-                const float fw = mw == -INFINITY ? 0.f : ex2_approx(mw - m);
+                const float fw = ex2_approx(s_m[w][h] - m);
                 ov = fmaf(fw, s_res[w][h][tid], ov);
                 lv = fmaf(fw, s_l[w][h], lv);
             }
@@ -406,9 +425,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             }
             __threadfence();
             __syncthreads();
-            const long long e_p = o_p + n_b - 1;
-            const int c_first = (int)(((o_p + 1) * C + F - 1) / F) - 1;
-            const int c_last = (int)(((e_p + 1) * C + F - 1) / F) - 1;
+            const int c_first = cta_of(o_p), c_last = cta_of(o_p + n_b - 1);
             const int n_seg = c_last - c_first + 1;
             if (tid == 0) {
                 const int prev = atomicAdd(&p.counters[b * H + kvh], 1);
@@ -417,13 +434,12 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             __syncthreads();
             if (s_last) {
                 __threadfence();
-                // last CTA of this (sequence, kv head): merge the partials in CTA order. All maxima / sums
-                // first (one round trip), then the value rows with several CTAs' loads in flight together.
+                // last CTA of this (sequence, kv head): merge the partials in CTA order. Maxima / sums and the
+                // value rows of the first pieces travel in the same round trip.
                 float* s_ml = &s_res[0][0][0];                            // [n_seg][2 * kGroup]: m then l
+                const int first_slot = share_start(c_first) < o_p ? 1 : 0;
                 auto part_of = [&](int k) -> const float* {
-                    const int c = c_first + k;
-                    const int sl = (k == 0 && ((long long)c * F / C) < o_p) ? 1 : 0;
-                    return p.partials + ((size_t)c * 2 + sl) * kPartialFloats;
+                    return p.partials + ((size_t)(c_first + k) * 2 + (k == 0 ? first_slot : 0)) * kPartialFloats;
                 };
                 // a pair cut into more pieces than the staging area holds (one very long sequence among
                 // short ones) reads its maxima / sums from the workspace directly
@@ -434,7 +450,6 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 if (staged)
                     for (int i = tid; i < n_seg * 2 * kGroup; i += kAttnThreads)
                         s_ml[i] = ld_cg_f32(part_of(i >> 3) + kGroup * kDim + (i & 7));
-                // the value rows of the first kMergeBatch pieces travel in the same round trip
                 constexpr int kMergeBatch = 8;
                 float ov0[kMergeBatch][kGroup];
 #pragma unroll
@@ -447,7 +462,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 float mg[kGroup];
 #pragma unroll
                 for (int h = 0; h < kGroup; ++h) {
-                    float m = -INFINITY;
+                    float m = kNoRef;
                     for (int k = 0; k < n_seg; ++k) m = fmaxf(m, ml(k, h));
                     mg[h] = m;
                     o[h] = 0.f;
@@ -458,8 +473,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                     if (k < n_seg) {
 #pragma unroll
                         for (int h = 0; h < kGroup; ++h) {
-                            const float mc = ml(k, h);
-                            const float fc = mc == -INFINITY ? 0.f : ex2_approx(mc - mg[h]);
+                            const float fc = ex2_approx(ml(k, h) - mg[h]);
                             o[h] = fmaf(fc, ov0[k][h], o[h]);
                             lh[h] = fmaf(fc, ml(k, kGroup + h), lh[h]);
                         }
@@ -473,8 +487,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                     for (int h = 0; h < kGroup; ++h) ov[h] = ld_cg_f32(pc + h * kDim);
 #pragma unroll
                     for (int h = 0; h < kGroup; ++h) {
-                        const float mc = ml(k, h);
-                        const float fc = mc == -INFINITY ? 0.f : ex2_approx(mc - mg[h]);
+                        const float fc = ex2_approx(ml(k, h) - mg[h]);
                         o[h] = fmaf(fc, ov[h], o[h]);
                         lh[h] = fmaf(fc, ml(k, kGroup + h), lh[h]);
                     }
@@ -511,7 +524,6 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 }
             }
             __syncthreads();                                              // everyone has read s_o
-            // cross-warp sum in two rounds through the three free warp slots of s_res
             if (warp > 0) {
 #pragma unroll
                 for (int h = 0; h < kGroup; ++h)
