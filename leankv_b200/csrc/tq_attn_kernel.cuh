@@ -44,6 +44,17 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int H = p.H, Hq = H * kGroup;
+    // The eight look-up table words are used by ~100 byte permutes per page: hold them in registers
+    // (an opaque move keeps the compiler from re-reading the parameter bank at every use).
+    uint32_t kh0, kh1, kl0, kl1, tl0, tl1, th0, th1;
+    asm volatile("mov.b32 %0, %1;" : "=r"(kh0) : "r"(p.kh0));
+    asm volatile("mov.b32 %0, %1;" : "=r"(kh1) : "r"(p.kh1));
+    asm volatile("mov.b32 %0, %1;" : "=r"(kl0) : "r"(p.kl0));
+    asm volatile("mov.b32 %0, %1;" : "=r"(kl1) : "r"(p.kl1));
+    asm volatile("mov.b32 %0, %1;" : "=r"(tl0) : "r"(p.tl0));
+    asm volatile("mov.b32 %0, %1;" : "=r"(tl1) : "r"(p.tl1));
+    asm volatile("mov.b32 %0, %1;" : "=r"(th0) : "r"(p.th0));
+    asm volatile("mov.b32 %0, %1;" : "=r"(th1) : "r"(p.th1));
     bool waited = (p.flags & LEANKV_ATTN_EARLY_FETCH) == 0;
     if (waited) pdl_begin();
     // Pull the inverse rotation (a constant, 64 KB) towards L2 early: whichever CTA ends up merging
@@ -246,10 +257,10 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
 #pragma unroll
                 for (int kb = 0; kb < 4; ++kb) {
                     const uint32_t sa = ua.s[kb], sa2 = sa >> 16, sb = ub.s[kb], sb2 = sb >> 16;
-                    const uint32_t ah0 = __byte_perm(p.kh0, p.kh1, sa), ah1 = __byte_perm(p.kh0, p.kh1, sa2);
-                    const uint32_t al0 = __byte_perm(p.kl0, p.kl1, sa), al1 = __byte_perm(p.kl0, p.kl1, sa2);
-                    const uint32_t bh0 = __byte_perm(p.kh0, p.kh1, sb), bh1 = __byte_perm(p.kh0, p.kh1, sb2);
-                    const uint32_t bl0 = __byte_perm(p.kl0, p.kl1, sb), bl1 = __byte_perm(p.kl0, p.kl1, sb2);
+                    const uint32_t ah0 = __byte_perm(kh0, kh1, sa), ah1 = __byte_perm(kh0, kh1, sa2);
+                    const uint32_t al0 = __byte_perm(kl0, kl1, sa), al1 = __byte_perm(kl0, kl1, sa2);
+                    const uint32_t bh0 = __byte_perm(kh0, kh1, sb), bh1 = __byte_perm(kh0, kh1, sb2);
+                    const uint32_t bl0 = __byte_perm(kl0, kl1, sb), bl1 = __byte_perm(kl0, kl1, sb2);
                     if (kb == 0) {
                         mma_s8_16832_bias(dh0, qa[kb], ah0, ah1);
                         mma_s8_16832_bias(dl0, qa[kb], al0, al1);
@@ -327,8 +338,8 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 for (int j = 0; j < 8; ++j) {
                     const uint32_t sa2 = ua.s[j >> 1] >> (16 * (j & 1));
                     const uint32_t sb2 = ub.s[j >> 1] >> (16 * (j & 1));
-                    const uint32_t la = __byte_perm(p.tl0, p.tl1, sa2), ha = __byte_perm(p.th0, p.th1, sa2);
-                    const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb2), hb = __byte_perm(p.th0, p.th1, sb2);
+                    const uint32_t la = __byte_perm(tl0, tl1, sa2), ha = __byte_perm(th0, th1, sa2);
+                    const uint32_t lb = __byte_perm(tl0, tl1, sb2), hb = __byte_perm(th0, th1, sb2);
                     mma_16816(acc[j], __byte_perm(la, ha, 0x5140), __byte_perm(la, ha, 0x7362),
                               __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362), b0, b1);
                 }
