@@ -48,13 +48,13 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kStages = 4;
 constexpr int kGroup = 4;                     // query heads per kv head
 constexpr int kPartialFloats = kGroup * kDim + 2 * kGroup;
-// Resident CTAs per SM: 5 (96 registers per thread, a few spilled bytes) by default; LEANKV_ATTN_OCC=4
-// selects the 128-register build of the same kernel.
+// Resident CTAs per SM: 4 (128 registers per thread, nothing spilled) by default, measured faster than
+// the 96-register build (5 CTAs per SM, a few spilled bytes), which LEANKV_ATTN_OCC=5 selects.
 int attn_occupancy() {
     static int occ = 0;
     if (occ == 0) {
         const char* e = std::getenv("LEANKV_ATTN_OCC");
-        occ = (e != nullptr && e[0] == '4') ? 4 : 5;
+        occ = (e != nullptr && e[0] == '5') ? 5 : 4;
     }
     return occ;
 }
@@ -209,7 +209,7 @@ AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     // One wave of resident CTAs; inputs too short to give every CTA kMinPagesPerCta pages get fewer
     // (the kernel applies the same rule to the page count it finds on the device).
     const long long slots = (long long)sm_count() * attn_occupancy();
-    long long want = (pairs * max_pages + kMinPagesPerCta - 1) / kMinPagesPerCta;
+    long long want = pairs * ((max_pages + kMinPagesPerCta - 1) / kMinPagesPerCta);
     if (want < 1) want = 1;
     pl.n_ctas = (int)(want < slots ? want : slots);
     pl.off_counters = 256;

@@ -95,10 +95,13 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     }
     long long C = gridDim.x;
     {
-        long long cap = F / kMinPagesPerCta;
+        // no more CTAs than give each about kMinPagesPerCta pages; whole multiples of the pair count, so that
+        // equal-length sequences are cut into equal pieces that end at pair boundaries
+        const long long pairs = (long long)p.B * H;
+        long long cap = (F + kMinPagesPerCta - 1) / kMinPagesPerCta;
+        if (cap >= pairs) cap = (cap + pairs - 1) / pairs * pairs;
         if (cap < 1) cap = 1;
         if (C > cap) C = cap;
-        const long long pairs = (long long)p.B * H;
         if (C >= pairs) C -= C % pairs;
     }
     if (F <= 0 || (long long)blockIdx.x >= C) {
@@ -218,8 +221,8 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             kscale = 256.0f * uq * p.c_unit * p.qscale;
             auto digits = [&](float x, int sh, uint32_t& hi, uint32_t& lo) {
                 const int qi = __float2int_rn(x * inv);
-                const int l8 = ((qi + 128) & 255) - 128;             // balanced low digit in [-128, 127]
-                const int h8 = (qi - l8) >> 8;                        // |qi| <= 32512 keeps this in [-127, 127]
+                const int h8 = (qi + 128) >> 8;                       // |qi| <= 32512 keeps this in [-127, 127]
+                const int l8 = qi - (h8 << 8);                        // balanced low digit in [-128, 127]
                 hi |= (uint32_t)(h8 & 255) << sh;
                 lo |= (uint32_t)(l8 & 255) << sh;
             };
@@ -241,10 +244,10 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
         const int last_len = min(max(p.last_len[b], 1), 16);
 
-        // One page. kMasked: the page may hold fewer than 16 valid tokens (a sequence's last page, or a page
-        // id that was rejected); the common case carries no masking code.
-        auto do_page = [&](const uint8_t* stage, int n_valid, auto masked_tag) {
-            constexpr bool kMasked = decltype(masked_tag)::value;
+        // One page; n_valid < 16 for a sequence's last page and 0 for a page id that was rejected. The body
+        // exists once (it is a few hundred instructions: copies of it would not fit the instruction cache
+        // close to the schedulers).
+        auto do_page = [&](const uint8_t* stage, int n_valid) {
             const uint32_t* kw = reinterpret_cast<const uint32_t*>(stage);
             const uint32_t* kn2 = reinterpret_cast<const uint32_t*>(stage + kNormOffsetBytes);
             const uint32_t* vw = reinterpret_cast<const uint32_t*>(stage + kChunkBytes);
@@ -289,14 +292,12 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             // scores relative to the reference value (log2 domain; the scale carries log2 e)
             float s0 = fmaf(v0, k0, -m_ref), s1 = fmaf(v1, k1, -m_ref), s2 = fmaf(v2, k2, -m_ref),
                   s3 = fmaf(v3, k3, -m_ref);
-            bool x0 = false, x1 = false, x2 = false, x3 = false;      // token masked out
-            if (kMasked) {
-                x0 = 2 * t >= n_valid; x1 = 2 * t + 1 >= n_valid; x2 = 8 + 2 * t >= n_valid; x3 = 9 + 2 * t >= n_valid;
-                if (x0) { s0 = -INFINITY; vna.x = 0.f; }
-                if (x1) { s1 = -INFINITY; vna.y = 0.f; }
-                if (x2) { s2 = -INFINITY; vnb.x = 0.f; }
-                if (x3) { s3 = -INFINITY; vnb.y = 0.f; }
-            }
+            // tokens beyond n_valid are masked out
+            const bool x0 = 2 * t >= n_valid, x1 = 2 * t + 1 >= n_valid, x2 = 8 + 2 * t >= n_valid, x3 = 9 + 2 * t >= n_valid;
+            if (x0) { s0 = -INFINITY; vna.x = 0.f; }
+            if (x1) { s1 = -INFINITY; vna.y = 0.f; }
+            if (x2) { s2 = -INFINITY; vnb.x = 0.f; }
+            if (x3) { s3 = -INFINITY; vnb.y = 0.f; }
             // ---- online softmax ----
             const float mx = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
             if (__any_sync(0xffffffffu, mx > kRescaleSlack)) {
@@ -346,35 +347,31 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             }
         };
 
-        for (int base = 0; base < n_my && !failed; base += kStages) {
-            const int id_nn = fetch(base + 2 * kStages);     // in flight while this group is processed
-            const unsigned bad = __ballot_sync(0xffffffffu, id_cur < 0) & 0xFu;
-#pragma unroll
-            for (int s = 0; s < kStages; ++s) {
-                const int i = base + s;
-                if (i < n_my && !failed) {                   // warp-uniform
-                    // the verdict is made warp-uniform so that no lane is left behind at a shuffle
-                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (phase >> s) & 1u))) {
-                        failed = true;
-                    } else {
-                        phase ^= 1u << s;
-                        inflight &= ~(1u << s);
-                        const uint8_t* stage = &s_ring[warp][s][0][0];
-                        const bool is_bad = (bad >> s) & 1u;
-                        if (is_bad || w_lo + i == n_b - 1)
-                            do_page(stage, is_bad ? 0 : last_len, std::true_type{});
-                        else
-                            do_page(stage, 16, std::false_type{});
-                        __syncwarp();   // every lane has finished reading this slot
-                        if (i + kStages < n_my) {
-                            if (lane == s) issue(id_nxt);
-                            inflight |= 1u << s;
-                        }
-                    }
-                }
+        int id_nn = fetch(2 * kStages);                      // two groups ahead, in flight while a group is processed
+        unsigned bad = __ballot_sync(0xffffffffu, id_cur < 0) & 0xFu;
+        for (int i = 0; i < n_my; ++i) {
+            const int s = i & (kStages - 1);
+            const uint32_t bar = bar0 + 8 * s;
+            // the verdict is made warp-uniform so that no lane is left behind at a shuffle
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar, (phase >> s) & 1u))) {
+                failed = true;
+                break;
             }
-            id_cur = id_nxt;
-            id_nxt = id_nn;
+            phase ^= 1u << s;
+            inflight &= ~(1u << s);
+            const int n_valid = ((bad >> s) & 1u) ? 0 : (w_lo + i == n_b - 1 ? last_len : 16);
+            do_page(&s_ring[warp][0][0][0] + s * (2 * kChunkBytes), n_valid);
+            __syncwarp();   // every lane has finished reading this slot
+            if (i + kStages < n_my) {
+                if (lane == s) issue(id_nxt);
+                inflight |= 1u << s;
+            }
+            if (s == kStages - 1) {                          // next group
+                id_cur = id_nxt;
+                id_nxt = id_nn;
+                id_nn = fetch(i + 1 + 2 * kStages);
+                bad = __ballot_sync(0xffffffffu, id_cur < 0) & 0xFu;
+            }
         }
         if (failed && inflight != 0) {
             // Give the copies still in flight a bounded chance to land before the CTA can exit.
@@ -440,11 +437,11 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             const int n_seg = c_last - c_first + 1;
             if (tid == 0) {
                 const int prev = atomicAdd(&p.counters[b * H + kvh], 1);
+                __threadfence();               // the other CTAs' partials are read after this point
                 s_last = (prev == n_seg - 1);
             }
             __syncthreads();
             if (s_last) {
-                __threadfence();
                 // last CTA of this (sequence, kv head): merge the partials in CTA order. Maxima / sums and the
                 // value rows of the first pieces travel in the same round trip.
                 float* s_ml = &s_res[0][0][0];                            // [n_seg][2 * kGroup]: m then l
@@ -461,7 +458,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 if (staged)
                     for (int i = tid; i < n_seg * 2 * kGroup; i += kAttnThreads)
                         s_ml[i] = ld_cg_f32(part_of(i >> 3) + kGroup * kDim + (i & 7));
-                constexpr int kMergeBatch = 8;
+                constexpr int kMergeBatch = 12;
                 float ov0[kMergeBatch][kGroup];
 #pragma unroll
                 for (int k = 0; k < kMergeBatch; ++k) {
@@ -521,7 +518,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
 #pragma unroll
             for (int h = 0; h < kGroup; ++h) r[h][0] = r[h][1] = r[h][2] = r[h][3] = 0.f;
             const float4* pv = reinterpret_cast<const float4*>(p.Pi_v) + (size_t)(32 * warp) * (kDim / 4) + lane;
-#pragma unroll 8
+#pragma unroll 16
             for (int ii = 0; ii < 32; ++ii) {
                 const float4 w4 = __ldg(pv + (size_t)ii * (kDim / 4));
                 const int i = 32 * warp + ii;
