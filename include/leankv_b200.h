@@ -15,6 +15,9 @@
  *  - "workspace" buffers hold split-K partial sums and arrival counters. A workspace
  *    must be zero-filled once after allocation; kernels leave the counters zeroed
  *    on exit. One workspace must not be shared by launches that can overlap in time.
+ *    The GEMV entry points keep their counters in the first 16 KiB whatever the shape, so
+ *    one workspace (sized for the largest shape) may serve launches of different shapes
+ *    with N <= 1 048 576 one after the other.
  */
 #ifndef LEANKV_B200_H
 #define LEANKV_B200_H

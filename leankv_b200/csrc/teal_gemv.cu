@@ -32,6 +32,7 @@ constexpr int kMaxRowsPerSplit = kWarps * 32 * kLaneSlots;  // 1024
 constexpr int kMaxSplits = 128;
 constexpr int kMaxSplitsNarrow = 40;   // = kWarps x the merge's load batch: the last CTA sums a slice in one round trip
 constexpr int kCtasPerSm = 4;
+constexpr size_t kCounterAreaBytes = 16384;   // counters of up to 4096 column slices (N <= 1 048 576)
 
 struct GemvParams {
     const __half* Wt;
@@ -94,7 +95,10 @@ GemvPlan make_plan(int N, int Z, int arrays) {
     if (rows > kMaxRowsPerSplit) rows = kMaxRowsPerSplit;
     pl.rows_per_split = rows;
     pl.k_splits = (Z + rows - 1) / rows;
-    pl.counter_bytes = round_up(sizeof(int) * (size_t)pl.n_slices, 256);
+    // The arrival counters sit in a fixed-size area in front of the partial sums, whatever the shape: a
+    // workspace shared by launches of different shapes (the projections of a decode step) must never have
+    // one shape's partial sums land on another shape's counters.
+    pl.counter_bytes = round_up(sizeof(int) * (size_t)pl.n_slices, kCounterAreaBytes);
     pl.partial_bytes =
         pl.k_splits > 1 ? sizeof(float) * (size_t)pl.k_splits * arrays * pl.n_slices * kColsPerCta : 0;
     return pl;

@@ -24,8 +24,10 @@ constexpr int kTcTokens = 64;
 constexpr int kPiStride = 136;            // halves per row (272 bytes): conflict-free 8 x 16-byte ldmatrix rows
 constexpr int kUStride = 136;             // floats per row of the unit-vector tile
 constexpr float kBand = 1e-4f;
+constexpr int kCodeStride = 132;          // bytes per token row of the code tile: 4-byte reads of 8 tokens x 4 quarters hit 32 banks
+constexpr int kListCap = 64;              // queue of boundary-band coordinates: flushed whenever it holds a full warp's worth
 constexpr size_t kTcSmemBytes = 2 * (size_t)kDim * kPiStride * sizeof(__half) +
-                                (size_t)kTcTokens * kUStride * sizeof(float) + (size_t)kTcTokens * kDim;
+                                (size_t)kTcTokens * kUStride * sizeof(float) + (size_t)kTcTokens * kCodeStride;
 
 struct AppendTcParams {
     AppendParams a;
@@ -60,8 +62,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) tq_pool_append_tc_kernel(const 
     __half* s_pih = reinterpret_cast<__half*>(tc_smem);
     __half* s_pil = s_pih + kDim * kPiStride;
     float* s_u = reinterpret_cast<float*>(s_pil + kDim * kPiStride);                 // [64][kUStride]
-    uint8_t* s_code = reinterpret_cast<uint8_t*>(s_u + kTcTokens * kUStride);        // [64][128]
+    uint8_t* s_code = reinterpret_cast<uint8_t*>(s_u + kTcTokens * kUStride);        // [64][kCodeStride]
     __shared__ float s_norm[kTcTokens];
+    __shared__ uint16_t s_list[kTcThreads / 32][kListCap];      // per warp: (slot << 7 | coordinate) awaiting the exact chain
     __shared__ float s_bounds[8];
 
     const AppendParams& p = tp.a;
@@ -174,9 +177,31 @@ __global__ void __launch_bounds__(kTcThreads, 2) tq_pool_append_tc_kernel(const 
             }
         }
 
-        // ---- codes; coordinates close to a boundary are decided by the sequential fp32 chain ----
+        // ---- codes; coordinates close to a boundary are queued for the sequential fp32 chain ----
         const float b1 = s_bounds[4], b2 = s_bounds[5], b3 = s_bounds[6];       // 0 < b1 < b2 < b3 (s_bounds[3] = 0)
-        uint8_t* code_rows = s_code + (size_t)(16 * warp) * kDim;
+        uint8_t* code_rows = s_code + (size_t)(16 * warp) * kCodeStride;
+        // exact value of one coordinate: y = fma chain over k ascending, from the fp32 unit vector
+        auto exact_code = [&](int slot, int coord) -> int {
+            const float4* pr = reinterpret_cast<const float4*>(Pi + (size_t)coord * kDim);
+            const float4* ur = reinterpret_cast<const float4*>(&s_u[(16 * warp + slot) * kUStride]);
+            float4 pv[kDim / 4];
+#pragma unroll
+            for (int k4 = 0; k4 < kDim / 4; ++k4) pv[k4] = __ldg(pr + k4);      // one round trip for the whole row
+            float ye = 0.f;
+#pragma unroll
+            for (int k4 = 0; k4 < kDim / 4; ++k4) {
+                const float4 uv = ur[k4];
+                ye = fmaf(pv[k4].x, uv.x, ye);
+                ye = fmaf(pv[k4].y, uv.y, ye);
+                ye = fmaf(pv[k4].z, uv.z, ye);
+                ye = fmaf(pv[k4].w, uv.w, ye);
+            }
+            int code = 0;
+#pragma unroll
+            for (int q = 0; q < 7; ++q) code += (ye > s_bounds[q]) ? 1 : 0;
+            return code;
+        };
+        uint32_t near_lo = 0, near_hi = 0;                     // bit 4n + i: value (n, i) of this lane is in the band
 #pragma unroll
         for (int n = 0; n < 16; ++n) {
 #pragma unroll
@@ -186,61 +211,85 @@ __global__ void __launch_bounds__(kTcThreads, 2) tq_pool_append_tc_kernel(const 
                 const float y = acc[n][i];
                 const float ay = fabsf(y);
                 const int mag = (ay > b1 ? 1 : 0) + (ay > b2 ? 1 : 0) + (ay > b3 ? 1 : 0);
-                int code = y > 0.f ? 4 + mag : 3 - mag;
+                const int code = y > 0.f ? 4 + mag : 3 - mag;
                 const bool near = ay <= kBand || fabsf(ay - b1) <= kBand || fabsf(ay - b2) <= kBand ||
                                   fabsf(ay - b3) <= kBand;
-                const bool live = slot >= slot0 && slot < slot0 + nt_valid;
-                if (near && live) {
-                    const float4* pr = reinterpret_cast<const float4*>(Pi + (size_t)coord * kDim);
-                    const float4* ur = reinterpret_cast<const float4*>(&s_u[(16 * warp + slot) * kUStride]);
-                    float ye = 0.f;
-#pragma unroll 8
-                    for (int k4 = 0; k4 < kDim / 4; ++k4) {
-                        const float4 pv = __ldg(pr + k4);
-                        const float4 uv = ur[k4];
-                        ye = fmaf(pv.x, uv.x, ye);
-                        ye = fmaf(pv.y, uv.y, ye);
-                        ye = fmaf(pv.z, uv.z, ye);
-                        ye = fmaf(pv.w, uv.w, ye);
-                    }
-                    code = 0;
-#pragma unroll
-                    for (int q = 0; q < 7; ++q) code += (ye > s_bounds[q]) ? 1 : 0;
-                    ++n_exact;
+                code_rows[slot * kCodeStride + coord] = (uint8_t)code;
+                if (near && slot >= slot0 && slot < slot0 + nt_valid) {
+                    if (n < 8) near_lo |= 1u << (4 * n + i);
+                    else near_hi |= 1u << (4 * (n - 8) + i);
                 }
-                code_rows[slot * kDim + coord] = (uint8_t)code;
             }
         }
         n_coords += (unsigned long long)nt_valid * 4;          // per lane: 128 coordinates / 32 lanes
+        n_exact += __popc(near_lo) + __popc(near_hi);
+        // The band coordinates of all lanes are compacted into a queue; whenever it holds 32 of them every
+        // lane runs one exact chain. (A page of all-zero vectors puts all 2048 coordinates in the band.)
+        if (__any_sync(0xffffffffu, (near_lo | near_hi) != 0u)) {
+            int cnt = 0;                                       // warp-uniform
+            auto flush = [&](int n_take) {
+                __syncwarp();
+                if (lane < n_take) {
+                    const int ent = s_list[warp][lane];
+                    code_rows[(ent >> 7) * kCodeStride + (ent & 127)] = (uint8_t)exact_code(ent >> 7, ent & 127);
+                }
+                const int rest = cnt - n_take;                 // < 32
+                const uint16_t moved = lane < rest ? s_list[warp][n_take + lane] : (uint16_t)0;
+                __syncwarp();
+                if (lane < rest) s_list[warp][lane] = moved;
+                cnt = rest;
+            };
+#pragma unroll 1
+            for (int idx = 0; idx < 64; ++idx) {
+                const bool flag = ((idx < 32 ? near_lo >> idx : near_hi >> (idx - 32)) & 1u) != 0u;
+                const unsigned m = __ballot_sync(0xffffffffu, flag);
+                if (m == 0u) continue;
+                if (flag) {
+                    const int n = idx >> 2, i = idx & 3;
+                    const int slot = g + (i >> 1) * 8, coord = n * 8 + 2 * t + (i & 1);
+                    s_list[warp][cnt + __popc(m & ((1u << lane) - 1u))] = (uint16_t)((slot << 7) | coord);
+                }
+                cnt += __popc(m);
+                if (cnt >= 32) flush(32);
+            }
+            if (cnt > 0) flush(cnt);
+        }
         __syncwarp();
         if (!page_ok) continue;                                // invalid table entry: write nothing
 
-        // ---- pack this page's chunk (same words as tq_pool_append_kernel) ----
+        // ---- pack this page's chunk (same words as tq_pool_append_kernel), four codes per shared-memory read ----
         uint8_t* chunk = p.pool + (((size_t)page * 2 + which) * p.H + h) * kChunkBytes;
         uint32_t* words = reinterpret_cast<uint32_t*>(chunk);
         __half* norms = reinterpret_cast<__half*>(chunk + kNormOffsetBytes);
         if (lane >= slot0 && lane < slot0 + nt_valid) norms[lane] = __float2half_rn(s_norm[16 * warp + lane]);
+        // squeezes the low nibbles of 4 bytes into 16 bits
+        auto pack4 = [](uint32_t v) -> uint32_t {
+            const uint32_t t2 = (v | (v >> 4)) & 0x00FF00FFu;
+            return (t2 | (t2 >> 8)) & 0xFFFFu;
+        };
         for (int w = lane; w < kChunkWords; w += 32) {
             const int kk = w >> 6, ui = w & 63;
             if (which == 0) {
+                // unit (slot, quarter t4): codes e = coordinates 32 t4 + e; word kk holds codes 8kk..8kk+7 as
+                // nibbles and bit kk of codes 24..31 in the nibbles' spare bits
                 const int slot = ui >> 2, t4 = ui & 3;
                 if (slot < slot0 || slot >= slot0 + nt_valid) continue;
-                uint32_t bits = 0;
-#pragma unroll 8
-                for (int e = 0; e < 32; ++e) bits |= unit_word_bits(e, kk, code_rows[slot * kDim + 32 * t4 + e]);
-                words[w] = bits;
+                const uint32_t* c4 = reinterpret_cast<const uint32_t*>(&code_rows[slot * kCodeStride + 32 * t4]);
+                const uint32_t lo = c4[2 * kk] & 0x07070707u, hi = c4[2 * kk + 1] & 0x07070707u;
+                const uint32_t s_lo = ((c4[6] >> kk) & 0x01010101u) << 3, s_hi = ((c4[7] >> kk) & 0x01010101u) << 3;
+                words[w] = pack4(lo) | (pack4(hi) << 16) | pack4(s_lo) | (pack4(s_hi) << 16);
             } else {
+                // unit (pair pr, group gg): coordinates 16 gg .. +15 of slots 2 pr (low nibbles) and 2 pr + 1
                 const int pr = ui < 32 ? (ui & 3) : 4 + (ui & 3);
                 const int gg = (ui & 31) >> 2;
-                const int sa = 2 * pr, sb = sa + 1;                        // slots of the pair
+                const int sa = 2 * pr, sb = sa + 1;
                 const bool has_a = sa >= slot0 && sa < slot0 + nt_valid, has_b = sb >= slot0 && sb < slot0 + nt_valid;
                 if (!has_a && !has_b) continue;
+                const uint32_t* ca = reinterpret_cast<const uint32_t*>(&code_rows[sa * kCodeStride + 16 * gg]);
+                const uint32_t* cb = reinterpret_cast<const uint32_t*>(&code_rows[sb * kCodeStride + 16 * gg]);
                 uint32_t bits = 0;
-#pragma unroll 8
-                for (int c = 0; c < 16; ++c) {
-                    if (has_a) bits |= unit_word_bits(2 * c, kk, code_rows[sa * kDim + 16 * gg + c]);
-                    if (has_b) bits |= unit_word_bits(2 * c + 1, kk, code_rows[sb * kDim + 16 * gg + c]);
-                }
+                if (has_a) bits |= (ca[kk] & 0x07070707u) | (((ca[3] >> kk) & 0x01010101u) << 3);
+                if (has_b) bits |= ((cb[kk] & 0x07070707u) << 4) | (((cb[3] >> kk) & 0x01010101u) << 7);
                 if (!(has_a && has_b)) {
                     // the other token of the pair was (or will be) written by another launch
                     const uint32_t keep = has_a ? 0xF0F0F0F0u : 0x0F0F0F0Fu;

@@ -279,3 +279,33 @@ def test_allreduce_wait_gives_up_when_a_peer_never_arrives():
     y2 = _allreduce_gemv(wt, x, 0.1, None, xc, 1)          # sticky status: returns without polling
     assert int(status.item()) == 1 and bool(torch.isfinite(y2.float()).all())
     torch.cuda.synchronize()
+
+
+def test_one_workspace_serves_projections_of_different_widths():
+    """A decode step runs all its projections through one workspace. The widest (the output head: 128
+    column slices at vocabulary 32768, 501 at 128256) must still find its arrival counters at zero after
+    narrower projections have left their partial sums in the same buffer."""
+    lib = _native.lib()
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(11)
+    shapes = [(6144, 512), (14336, 512), (512, 14336), (32768, 512), (128256, 512)]     # (N, Z)
+    need = max(lib.leankv_sparse_gemv_workspace_bytes(n, z) for n, z in shapes)
+    need = max(need, lib.leankv_sparse_swiglu_workspace_bytes(14336, 512))
+    ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    mats = {(n, z): (torch.randn(z, n, device=dev, generator=gen) * 0.05).half() for n, z in shapes}
+    xs = {z: torch.randn(z, device=dev, generator=gen).half() for z in {z for _, z in shapes}}
+    for _ in range(2):                                           # second round: everything has been used before
+        for n, z in shapes:
+            y = torch.full((n,), float("nan"), dtype=torch.float16, device=dev)
+            _native.check(lib.leankv_sparse_gemv_f16(mats[(n, z)].data_ptr(), xs[z].data_ptr(), y.data_ptr(), n, z,
+                                                     0.3, None, None, ws.data_ptr(), ws.numel(), None, st), "gemv")
+            xm = xs[z].float() * (xs[z].abs().float() > 0.3)
+            want = xm @ mats[(n, z)].float()
+            assert torch.isfinite(y).all(), (n, z)
+            assert rel_l2(y.cpu(), want.cpu()) < 1e-3, (n, z)
+        g = torch.full((14336,), float("nan"), dtype=torch.float16, device=dev)
+        _native.check(lib.leankv_sparse_swiglu_f16(mats[(14336, 512)].data_ptr(), mats[(14336, 512)].data_ptr(),
+                                                   xs[512].data_ptr(), g.data_ptr(), 14336, 512, 0.3, 0.3,
+                                                   ws.data_ptr(), ws.numel(), None, st), "swiglu")
+        assert torch.isfinite(g).all()
