@@ -824,49 +824,53 @@ def decode_parity(eng, prompt, cfg, dev, world, rank, group, history, tp_steps: 
     if world == 1:
         return out
 
-    # (2) tensor parallel against the single-GPU engine on the same seeded weights, teacher-forced on the
-    # tensor-parallel run's tokens. With TEAL off the two differ only by the order of fp16 partial sums (bound
-    # 2e-2, enforced). With TEAL on (the timed configuration) a last-bit difference next to a threshold switches
-    # a whole weight column on or off and the difference grows with depth: reported, not bounded.
-    def tp_run():
-        first_tok = eng.prefill(prompt)
-        toks, logits = [], []
-        for _ in range(tp_steps):
-            toks.append(int(eng.token.item()))
-            eng.step()
-            torch.cuda.synchronize()
-            logits.append(eng.logits.float().clone())
-        eng.check_status()
-        return first_tok, toks, logits
-
-    eng.set_thresholds(None)
-    runs = {"teal_off": tp_run()}
-    eng.set_thresholds(saved)
-    runs["teal_on"] = tp_run()
+    # (2) tensor parallel against the single-GPU engine on the same seeded weights. Every rank builds the
+    # single-GPU engine, both engines process the prompt, and the tensor-parallel engine then takes over the
+    # single-GPU engine's packed pages (its slice of the kv heads) and first token, so that both decode from
+    # the same cache: a 3-bit code is a discontinuity, and codes produced by GEMMs of another width differ in
+    # a few coordinates per thousand, which 32 random layers amplify to several per cent (reported below as
+    # "free_running"). From the common cache the steps differ only by the order of fp16 partial sums: with
+    # TEAL off the bound 2e-2 is enforced; with TEAL on (the timed configuration) a last-bit difference next
+    # to a threshold switches a weight column on or off, so that figure is reported, not bounded.
     gathered = [torch.empty_like(history) for _ in range(world)]
     dist.all_gather(gathered, history, group=group)
     identical = all(torch.equal(gathered[0], g) for g in gathered[1:])
     tp = {"ranks_identical": bool(identical), "tokens_compared": int(history.numel()), "timed_out": False,
           "steps": tp_steps, "bound": 2e-2}
-    if rank == 0:
-        single = DecodeEngine.random_init(cfg, dev, seed=0, max_seq_len=eng.max_seq_len)
-        for name, thr in (("teal_off", None), ("teal_on", saved)):
-            first_tok, toks, logits = runs[name]
-            single.set_thresholds(thr)
+    single = DecodeEngine.random_init(cfg, dev, seed=0, max_seq_len=eng.max_seq_len)
+    r0 = rank * eng.nkv
+    for name, thr in (("teal_off", None), ("teal_on", saved)):
+        eng.set_thresholds(thr)
+        single.set_thresholds(thr)
+        res = {}
+        for mode in ("common_cache", "free_running"):
             tok0 = single.prefill(prompt)
+            tok_tp = eng.prefill(prompt)
+            if mode == "common_cache":
+                for l in range(cfg.num_layers):
+                    eng.pools[l].copy_(single.pools[l][:, :, r0:r0 + eng.nkv])
+                eng.token.copy_(single.token)
             errs = []
-            for i in range(tp_steps):
-                single.token.fill_(toks[i])
+            for _ in range(tp_steps):
+                tok = int(eng.token.item())
+                eng.step()
+                single.token.fill_(tok)
                 single.step()
                 torch.cuda.synchronize()
-                errs.append(rel(logits[i], single.logits.float()))
+                errs.append(rel(eng.logits.float(), single.logits.float()))
+            eng.check_status()
             single.check_status()
-            tp[name] = {"per_step_rel_l2": errs, "max_rel_l2": max(errs), "first_token_equal": bool(tok0 == first_tok)}
-        tp["max_rel_l2"] = tp["teal_off"]["max_rel_l2"]
-        del single
-        torch.cuda.empty_cache()
+            worst = torch.tensor([max(errs)], dtype=torch.float64, device=dev)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX, group=group)
+            res[mode] = {"per_step_rel_l2_rank0": errs, "max_rel_l2": float(worst.item()),
+                         "first_token_equal": bool(tok0 == tok_tp)}
+        tp[name] = res
+    tp["max_rel_l2"] = tp["teal_off"]["common_cache"]["max_rel_l2"]
+    del single
+    torch.cuda.empty_cache()
+    eng.set_thresholds(saved)
     dist.barrier(group=group)
-    tp["ok"] = bool(identical and (rank != 0 or tp["max_rel_l2"] <= tp["bound"]))
+    tp["ok"] = bool(identical and tp["max_rel_l2"] <= tp["bound"])
     out["tp"] = tp
     return out
 
