@@ -353,6 +353,26 @@ int leankv_batch_decode_end(const void* logits, int vocab, int B, long long* tok
                             long long* history, int history_cap, int32_t* pos, int32_t* steps,
                             void* stream);
 
+/* ------------------------------------------------------------------------- *
+ * Page table of a paged cache, kept on the device. Replaces the host loops of
+ * leankv/turboquant/paged_cache.py: _allocate_page (:96-103, LIFO free list), the page assignment
+ * of update (:147-164) and the flat metadata built for every attention call (:215-233).
+ *
+ * State (int32, device): seq_len [B]; block_table [B][max_pages_per_seq] (pages of sequence b in
+ * order); free_stack [n_pages] with *free_top entries in use (the top is popped first).
+ * One step: every sequence grows by t_new tokens (t_new = 0 only rebuilds the flat arrays), taking
+ * the pages it lacks from the stack, sequence 0 first. Outputs for leankv_tq_pool_append /
+ * leankv_tq_decode_attn: kv_indptr [B+1], kv_page_indices [pages in use], kv_last_page_len [B]
+ * (16 for a full last page), start_pos [B] (length before this step).
+ * If the stack holds too few pages (status |= 1) or a row of the block table would overflow
+ * (status |= 2) no sequence grows: the host mirrors the arithmetic and raises before launching,
+ * the status word is the backstop. B <= 1024.
+ * ------------------------------------------------------------------------- */
+int leankv_paged_table_step(int t_new, int B, int32_t* seq_len, int32_t* block_table,
+                            int max_pages_per_seq, int32_t* free_stack, int32_t* free_top,
+                            int32_t* kv_indptr, int32_t* kv_page_indices, int32_t* kv_last_page_len,
+                            int32_t* start_pos, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

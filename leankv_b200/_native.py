@@ -108,6 +108,8 @@ SIGNATURES = {
                                           c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "leankv_batch_qkv_post": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "leankv_paged_table_step": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "leankv_silu_mul_f16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "leankv_batch_decode_end": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p]),

@@ -335,3 +335,96 @@ extern "C" int leankv_batch_decode_end(const void* logits, int vocab, int B, lon
                                   steps));
     return LEANKV_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Page table of a paged cache kept on the device (replaces the host loops of
+// leankv/turboquant/paged_cache.py:96-103 (_allocate_page), :147-164 (page assignment in update) and
+// :215-233 (flat metadata for the attention call)).
+// ---------------------------------------------------------------------------------------------
+namespace leankv {
+namespace {
+
+constexpr int kTableThreads = 1024;
+
+// One CTA. Sequence b grows by t_new tokens: it takes the pages it lacks from the top of the free
+// stack (sequence 0 first, as the reference's loop does), its length advances, and the flat
+// (kv_indptr, kv_page_indices, kv_last_page_len, start_pos) arrays of the append / attention calls are
+// rebuilt. If the stack does not hold enough pages nothing changes and status bit 0 is set.
+__global__ void __launch_bounds__(kTableThreads) paged_table_step_kernel(
+    int t_new, int B, int32_t* seq_len, int32_t* block_table, int pps_cap, int32_t* free_stack, int32_t* free_top,
+    int32_t* kv_indptr, int32_t* kv_page_indices, int32_t* kv_last_page_len, int32_t* start_pos, int32_t* status) {
+    __shared__ int s_scan[kTableThreads];
+    __shared__ int s_fail, s_top;
+    pdl_begin();
+    const int b = threadIdx.x;
+    const int len = b < B ? seq_len[b] : 0;
+    const int have = (len + 15) / 16;
+    const int want = b < B ? (len + t_new + 15) / 16 : 0;
+    const int need = max(want - have, 0);
+    // inclusive scans (Hillis-Steele over the CTA) of the pages needed and of the pages held afterwards
+    auto scan = [&](int v) -> int {
+        s_scan[b] = v;
+        __syncthreads();
+        for (int o = 1; o < kTableThreads; o <<= 1) {
+            const int add = b >= o ? s_scan[b - o] : 0;
+            __syncthreads();
+            s_scan[b] += add;
+            __syncthreads();
+        }
+        const int incl = s_scan[b];
+        __syncthreads();
+        return incl;
+    };
+    const int need_incl = scan(need);
+    const int overflow = __syncthreads_or(b < B && want > pps_cap);   // a row of the block table would not hold it
+    if (b == kTableThreads - 1) {
+        const int total = need_incl, top = *free_top;                 // the last thread's inclusive sum is the total
+        const bool fail = total > top || overflow != 0;
+        if (total > top) atomicOr(status, 1);
+        if (overflow) atomicOr(status, 2);
+        if (!fail) *free_top = top - total;
+        s_fail = fail ? 1 : 0;
+        s_top = top;
+    }
+    __syncthreads();
+    const int top = s_top;
+    int new_len = len;
+    if (s_fail == 0 && b < B) {
+        const int first = need_incl - need;              // pages popped by sequences before this one
+        for (int i = 0; i < need; ++i) block_table[(size_t)b * pps_cap + have + i] = free_stack[top - 1 - first - i];
+        new_len = len + t_new;
+        seq_len[b] = new_len;
+    }
+    const int pages_now = b < B ? (new_len + 15) / 16 : 0;
+    const int pages_incl = scan(pages_now);
+    if (b < B) {
+        start_pos[b] = len;
+        kv_indptr[b + 1] = pages_incl;
+        if (b == 0) kv_indptr[0] = 0;
+        const int rem = new_len % 16;
+        kv_last_page_len[b] = rem > 0 ? rem : 16;        // 0 -> page_size, the reference's convention (:225-226)
+    }
+    __syncthreads();
+    if (b < B) {
+        const int off = pages_incl - pages_now;
+        for (int i = 0; i < pages_now; ++i) kv_page_indices[off + i] = block_table[(size_t)b * pps_cap + i];
+    }
+}
+
+}  // namespace
+}  // namespace leankv
+
+extern "C" int leankv_paged_table_step(int t_new, int B, int32_t* seq_len, int32_t* block_table,
+                                       int max_pages_per_seq, int32_t* free_stack, int32_t* free_top,
+                                       int32_t* kv_indptr, int32_t* kv_page_indices, int32_t* kv_last_page_len,
+                                       int32_t* start_pos, int32_t* status, void* stream) {
+    if (t_new < 0 || B <= 0 || max_pages_per_seq <= 0 || !seq_len || !block_table || !free_stack || !free_top ||
+        !kv_indptr || !kv_page_indices || !kv_last_page_len || !start_pos || !status)
+        return LEANKV_EINVAL;
+    if (B > kTableThreads) return LEANKV_ELIMIT;
+    LEANKV_CUDA_TRY(launch_kernel(paged_table_step_kernel, dim3(1), dim3(kTableThreads), 0,
+                                  static_cast<cudaStream_t>(stream), t_new, B, seq_len, block_table, max_pages_per_seq,
+                                  free_stack, free_top, kv_indptr, kv_page_indices, kv_last_page_len, start_pos,
+                                  status));
+    return LEANKV_OK;
+}

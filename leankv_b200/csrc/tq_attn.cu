@@ -193,8 +193,13 @@ __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const flo
     for (int h = 0; h < kGroup; ++h) qprime[(size_t)(v0 + h) * kDim + j] = acc[h];
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // ---- main kernel -----------------------------------------------------------
 #include "tq_attn_kernel.cuh"
+#include "tq_attn_kernel_split.cuh"
 
 // ---- host side ---------------------------------------------------------------
 struct AttnPlan {
@@ -202,13 +207,23 @@ struct AttnPlan {
     size_t off_counters, off_qprime, off_partials, total;
 };
 
+// LEANKV_ATTN_SPLIT=1 selects the kernel with separate score and value warps per page stream.
+bool attn_split() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("LEANKV_ATTN_SPLIT");
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     AttnPlan pl;
     if (max_pages < 1) max_pages = 1;
     const long long pairs = (long long)B * Hkv;
     // One wave of resident CTAs; inputs too short to give every CTA kMinPagesPerCta pages get fewer
     // (the kernel applies the same rule to the page count it finds on the device).
-    const long long slots = (long long)sm_count() * attn_occupancy();
+    const long long slots = (long long)sm_count() * (attn_split() ? 3 : attn_occupancy());
     long long want = pairs * ((max_pages + kMinPagesPerCta - 1) / kMinPagesPerCta);
     if (want < 1) want = 1;
     pl.n_ctas = (int)(want < slots ? want : slots);
@@ -357,7 +372,9 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
-    if (attn_occupancy() == 4)
+    if (attn_split())
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_split_kernel, dim3(pl.n_ctas), dim3(kSplitThreads), 0, st, p));
+    else if (attn_occupancy() == 4)
         LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     else
         LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));

@@ -1,0 +1,614 @@
+// Variant of the decode-attention kernel in which every page stream is served by two warps: a "score"
+// warp (key chunk -> integer score MMAs -> online softmax) and a "value" warp (value chunk -> value MMAs
+// into the accumulators). The score warp hands each page's four probabilities per lane and the lane's
+// rescale factor to its value warp through a small shared-memory queue guarded by mbarriers, and may run
+// a few pages ahead. Each warp keeps about half the registers of the single-warp form (no accumulators
+// in the score warp, no query operand / score registers in the value warp), so more warps are resident
+// per SM. Work split, merge and numerics are those of tq_decode_attn_kernel (same header comment).
+
+constexpr int kSplitThreads = 2 * kAttnThreads;      // 4 score warps + 4 value warps
+constexpr int kDepth = 4;                            // probability queue slots per warp pair
+
+__global__ void __launch_bounds__(kSplitThreads, 3) tq_decode_attn_split_kernel(const AttnParams p) {
+    // per warp pair: a ring of kStages key chunks (score warp) and one of value chunks (value warp)
+    __shared__ __align__(128) uint8_t s_ring[2][kAttnWarps][kStages][kChunkBytes];
+    __shared__ __align__(8) uint64_t s_bar[2][kAttnWarps][kStages];
+    // probability queue: p[4] per lane, then the lane's rescale factor
+    __shared__ __align__(16) float4 s_prob[kAttnWarps][kDepth][32];
+    __shared__ float s_fsc[kAttnWarps][kDepth][32];
+    __shared__ __align__(8) uint64_t s_full[kAttnWarps][kDepth], s_empty[kAttnWarps][kDepth];
+    __shared__ __align__(16) float s_res[kAttnWarps][kGroup][kDim];   // warp results, later scratch of the merge
+    __shared__ float s_m[kAttnWarps][kGroup], s_l[kAttnWarps][kGroup];
+    __shared__ int s_ip[kAttnThreads];                                // kv_indptr of a small batch
+    __shared__ int s_last;
+    static_assert(kStages == 4, "the page loop is unrolled over a 4-slot ring");
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = (tid >> 5) & (kAttnWarps - 1);      // warp pair = page stream
+    const bool is_v = tid >= kAttnThreads;               // value warp of the pair
+    const int role = is_v ? 1 : 0;
+    const int g = lane >> 2, t = lane & 3;
+    const int H = p.H, Hq = H * kGroup;
+    // This warp's look-up tables, held in registers (an opaque move keeps the compiler from re-reading the
+    // parameter bank at every use): score warps the centroids' high / low digit bytes, value warps the low /
+    // high bytes of the fp16 centroids.
+    uint32_t ta0, ta1, tb0, tb1;
+    asm volatile("mov.b32 %0, %1;" : "=r"(ta0) : "r"(is_v ? p.tl0 : p.kh0));
+    asm volatile("mov.b32 %0, %1;" : "=r"(ta1) : "r"(is_v ? p.tl1 : p.kh1));
+    asm volatile("mov.b32 %0, %1;" : "=r"(tb0) : "r"(is_v ? p.th0 : p.kl0));
+    asm volatile("mov.b32 %0, %1;" : "=r"(tb1) : "r"(is_v ? p.th1 : p.kl1));
+    // barrier among the four score warps (the value warps run ahead into the next segment meanwhile)
+    auto bar_score_warps = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+    bool waited = (p.flags & LEANKV_ATTN_EARLY_FETCH) == 0;
+    if (waited) pdl_begin();
+    // Pull the inverse rotation (a constant, 64 KB) towards L2 early: whichever CTA ends up merging
+    // needs it at the very end of the critical path.
+    if (blockIdx.x == 0)
+        for (int i = tid; i < kDim * kDim / 32; i += kSplitThreads)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Pi_v + i * 32));
+
+    const uint32_t bar0 = smem_u32(&s_bar[role][warp][0]);
+    const uint32_t ring0 = smem_u32(&s_ring[role][warp][0][0]);
+    const uint32_t full0 = smem_u32(&s_full[warp][0]), empty0 = smem_u32(&s_empty[warp][0]);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        if (!is_v) {
+#pragma unroll
+            for (int d = 0; d < kDepth; ++d) { mbar_init(full0 + 8 * d, 1); mbar_init(empty0 + 8 * d, 1); }
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();          // the queue barriers of a pair are initialised before its other warp uses them
+
+    // ---- this CTA's share of the flat page list ----
+    // With early fetch everything up to the first pdl_begin() below runs while the launch before this
+    // one may still be executing; it reads only the page table and pages that older launches wrote.
+    // A batch of fewer than 128 sequences has its whole indptr fetched in one go (one memory round trip
+    // before the page ids can be asked for); larger batches read it from global memory as needed.
+    const bool small_b = p.B < kAttnThreads;
+    if (small_b) {
+        if (tid <= p.B && tid < kAttnThreads) s_ip[tid] = p.indptr[tid];
+        __syncthreads();
+    }
+    auto ip = [&](int i) -> int { return small_b ? s_ip[i] : p.indptr[i]; };
+    const int ip0 = ip(0);
+    const long long F = (long long)H * (ip(p.B) - ip0);
+    // sequences without pages produce zeros; CTAs share them out
+    for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
+        if (ip(b + 1) - ip(b) <= 0) {
+            if (!waited) { pdl_begin(); waited = true; }
+            __half* o = p.out + (size_t)b * Hq * kDim;
+            for (int i = tid; i < Hq * kDim; i += kSplitThreads) o[i] = __float2half_rn(0.f);
+        }
+    }
+    long long C = gridDim.x;
+    {
+        // no more CTAs than give each about kMinPagesPerCta pages; whole multiples of the pair count, so that
+        // equal-length sequences are cut into equal pieces that end at pair boundaries
+        const long long pairs = (long long)p.B * H;
+        long long cap = (F + kMinPagesPerCta - 1) / kMinPagesPerCta;
+        if (cap >= pairs) cap = (cap + pairs - 1) / pairs * pairs;
+        if (cap < 1) cap = 1;
+        if (C > cap) C = cap;
+        if (C >= pairs) C -= C % pairs;
+    }
+    if (F <= 0 || (long long)blockIdx.x >= C) {
+        if (!waited) pdl_begin();
+        return;
+    }
+    // floor(c * F / C) and its inverse; 32-bit arithmetic when the products fit (the usual case)
+    const bool fits32 = (F + 1) * C + F < (1ll << 32);
+    auto share_start = [&](long long c) -> long long {
+        return fits32 ? (long long)((unsigned)c * (unsigned)F / (unsigned)C) : c * F / C;
+    };
+    auto cta_of = [&](long long f) -> int {        // the CTA whose share holds flat page f
+        return fits32 ? (int)(((unsigned)(f + 1) * (unsigned)C + (unsigned)F - 1u) / (unsigned)F) - 1
+                      : (int)(((f + 1) * C + F - 1) / F) - 1;
+    };
+    const long long f_lo = share_start(blockIdx.x), f_hi = share_start((long long)blockIdx.x + 1);
+
+    // sequence that holds flat page f_lo: the last b with H * (indptr[b] - indptr[0]) <= f_lo
+    int b;
+    {
+        int lo = 0, hi = p.B;
+        while (hi - lo > 1) {
+            const int step = (hi - lo + kAttnThreads - 1) / kAttnThreads;
+            const long long idx = (long long)lo + (long long)(tid + 1) * step;
+            const bool pred = tid < kAttnThreads && idx < hi && (long long)H * (ip((int)idx) - ip0) <= f_lo;
+            const int cnt = __syncthreads_count(pred);
+            lo += cnt * step;
+            hi = min(hi, lo + step);
+        }
+        b = lo;
+    }
+    int seq_pg0 = ip(b);
+    int n_b = ip(b + 1) - seq_pg0;
+    int kvh, pg;
+    {
+        const long long r = f_lo - (long long)H * (seq_pg0 - ip0);    // < H * n_b
+        kvh = fits32 ? (int)((unsigned)r / (unsigned)n_b) : (int)(r / n_b);
+        pg = (int)(r - (long long)kvh * n_b);
+    }
+
+    const size_t page_stride = (size_t)2 * H * kChunkBytes;       // K chunk of a page -> next page
+    const size_t kv_stride = (size_t)H * kChunkBytes;             // K chunk -> V chunk of that page
+    const int l4 = lane & 3;
+    unsigned phase = 0;              // bit s: parity the next wait on ring slot s looks for
+    unsigned qphase = 0;             // bit d: parity the next wait on queue slot d looks for (full / empty by role)
+    unsigned qcount = 0;             // pages this pair has put through the queue so far
+    unsigned inflight = 0;           // bit s: a copy into ring slot s has been issued and not yet waited for
+    bool failed = false;             // a bounded wait gave up: the warp stops using its ring
+
+    for (long long f = f_lo; f < f_hi;) {
+        const int seg_len = (int)min((long long)(n_b - pg), f_hi - f);
+        if (seg_len <= 0) break;         // cannot happen for a consistent page table; never loop on an inconsistent one
+        const bool whole = seg_len == n_b;
+        // ---- this warp's pages of the segment ----
+        const int w_lo = pg + (int)(((long long)seg_len * warp) / kAttnWarps);
+        const int w_hi = pg + (int)(((long long)seg_len * (warp + 1)) / kAttnWarps);
+        const int n_my = failed ? 0 : w_hi - w_lo;
+        const uint8_t* pool_kvh = p.pool + (size_t)kvh * kChunkBytes;
+        // lane s (s < 4) feeds ring slot s
+        auto issue = [&](int page) {                              // this warp's chunk of the page: key or value
+            const uint8_t* src = pool_kvh + (size_t)(page < 0 ? 0 : page) * page_stride + (is_v ? kv_stride : 0);
+            const uint32_t bar = bar0 + 8 * l4, dst = ring0 + l4 * kChunkBytes;
+            mbar_expect_tx(bar, kChunkBytes);
+            bulk_g2s(dst, src, kChunkBytes, bar);
+        };
+        // Page ids travel in groups of four: lane (any g, l4) holds the id of page base + l4 (lanes with
+        // equal l4 read the same word). Ids outside the pool are flagged once and read as pages without
+        // valid tokens.
+        auto fetch = [&](int base) -> int {
+            int id = 0;
+            if (base + l4 < n_my) {
+                id = p.indices[seq_pg0 + w_lo + base + l4];
+                if (id < 0 || id >= p.n_pages) {
+                    id = -1;
+                    if (lane < 4 && !is_v) atomicOr(p.status, kStatusBadPage);
+                }
+            }
+            return id;
+        };
+        int id_cur = fetch(0), id_nxt = fetch(kStages);
+        // first copies; before the dependency wait the sequence's last page (the one the preceding
+        // launch may be writing the new token into) is left out and issued right after the wait
+        {
+            const int i_seq_last = n_b - 1 - w_lo;
+            const bool mine0 = lane < kStages && lane < n_my;
+            const bool hold = !waited && lane == i_seq_last;
+            if (mine0 && !hold) issue(id_cur);
+            if (!waited) {
+                pdl_begin();
+                waited = true;
+                if (mine0 && hold) issue(id_cur);
+            }
+            inflight |= (1u << min(n_my, kStages)) - 1u;
+        }
+
+        const int last_len = min(max(p.last_len[b], 1), 16);
+        int id_nn = fetch(2 * kStages);                      // two groups ahead, in flight while a group is processed
+        unsigned bad = __ballot_sync(0xffffffffu, id_cur < 0) & 0xFu;
+        // page loop bookkeeping shared by both roles: wait for ring slot s, and refill it afterwards
+        auto next_group = [&](int i) {
+            id_cur = id_nxt;
+            id_nxt = id_nn;
+            id_nn = fetch(i + 1 + 2 * kStages);
+            bad = __ballot_sync(0xffffffffu, id_cur < 0) & 0xFu;
+        };
+
+        if (!is_v) {
+            // ================= score warp =================
+            // Query as the A operand of the integer score MMA. One m16n8k32 step covers 32 coordinates: rows
+            // 0..7 hold the high digit of the query, rows 8..15 its low digit (heads 0..3, repeated in rows
+            // 4..7 so that all lanes do the same work). Multiplied with the centroids' high digits that gives
+            // HH (rows 0..7) and q_lo x c_hi (rows 8..15); with the centroids' low digits q_hi x c_lo and
+            // q_lo x c_lo. Lane (g, t) holds head g & 3, rotated coordinates 32t .. 32t+31; k-block kb covers
+            // coordinates 32t + 8kb .. +7.
+            uint32_t qa[4][4];
+            float kscale;            // score per integer unit of (256 * HH + MID), before the key norm
+            {
+                const int head = g & 3;
+                const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
+                float4 v[8];
+                float amax = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    v[s] = *reinterpret_cast<const float4*>(qp + 4 * s);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[s].x), fabsf(v[s].y)), fmaxf(fabsf(v[s].z), fabsf(v[s].w))));
+                }
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float uq = amax > 0.f ? amax * (1.0f / kFixedMax) : 1.0f;
+                const float inv = 1.0f / uq;
+                kscale = 256.0f * uq * p.c_unit * p.qscale;
+                auto digits = [&](float x, int sh, uint32_t& hi, uint32_t& lo) {
+                    const int qi = __float2int_rn(x * inv);
+                    const int h8 = (qi + 128) >> 8;                       // |qi| <= 32512 keeps this in [-127, 127]
+                    const int l8 = qi - (h8 << 8);                        // balanced low digit in [-128, 127]
+                    hi |= (uint32_t)(h8 & 255) << sh;
+                    lo |= (uint32_t)(l8 & 255) << sh;
+                };
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    uint32_t hi = 0, lo = 0;
+                    digits(v[s].x, 0, hi, lo);
+                    digits(v[s].y, 8, hi, lo);
+                    digits(v[s].z, 16, hi, lo);
+                    digits(v[s].w, 24, hi, lo);
+                    qa[s >> 1][2 * (s & 1)] = hi;          // a0 / a2: rows 0..7, k 0..15 / 16..31
+                    qa[s >> 1][2 * (s & 1) + 1] = lo;      // a1 / a3: rows 8..15
+                }
+            }
+            float m_ref = kNoRef, l_run = 0.f;        // head g & 3, this lane's four tokens per page
+
+            for (int i = 0; i < n_my; ++i) {
+                const int s = i & (kStages - 1);
+                // the verdict is made warp-uniform so that no lane is left behind at a shuffle
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar0 + 8 * s, (phase >> s) & 1u))) {
+                    failed = true;
+                    break;
+                }
+                phase ^= 1u << s;
+                inflight &= ~(1u << s);
+                const int n_valid = ((bad >> s) & 1u) ? 0 : (w_lo + i == n_b - 1 ? last_len : 16);
+                const uint8_t* stage = &s_ring[0][warp][0][0] + s * kChunkBytes;
+                const uint32_t* kw = reinterpret_cast<const uint32_t*>(stage);
+                const uint32_t* kn2 = reinterpret_cast<const uint32_t*>(stage + kNormOffsetBytes);
+
+                // ---- scores: D[row][token], tokens 0..7 in tile 0 and 8..15 in tile 1 ----
+                int dh0[4], dl0[4], dh1[4], dl1[4];       // centroid high / low digits, tile 0 / 1
+                {
+                    const Unit ua = load_unit(kw, lane), ub = load_unit(kw, 32 + lane);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        const uint32_t sa = ua.s[kb], sa2 = sa >> 16, sb = ub.s[kb], sb2 = sb >> 16;
+                        const uint32_t ah0 = __byte_perm(ta0, ta1, sa), ah1 = __byte_perm(ta0, ta1, sa2);
+                        const uint32_t al0 = __byte_perm(tb0, tb1, sa), al1 = __byte_perm(tb0, tb1, sa2);
+                        const uint32_t bh0 = __byte_perm(ta0, ta1, sb), bh1 = __byte_perm(ta0, ta1, sb2);
+                        const uint32_t bl0 = __byte_perm(tb0, tb1, sb), bl1 = __byte_perm(tb0, tb1, sb2);
+                        if (kb == 0) {
+                            mma_s8_16832_bias(dh0, qa[kb], ah0, ah1);
+                            mma_s8_16832_bias(dl0, qa[kb], al0, al1);
+                            mma_s8_16832_bias(dh1, qa[kb], bh0, bh1);
+                            mma_s8_16832_bias(dl1, qa[kb], bl0, bl1);
+                        } else {
+                            mma_s8_16832(dh0, qa[kb], ah0, ah1);
+                            mma_s8_16832(dl0, qa[kb], al0, al1);
+                            mma_s8_16832(dh1, qa[kb], bh0, bh1);
+                            mma_s8_16832(dl1, qa[kb], bl0, bl1);
+                        }
+                    }
+                }
+                // tokens of this lane: 2t, 2t+1 (tile 0) and 8+2t, 9+2t (tile 1); norms as fp16 pairs
+                const float2 kna = h2_to_f2(kn2[t]), knb = h2_to_f2(kn2[4 + t]);
+                __syncwarp();   // every lane has finished reading this slot
+                if (i + kStages < n_my) {
+                    if (lane == s) issue(id_nxt);
+                    inflight |= 1u << s;
+                }
+                // 256 * HH + (q_lo c_hi + q_hi c_lo): c0/c1 of the high-digit tile are HH, its c2/c3 and the
+                // low-digit tile's c0/c1 are the two mixed sums. Every sum carries the accumulator bias; all
+                // three subtractions are exact.
+                auto val = [](const int (&dh)[4], const int (&dl)[4], int c) -> float {
+                    const float mid = (__int_as_float(dh[2 + c]) - 2.f * kBiasF) + __int_as_float(dl[c]);
+                    return fmaf(__int_as_float(dh[c]) - kBiasF, 256.f, mid);
+                };
+                const float v0 = val(dh0, dl0, 0), v1 = val(dh0, dl0, 1), v2 = val(dh1, dl1, 0), v3 = val(dh1, dl1, 1);
+                const float k0 = kscale * kna.x, k1 = kscale * kna.y, k2 = kscale * knb.x, k3 = kscale * knb.y;
+                // scores relative to the reference value (log2 domain; the scale carries log2 e)
+                float s0 = fmaf(v0, k0, -m_ref), s1 = fmaf(v1, k1, -m_ref), s2 = fmaf(v2, k2, -m_ref),
+                      s3 = fmaf(v3, k3, -m_ref);
+                // tokens beyond n_valid are masked out
+                const bool x0 = 2 * t >= n_valid, x1 = 2 * t + 1 >= n_valid, x2 = 8 + 2 * t >= n_valid, x3 = 9 + 2 * t >= n_valid;
+                if (x0) s0 = -INFINITY;
+                if (x1) s1 = -INFINITY;
+                if (x2) s2 = -INFINITY;
+                if (x3) s3 = -INFINITY;
+                // ---- online softmax ----
+                float fsc = 1.0f;                        // factor the value warp applies to this head's accumulators first
+                const float mx = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
+                if (__any_sync(0xffffffffu, mx > kRescaleSlack)) {
+                    // some head's reference value moves: its lanes agree on the page's true maximum as the new one
+                    float mh = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, 2));
+                    const float r0 = x0 ? -INFINITY : v0 * k0, r1 = x1 ? -INFINITY : v1 * k1;
+                    const float r2 = x2 ? -INFINITY : v2 * k2, r3 = x3 ? -INFINITY : v3 * k3;
+                    float tm = fmaxf(fmaxf(r0, r1), fmaxf(r2, r3));
+                    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+                    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+                    if (mh > kRescaleSlack) {
+                        fsc = ex2_approx(m_ref - tm);          // 0 on the first page (m_ref = kNoRef)
+                        l_run *= fsc;
+                        m_ref = tm;
+                        s0 = r0 - tm; s1 = r1 - tm; s2 = r2 - tm; s3 = r3 - tm;
+                    }
+                }
+                const float p0 = ex2_approx(s0), p1 = ex2_approx(s1), p2 = ex2_approx(s2), p3 = ex2_approx(s3);
+                l_run += (p0 + p1) + (p2 + p3);
+                // ---- hand the page's probabilities to the value warp ----
+                const unsigned d = qcount & (kDepth - 1);
+                if (qcount >= (unsigned)kDepth) {            // the slot has been used before: wait until it was read
+                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(empty0 + 8 * d, (qphase >> d) & 1u))) {
+                        failed = true;
+                        break;
+                    }
+                    qphase ^= 1u << d;
+                }
+                s_prob[warp][d][lane] = make_float4(p0, p1, p2, p3);
+                s_fsc[warp][d][lane] = fsc;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * d);
+                ++qcount;
+                if (s == kStages - 1) next_group(i);
+            }
+            // ---- warp result -> shared memory ----
+            l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+            l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+            if (g < 4 && t == 0) {                     // lanes g >= 4 hold copies of heads 0..3
+                s_m[warp][g] = m_ref;
+                s_l[warp][g] = l_run;
+            }
+        } else {
+            // ================= value warp =================
+            float acc[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+            for (int i = 0; i < n_my; ++i) {
+                const int s = i & (kStages - 1);
+                const unsigned d = qcount & (kDepth - 1);
+                bool ok = mbar_wait_bounded(bar0 + 8 * s, (phase >> s) & 1u);
+                ok = ok && mbar_wait_bounded(full0 + 8 * d, (qphase >> d) & 1u);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    failed = true;
+                    break;
+                }
+                phase ^= 1u << s;
+                qphase ^= 1u << d;
+                inflight &= ~(1u << s);
+                const float4 pr = s_prob[warp][d][lane];
+                const float fsc = s_fsc[warp][d][lane];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * d);
+                ++qcount;
+                if (__any_sync(0xffffffffu, fsc != 1.0f)) {
+                    // a head's reference value moved: rescale the accumulator columns of the heads this lane holds
+                    const float fa = __shfl_sync(0xffffffffu, fsc, ((2 * t) & 3) * 4);
+                    const float fb = __shfl_sync(0xffffffffu, fsc, ((2 * t + 1) & 3) * 4);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        acc[j][0] *= fa; acc[j][2] *= fa;
+                        acc[j][1] *= fb; acc[j][3] *= fb;
+                    }
+                }
+                const int n_valid = ((bad >> s) & 1u) ? 0 : (w_lo + i == n_b - 1 ? last_len : 16);
+                const uint8_t* stage = &s_ring[1][warp][0][0] + s * kChunkBytes;
+                const uint32_t* vw = reinterpret_cast<const uint32_t*>(stage);
+                const uint32_t* vn2 = reinterpret_cast<const uint32_t*>(stage + kNormOffsetBytes);
+                float2 vna = h2_to_f2(vn2[t]), vnb = h2_to_f2(vn2[4 + t]);
+                if (2 * t >= n_valid) vna.x = 0.f;            // masked tokens carry probability 0; their norm may be stale
+                if (2 * t + 1 >= n_valid) vna.y = 0.f;
+                if (8 + 2 * t >= n_valid) vnb.x = 0.f;
+                if (9 + 2 * t >= n_valid) vnb.y = 0.f;
+                // Probabilities (times value norms) arrive in the layout of the value MMA's B operand: rows =
+                // tokens 2t, 2t+1, 2t+8, 2t+9, column g = head g & 3 (columns 4..7 repeat 0..3 and are never
+                // stored). fp16 rounding of the probabilities is independent from token to token and averages
+                // out over the sum.
+                const uint32_t b0 = pack_h2(pr.x * vna.x, pr.y * vna.y);
+                const uint32_t b1 = pack_h2(pr.z * vnb.x, pr.w * vnb.y);
+                {
+                    const Unit ua = load_unit(vw, lane), ub = load_unit(vw, 32 + lane);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t sa2 = ua.s[j >> 1] >> (16 * (j & 1));
+                        const uint32_t sb2 = ub.s[j >> 1] >> (16 * (j & 1));
+                        const uint32_t la = __byte_perm(ta0, ta1, sa2), ha = __byte_perm(tb0, tb1, sa2);
+                        const uint32_t lb = __byte_perm(ta0, ta1, sb2), hb = __byte_perm(tb0, tb1, sb2);
+                        mma_16816(acc[j], __byte_perm(la, ha, 0x5140), __byte_perm(la, ha, 0x7362),
+                                  __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362), b0, b1);
+                    }
+                }
+                __syncwarp();   // every lane has finished reading this slot
+                if (i + kStages < n_my) {
+                    if (lane == s) issue(id_nxt);
+                    inflight |= 1u << s;
+                }
+                if (s == kStages - 1) next_group(i);
+            }
+            if (t < 2) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // rows g / g+8 of m-tile j are rotated coordinates 16g+2j / 16g+2j+1; columns 2t, 2t+1
+                    // are heads 2t and 2t+1.
+                    *reinterpret_cast<float2*>(&s_res[warp][2 * t][16 * g + 2 * j]) = make_float2(acc[j][0], acc[j][2]);
+                    *reinterpret_cast<float2*>(&s_res[warp][2 * t + 1][16 * g + 2 * j]) = make_float2(acc[j][1], acc[j][3]);
+                }
+            }
+        }
+        if (failed && inflight != 0) {
+            // Give the copies still in flight a bounded chance to land before the CTA can exit.
+            if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+#pragma unroll
+            for (int s = 0; s < kStages; ++s)
+                if ((inflight >> s) & 1u) mbar_wait_bounded(bar0 + 8 * s, (phase >> s) & 1u);
+            inflight = 0;
+        }
+        __syncthreads();                       // both roles' results are in shared memory
+
+        if (!is_v) {
+        // ---- CTA merge over its 4 warps: thread = rotated coordinate ----
+        float o[kGroup], mh[kGroup], lh[kGroup];
+#pragma unroll
+        for (int h = 0; h < kGroup; ++h) {
+            float m = s_m[0][h];
+#pragma unroll
+            for (int w = 1; w < kAttnWarps; ++w) m = fmaxf(m, s_m[w][h]);
+            float ov = 0.f, lv = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; ++w) {
+                const float fw = ex2_approx(s_m[w][h] - m);
+                ov = fmaf(fw, s_res[w][h][tid], ov);
+                lv = fmaf(fw, s_l[w][h], lv);
+            }
+            o[h] = ov; mh[h] = m; lh[h] = lv;
+        }
+        bar_score_warps();                       // s_res / s_m / s_l may be overwritten from here on
+
+        bool finish = whole;
+        if (!whole) {
+            // partial slot: 1 if this pair started in an earlier part of this CTA's share (it is then
+            // the CTA's last segment), 0 if the CTA's share starts inside or at the start of the pair
+            const long long o_p = (long long)H * (seq_pg0 - ip0) + (long long)kvh * n_b;
+            const int slot = f_lo < o_p ? 1 : 0;
+            float* mine = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPartialFloats;
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) mine[h * kDim + tid] = o[h];
+            if (tid < kGroup) {
+                mine[kGroup * kDim + tid] = mh[tid];
+                mine[kGroup * kDim + kGroup + tid] = lh[tid];
+            }
+            __threadfence();
+            bar_score_warps();
+            const int c_first = cta_of(o_p), c_last = cta_of(o_p + n_b - 1);
+            const int n_seg = c_last - c_first + 1;
+            if (tid == 0) {
+                const int prev = atomicAdd(&p.counters[b * H + kvh], 1);
+                __threadfence();               // the other CTAs' partials are read after this point
+                s_last = (prev == n_seg - 1);
+            }
+            bar_score_warps();
+            if (s_last) {
+                // last CTA of this (sequence, kv head): merge the partials in CTA order. Maxima / sums and the
+                // value rows of the first pieces travel in the same round trip.
+                float* s_ml = &s_res[0][0][0];                            // [n_seg][2 * kGroup]: m then l
+                const int first_slot = share_start(c_first) < o_p ? 1 : 0;
+                auto part_of = [&](int k) -> const float* {
+                    return p.partials + ((size_t)(c_first + k) * 2 + (k == 0 ? first_slot : 0)) * kPartialFloats;
+                };
+                // a pair cut into more pieces than the staging area holds (one very long sequence among
+                // short ones) reads its maxima / sums from the workspace directly
+                const bool staged = n_seg * 2 * kGroup <= kAttnWarps * kGroup * kDim;
+                auto ml = [&](int k, int j) -> float {
+                    return staged ? s_ml[k * 2 * kGroup + j] : ld_cg_f32(part_of(k) + kGroup * kDim + j);
+                };
+                if (staged)
+                    for (int i = tid; i < n_seg * 2 * kGroup; i += kAttnThreads)
+                        s_ml[i] = ld_cg_f32(part_of(i >> 3) + kGroup * kDim + (i & 7));
+                constexpr int kMergeBatch = 12;
+                float ov0[kMergeBatch][kGroup];
+#pragma unroll
+                for (int k = 0; k < kMergeBatch; ++k) {
+                    const float* pc = part_of(k < n_seg ? k : 0) + tid;
+#pragma unroll
+                    for (int h = 0; h < kGroup; ++h) ov0[k][h] = k < n_seg ? ld_cg_f32(pc + h * kDim) : 0.f;
+                }
+                bar_score_warps();
+                float mg[kGroup];
+#pragma unroll
+                for (int h = 0; h < kGroup; ++h) {
+                    float m = kNoRef;
+                    for (int k = 0; k < n_seg; ++k) m = fmaxf(m, ml(k, h));
+                    mg[h] = m;
+                    o[h] = 0.f;
+                    lh[h] = 0.f;
+                }
+#pragma unroll
+                for (int k = 0; k < kMergeBatch; ++k) {
+                    if (k < n_seg) {
+#pragma unroll
+                        for (int h = 0; h < kGroup; ++h) {
+                            const float fc = ex2_approx(ml(k, h) - mg[h]);
+                            o[h] = fmaf(fc, ov0[k][h], o[h]);
+                            lh[h] = fmaf(fc, ml(k, kGroup + h), lh[h]);
+                        }
+                    }
+                }
+#pragma unroll 4
+                for (int k = kMergeBatch; k < n_seg; ++k) {
+                    const float* pc = part_of(k) + tid;
+                    float ov[kGroup];
+#pragma unroll
+                    for (int h = 0; h < kGroup; ++h) ov[h] = ld_cg_f32(pc + h * kDim);
+#pragma unroll
+                    for (int h = 0; h < kGroup; ++h) {
+                        const float fc = ex2_approx(ml(k, h) - mg[h]);
+                        o[h] = fmaf(fc, ov[h], o[h]);
+                        lh[h] = fmaf(fc, ml(k, kGroup + h), lh[h]);
+                    }
+                }
+                bar_score_warps();                                          // s_ml is overwritten below
+                if (tid == 0) p.counters[b * H + kvh] = 0;
+                finish = true;
+            }
+        }
+
+        if (finish) {
+            // ---- normalise, undo the centroid scale, rotate back: out = o @ Pi_v ----
+            float* s_o = &s_res[0][0][0];                                 // [kGroup][kDim]
+            float* s_part = &s_res[1][0][0];                              // [kAttnWarps - 1][kGroup][kDim]
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) s_o[h * kDim + tid] = lh[h] > 0.f ? o[h] * (p.inv_alpha / lh[h]) : 0.f;
+            bar_score_warps();
+            // warp w sums rows 32w .. 32w+31 of Pi_v for 4 output columns per lane (coalesced 16-byte loads)
+            float r[kGroup][4];
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) r[h][0] = r[h][1] = r[h][2] = r[h][3] = 0.f;
+            const float4* pv = reinterpret_cast<const float4*>(p.Pi_v) + (size_t)(32 * warp) * (kDim / 4) + lane;
+#pragma unroll 16
+            for (int ii = 0; ii < 32; ++ii) {
+                const float4 w4 = __ldg(pv + (size_t)ii * (kDim / 4));
+                const int i = 32 * warp + ii;
+#pragma unroll
+                for (int h = 0; h < kGroup; ++h) {
+                    const float sv = s_o[h * kDim + i];
+                    r[h][0] = fmaf(sv, w4.x, r[h][0]);
+                    r[h][1] = fmaf(sv, w4.y, r[h][1]);
+                    r[h][2] = fmaf(sv, w4.z, r[h][2]);
+                    r[h][3] = fmaf(sv, w4.w, r[h][3]);
+                }
+            }
+            bar_score_warps();                                              // everyone has read s_o
+            if (warp > 0) {
+#pragma unroll
+                for (int h = 0; h < kGroup; ++h)
+                    *reinterpret_cast<float4*>(&s_part[((warp - 1) * kGroup + h) * kDim + 4 * lane]) =
+                        make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);
+            }
+            bar_score_warps();
+            if (warp == 0) {
+                __half* out_base = p.out + ((size_t)b * Hq + (size_t)kvh * kGroup) * kDim;
+#pragma unroll
+                for (int h = 0; h < kGroup; ++h) {
+                    float4 v = make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);
+#pragma unroll
+                    for (int w = 0; w < kAttnWarps - 1; ++w) {
+                        const float4 a = *reinterpret_cast<const float4*>(&s_part[(w * kGroup + h) * kDim + 4 * lane]);
+                        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    }
+                    const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&h01);
+                    pk.y = *reinterpret_cast<const uint32_t*>(&h23);
+                    *reinterpret_cast<uint2*>(out_base + h * kDim + 4 * lane) = pk;
+                }
+            }
+            bar_score_warps();                                              // s_res is free for the next segment
+        }
+        }   // score warps
+
+        // ---- advance to the next pair ----
+        f += seg_len;
+        pg += seg_len;
+        if (pg >= n_b && f < f_hi) {
+            pg = 0;
+            if (++kvh == H) {
+                kvh = 0;
+                do {
+                    ++b;
+                    seq_pg0 = ip(b);
+                    n_b = ip(b + 1) - seq_pg0;
+                } while (n_b <= 0 && b + 1 < p.B);
+            }
+        }
+    }
+}

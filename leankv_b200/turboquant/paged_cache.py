@@ -7,6 +7,12 @@ kernel behind ``leankv_tq_decode_attn``; FlashInfer is not needed. Page-table co
 (``kv_indptr`` / ``kv_page_indices`` / ``kv_last_page_len`` int32, LIFO free list, one
 page table shared by all layers) are the reference's (``paged_cache.py:78,96-115,215-233``).
 
+The page table lives on the device: a free-page stack, a block table (pages of each sequence in
+order) and the sequence lengths are advanced by one small kernel per step
+(``leankv_paged_table_step``), which also rebuilds the flat arrays the append and attention calls
+read. The host only mirrors the lengths as integers (HF asks for them every step, and pool
+exhaustion is raised before anything is launched); it builds no per-token lists or tensors.
+
 ``update`` appends through the fused rotate+quantize+pack kernel and, for HF
 compatibility, returns dense K/V de-quantized from the pages; ``decode_attention`` is the
 fast path.
@@ -57,50 +63,93 @@ class PagedKVCache:
         self._centroids_host = self.key_quantizers[0].centroids.float().cpu().contiguous()
         self._bounds = self.key_quantizers[0].decision_boundaries.float().contiguous()
 
-        self._free_pages = list(range(max_pages))
-        self._seq_page_indices: list[list[int]] = []
-        self._seq_lengths: list[int] = []
+        self._seq_lengths: list[int] = []     # host mirror of the device lengths (plain integers)
         self._batch_size = 0
-        self._pending_start: list[int] = []   # start positions of the append in flight (per layer pass)
-        self._meta = None                     # device copies of the page table, rebuilt when stale
+        self._free_count = max_pages          # host mirror of the free stack's height
         self._workspace = None
-        self._start_dev = None
         self.fused_decode = False             # set by hf_attention.enable_paged_attention
+        self._alloc_tables(0)
 
-    # ── page management ────────────────────────────────────────────────
+    # ── page table (device) ─────────────────────────────────────────────
 
-    def _allocate_page(self) -> int:
-        if not self._free_pages:
-            raise RuntimeError(
-                f"PagedKVCache: out of pages ({self.max_pages} used). "
-                f"Increase max_pages or reduce batch/sequence length.")
-        return self._free_pages.pop()
-
-    def _free_sequence_pages(self, batch_idx: int):
-        self._free_pages.extend(self._seq_page_indices[batch_idx])
-        self._seq_page_indices[batch_idx] = []
-        self._seq_lengths[batch_idx] = 0
-        self._meta = None
+    def _alloc_tables(self, batch_cap: int):
+        """(Re)allocate the per-sequence device arrays for ``batch_cap`` sequences, keeping their content.
+        The first call also creates the free stack (LIFO like the reference's list: page
+        ``max_pages - 1`` is handed out first)."""
+        dev, i32 = self._device, torch.int32
+        old_table = getattr(self, "_block_table", None)
+        old_len = getattr(self, "_seq_len_dev", None)
+        rows = max(batch_cap, 1)
+        self._batch_cap = batch_cap
+        self._pps_cap = self.max_pages                       # a single sequence may take the whole pool
+        self._block_table = torch.zeros(rows, self._pps_cap, dtype=i32, device=dev)
+        self._seq_len_dev = torch.zeros(rows, dtype=i32, device=dev)
+        self._kv_indptr = torch.zeros(rows + 1, dtype=i32, device=dev)
+        self._kv_last = torch.zeros(rows, dtype=i32, device=dev)
+        self._start_dev = torch.zeros(rows, dtype=i32, device=dev)
+        if old_table is None:
+            self._free_stack = torch.arange(self.max_pages, dtype=i32, device=dev)
+            self._free_top = torch.full((1,), self.max_pages, dtype=i32, device=dev)
+            self._kv_page_indices = torch.zeros(self.max_pages, dtype=i32, device=dev)
+            self._status = torch.zeros(1, dtype=i32, device=dev)
+        else:
+            n = old_table.shape[0]
+            self._block_table[:n] = old_table
+            self._seq_len_dev[:n] = old_len
+        self._meta_batch = -1                                # batch size the flat arrays were built for
 
     def _ensure_batch_size(self, batch_size: int):
-        while len(self._seq_page_indices) < batch_size:
-            self._seq_page_indices.append([])
+        if batch_size > self._batch_cap:
+            self._alloc_tables(batch_size)
+        while len(self._seq_lengths) < batch_size:
             self._seq_lengths.append(0)
         self._batch_size = max(self._batch_size, batch_size)
 
+    def _table_step(self, t_new: int, batch: int):
+        """Advance every sequence by ``t_new`` tokens on the device and rebuild the flat arrays."""
+        with torch.cuda.device(self._device):
+            rc = _native.lib().leankv_paged_table_step(
+                t_new, batch, self._seq_len_dev.data_ptr(), self._block_table.data_ptr(), self._pps_cap,
+                self._free_stack.data_ptr(), self._free_top.data_ptr(), self._kv_indptr.data_ptr(),
+                self._kv_page_indices.data_ptr(), self._kv_last.data_ptr(), self._start_dev.data_ptr(),
+                self._status.data_ptr(), _native.current_stream())
+        _native.check(rc, "leankv_paged_table_step")
+        self._meta_batch = batch
+
+    def _allocate_page(self) -> int:
+        """Pop one page off the free stack (the reference's method of this name, ``paged_cache.py:96-103``).
+        The step kernel does this for whole batches; this single-page form reads the id back to the host."""
+        if self._free_count == 0:
+            raise RuntimeError(
+                f"PagedKVCache: out of pages ({self.max_pages} used). "
+                f"Increase max_pages or reduce batch/sequence length.")
+        page = int(self._free_stack[self._free_count - 1])
+        self._free_top -= 1
+        self._free_count -= 1
+        return page
+
+    def _free_sequence_pages(self, batch_idx: int):
+        """Return a sequence's pages to the stack (in order, so that the last one is reused first)."""
+        n = math.ceil(self._seq_lengths[batch_idx] / PAGE)
+        if n:
+            top = self._free_count                               # stack height == free pages
+            self._free_stack[top:top + n] = self._block_table[batch_idx, :n]
+            self._free_top += n
+            self._free_count += n
+        self._seq_len_dev[batch_idx] = 0
+        self._seq_lengths[batch_idx] = 0
+        self._meta_batch = -1
+
     def _device_meta(self, batch_size: int):
         """(kv_indptr, kv_page_indices, kv_last_page_len) int32 on the device."""
-        if self._meta is None or self._meta[3] != batch_size:
-            indptr, flat, last = [0], [], []
-            for b in range(batch_size):
-                pages = self._seq_page_indices[b]
-                flat.extend(pages)
-                indptr.append(len(flat))
-                rem = self._seq_lengths[b] % PAGE
-                last.append(rem if rem > 0 else PAGE)
-            mk = lambda v: torch.tensor(v if v else [0], dtype=torch.int32, device=self._device)
-            self._meta = (mk(indptr), mk(flat), mk(last), batch_size)
-        return self._meta[:3]
+        if self._meta_batch != batch_size:
+            self._ensure_batch_size(batch_size)
+            self._table_step(0, batch_size)                      # rebuild only
+        return self._kv_indptr, self._kv_page_indices, self._kv_last
+
+    def page_table_status(self) -> int:
+        """Device status word of the page table (0 = clean, 1 = pool exhausted, 2 = block table row full)."""
+        return int(self._status.item())
 
     # ── appends ────────────────────────────────────────────────────────
 
@@ -121,21 +170,21 @@ class PagedKVCache:
         _native.require_cuda(key_states, "key_states")
         batch, _, t_new, _ = key_states.shape
         if layer_idx == 0:
-            # the page table is shared by all layers: pages are assigned once per step
+            # the page table is shared by all layers: pages are assigned once per step, on the device;
+            # the host checks the pool size with integer arithmetic first (same error as the reference)
             self._seen_tokens += t_new
             self._ensure_batch_size(batch)
-            self._pending_start = list(self._seq_lengths[:batch])
+            need = sum(math.ceil((n + t_new) / PAGE) - math.ceil(n / PAGE) for n in self._seq_lengths[:batch])
+            if need > self._free_count:
+                raise RuntimeError(
+                    f"PagedKVCache: out of pages ({self.max_pages} used). "
+                    f"Increase max_pages or reduce batch/sequence length.")
+            self._table_step(t_new, batch)
+            self._free_count -= need
             for b in range(batch):
-                need = math.ceil((self._seq_lengths[b] + t_new) / PAGE)
-                while len(self._seq_page_indices[b]) < need:
-                    self._seq_page_indices[b].append(self._allocate_page())
                 self._seq_lengths[b] += t_new
-            self._meta = None
-            self._start_dev = torch.tensor(self._pending_start[:batch], dtype=torch.int32, device=self._device)
         indptr, flat, _ = self._device_meta(batch)
-        if self._start_dev is None or self._start_dev.numel() != batch:
-            self._start_dev = torch.tensor(self._pending_start[:batch], dtype=torch.int32, device=self._device)
-        start = self._start_dev          # one host-to-device copy per step, shared by all layers
+        start = self._start_dev          # written by the table step, shared by all layers
         k = key_states.to(torch.float16).contiguous()
         v = value_states.to(torch.float16).contiguous()
         kq, vq = self.key_quantizers[layer_idx], self.val_quantizers[layer_idx]
@@ -150,8 +199,7 @@ class PagedKVCache:
     def unpack_sequence(self, layer_idx: int, batch_idx: int, which: int):
         """Codes (uint8 [Hkv, T, 64], reference nibble format) and norms (fp32 [Hkv, T]) of one sequence."""
         t = self._seq_lengths[batch_idx]
-        pages = torch.tensor(self._seq_page_indices[batch_idx] or [0], dtype=torch.int32,
-                             device=self._device)
+        pages = self._block_table[batch_idx, :max(math.ceil(t / PAGE), 1)]      # device view, no host list
         idx = torch.empty(self.num_kv_heads, t, 64, dtype=torch.uint8, device=self._device)
         norms = torch.empty(self.num_kv_heads, t, dtype=torch.float32, device=self._device)
         with torch.cuda.device(self._device):
@@ -186,7 +234,7 @@ class PagedKVCache:
         _native.require_cuda(query, "query")
         batch = query.shape[0]
         indptr, flat, last = self._device_meta(batch)
-        max_pages_seq = max(len(p) for p in self._seq_page_indices[:batch])
+        max_pages_seq = max(math.ceil(n / PAGE) for n in self._seq_lengths[:batch])
         q = query.to(torch.float16).contiguous()
         out = torch.empty_like(q)
         lib = _native.lib()
@@ -247,14 +295,12 @@ class PagedKVCache:
         pass
 
     def reset(self):
-        self._free_pages = list(range(self.max_pages))
-        self._seq_page_indices = []
         self._seq_lengths = []
         self._batch_size = 0
         self._seen_tokens = 0
-        self._meta = None
-        self._start_dev = None
-        self._pending_start = []
+        self._free_count = self.max_pages
+        self._block_table = None
+        self._alloc_tables(0)
         self.kv_data.zero_()
 
     @property
@@ -301,7 +347,7 @@ class PagedKVCache:
     # ── diagnostics ────────────────────────────────────────────────────
 
     def get_pages_used(self) -> int:
-        return self.max_pages - len(self._free_pages)
+        return self.max_pages - self._free_count
 
     def bytes_per_page(self) -> int:
         """Bytes one page occupies in one layer (K and V, all kv heads)."""

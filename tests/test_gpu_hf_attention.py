@@ -50,8 +50,8 @@ def test_fused_decode_matches_dense_route_and_generate_runs(capsys):
     assert errs[0] < 1e-6                     # the prompt pass is the same code either way
     assert max(errs) < 1e-2                   # fp16 K_hat/V_hat + SDPA vs fp32 accumulation on the codes
     # same pages either way: the appended codes do not depend on which attention ran
-    assert torch.equal(cache.kv_data[0][cache._seq_page_indices[0][0]],
-                       dense_cache.kv_data[0][dense_cache._seq_page_indices[0][0]])
+    assert torch.equal(cache.kv_data[0][int(cache._block_table[0, 0])],
+                       dense_cache.kv_data[0][int(dense_cache._block_table[0, 0])])
 
     # stock generate() on a fresh cache
     reset_optimizations(model)

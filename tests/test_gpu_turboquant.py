@@ -443,3 +443,58 @@ def test_tensor_core_append_writes_the_same_pool_as_the_fp32_kernel_on_all_of_co
     assert out["tc"][0] == out["fp32"][0]
     assert out["tc"][2] == 2 * 16 * 8 * 4096 * 128 and out["fp32"][2] == 0
     assert 0 < out["tc"][1] < 0.02 * out["tc"][2]
+
+
+def test_paged_cache_page_table_on_device_follows_the_reference_allocator():
+    """Pages are handed out by the device kernel exactly as the reference's host loops would
+    (LIFO free list, sequence 0 first, one shared table for all layers), including reuse after a
+    sequence has been freed; exhaustion raises before anything is launched."""
+    import math
+
+    dev = _dev()
+    cache = PagedKVCache(num_layers=1, num_kv_heads=2, num_q_heads=8, max_pages=24, device=dev)
+    free = list(range(24))                      # the reference's bookkeeping, restated
+    seq_pages = [[], [], []]
+    lens = [0, 0, 0]
+
+    def ref_step(t_new):
+        for b in range(3):
+            need = math.ceil((lens[b] + t_new) / 16)
+            while len(seq_pages[b]) < need:
+                seq_pages[b].append(free.pop())
+            lens[b] += t_new
+
+    def check():
+        table = cache._block_table.cpu()
+        for b in range(3):
+            assert table[b, :len(seq_pages[b])].tolist() == seq_pages[b]
+        assert cache._seq_len_dev[:3].tolist() == lens and cache._seq_lengths == lens
+        assert int(cache._free_top) == len(free) == 24 - cache.get_pages_used()
+        assert cache._free_stack[:len(free)].tolist() == free
+        flat = [p for b in range(3) for p in seq_pages[b]]
+        assert cache._kv_page_indices[:len(flat)].tolist() == flat
+        assert cache._kv_indptr[:4].tolist() == [0] + list(np.cumsum([len(p) for p in seq_pages]))
+        assert cache._kv_last[:3].tolist() == [(n % 16) or 16 for n in lens]
+        assert cache.page_table_status() == 0
+
+    gen = torch.Generator().manual_seed(5)
+    for t_new in (33, 1, 1, 14, 1, 20):
+        k = torch.randn(3, 2, t_new, 128, generator=gen).half().to(dev)
+        cache.append(0, k, k)
+        ref_step(t_new)
+        check()
+    # free sequence 1, then grow again: its pages come back in LIFO order
+    cache._free_sequence_pages(1)
+    free.extend(seq_pages[1]); seq_pages[1] = []; lens[1] = 0
+    k = torch.randn(3, 2, 17, 128, generator=gen).half().to(dev)
+    cache.append(0, k, k)
+    ref_step(17)
+    check()
+    with pytest.raises(RuntimeError, match="out of pages"):
+        big = torch.zeros(3, 2, 400, 128, dtype=torch.float16, device=dev)
+        cache.append(0, big, big)
+    check()                                     # nothing changed
+    # the device backstop: ask the kernel for more pages than the stack holds
+    rc = cache._table_step(4000, 3)
+    assert cache.page_table_status() & 1
+    assert cache._seq_len_dev[:3].tolist() == lens          # no sequence grew
