@@ -482,6 +482,51 @@ def _leg_attn(out, lib, st, dev, peak_gbs, iters):
     out["tq_decode_attn_rotated_b16_t4096"] = {"us": t4 * 1e6, "algorithmic_bytes": alg4, "gbs": alg4 / t4 / 1e9,
                                                "frac": alg4 / t4 / 1e9 / peak_gbs, "launches_timed": iters}
 
+    # chunked-prefill attention on the packed pages: the 512-token prompt of config 4 (sequence 0's first 32
+    # pages), and a 512-token chunk at the end of a 4096-token context; beside it the route it replaces
+    # (unpack + de-quantize the context to fp16 + library attention)
+    import torch.nn.functional as F
+    for start in (0, T - 512):
+        Tc = 512
+        qp = torch.randn(Tc, 32, 128, generator=torch.Generator().manual_seed(5)).half().to(dev)
+        op = torch.empty_like(qp)
+        wsp = torch.zeros(lib.leankv_tq_prefill_attn_workspace_bytes(Tc, start, 32, H), dtype=torch.uint8, device=dev)
+        fn5 = lambda i: lib.leankv_tq_prefill_attn(qp.data_ptr(), op.data_ptr(), Tc, start, 32, H,
+                                                   pools[i].data_ptr(), kv.n_pages, pages0.data_ptr(),
+                                                   Pk.data_ptr(), Pv.data_ptr(), cents_h.data_ptr(),
+                                                   1.0 / math.sqrt(128.0), wsp.data_ptr(), wsp.numel(), st)
+        t5 = time_kernel(fn5, len(pools), max(10, iters // 10), warmup=3)
+        n_ctx = start + Tc
+        cents_d = cents_h.to(dev)
+
+        def dense_route(i):
+            hats = []
+            for which, Pi in ((0, Pk), (1, Pv)):
+                idx = torch.empty(H, n_ctx, 64, dtype=torch.uint8, device=dev)
+                nrm = torch.empty(H, n_ctx, dtype=torch.float32, device=dev)
+                lib.leankv_tq_pool_unpack(pools[i].data_ptr(), kv.n_pages, H, pages0.data_ptr(), n_ctx, which,
+                                          idx.data_ptr(), nrm.data_ptr(), st)
+                hat = torch.empty(1, H, n_ctx, 128, dtype=torch.float16, device=dev)
+                lib.leankv_tq_dequantize(idx.data_ptr(), nrm.data_ptr(), H * n_ctx, 128, 3, Pi.data_ptr(),
+                                         cents_d.data_ptr(), hat.data_ptr(), 0, st)
+                hats.append(hat)
+            mask = None
+            if start:
+                mask = (torch.arange(n_ctx, device=dev)[None, :] <= (start + torch.arange(Tc, device=dev))[:, None])
+            return F.scaled_dot_product_attention(qp.transpose(0, 1).unsqueeze(0), hats[0], hats[1], attn_mask=mask,
+                                                  is_causal=mask is None, enable_gqa=True)
+
+        t6 = time_kernel(dense_route, len(pools), max(10, iters // 10), warmup=3)
+        torch.cuda.synchronize()
+        ref = dense_route(0).squeeze(0).transpose(0, 1).float()
+        fn5(0)
+        torch.cuda.synchronize()
+        rel = float(((op.float() - ref).norm() / ref.norm()))
+        out[f"tq_prefill_attn_t{Tc}_ctx{n_ctx}"] = {
+            "us": t5 * 1e6, "launches_timed": 3 * max(10, iters // 10),
+            "dequantize_plus_library_attention_us": t6 * 1e6, "rel_l2_vs_that_route": rel,
+            "fp16_kv_bytes_never_materialised": 2 * H * n_ctx * 256}
+
 
 # ── GPU comparators: the reference's own GPU code and a stock fp16 paged decode, outside the product path ──
 

@@ -235,6 +235,26 @@ int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int B, int n_q_
  * ever gave up). Copied to *status with a synchronous 4-byte copy from `workspace`. */
 int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
 
+/* Causal attention of a chunk of T prompt tokens (absolute positions start_pos .. start_pos+T-1) of ONE
+ * sequence over its packed pages — the chunked-prefill counterpart of leankv_tq_decode_attn. The
+ * chunk's K/V must already be in the pool (leankv_tq_pool_append before this call), so that, like the
+ * reference's TurboQuantCache with hot_buffer_size = 0 (leankv/turboquant/cache.py:84-127: update()
+ * returns de-quantized K/V for all tokens, the new ones included), every token attends to quantized
+ * keys and values only, and never to an fp16 copy. Replaces, for prompt chunks, cache.update +
+ * eager attention (leankv/turboquant/cache.py:136-142, transformers modeling_mistral.py:96-117).
+ * q, out: [T][n_q_heads][128] fp16. seq_pages (device): the sequence's page ids in order, at least
+ * (start_pos + T + 15) / 16 of them. Row t of the chunk is computed by the decode kernel as one row of
+ * a batch whose page list ends at position start_pos + t (the causal mask is the page table), so it
+ * agrees with a decode step at that position up to the rounding of the partial merge (the split of
+ * a row's pages over CTAs depends on the batch). The workspace rules of leankv_tq_decode_attn apply
+ * (zeroed once, first word = status); two launches (page-table rows, query rotation) precede the
+ * attention kernel. */
+size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, int n_q_heads, int n_kv_heads);
+int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads, int n_kv_heads,
+                           const void* pool, int n_pages, const int32_t* seq_pages, const float* Pi_k,
+                           const float* Pi_v, const float* centroids, float scale, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------- *
  * Glue kernels of a batch-1 decode step (no reference counterpart: the reference leaves
  * these steps to the HF modules around its hooks — MistralRMSNorm, apply_rotary_pos_emb,

@@ -90,6 +90,10 @@ SIGNATURES = {
     "leankv_decode_qkv_post": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "leankv_tq_decode_attn_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "leankv_tq_prefill_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "leankv_tq_prefill_attn": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_size_t,
+                                       c_void_p]),
     "leankv_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "leankv_decode_begin": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "leankv_rope_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

@@ -43,6 +43,7 @@ namespace leankv {
 namespace {
 
 constexpr int kDim = LEANKV_TQ_DIM;
+constexpr int kPage = LEANKV_TQ_PAGE_TOKENS;
 constexpr int kAttnWarps = 4;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kStages = 4;
@@ -66,6 +67,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 // status bits written to the workspace status word
 constexpr int kStatusWaitTimeout = 1;
 constexpr int kStatusBadPage = 2;
+constexpr int kAttnRowsFolded = 1 << 16;     // internal launch flag (see row_of in the kernel)
 
 struct AttnParams {
     const float* qprime;      // [B][Hq][128] rotated query Pi_k q
@@ -167,22 +169,26 @@ __device__ __forceinline__ Unit load_unit(const uint32_t* words, int ui) {
 }
 
 // ---- query rotation --------------------------------------------------------
-// q_rot[v][j] = sum_k Pi_k[j][k] q[v][k] (ascending k). One CTA rotates the kGroup query heads of a
-// (sequence, kv head) pair, so each row of Pi_k is fetched once per four heads.
+// q_rot[v][j] = sum_k Pi_k[j][k] q[v][k] (ascending k). One CTA rotates kHeads consecutive query heads
+// (the kGroup heads of one (sequence, kv head) pair; 16 heads when there are many rows, as in a prefill
+// chunk), so each row of Pi_k is fetched once per kHeads heads.
+template <int kHeads>
 __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const float* Pi_k, float* qprime) {
-    __shared__ float s_q[kGroup][kDim];
+    __shared__ float s_q[kHeads][kDim];
     pdl_begin();
-    const int v0 = blockIdx.x * kGroup, j = threadIdx.x;
+    const int v0 = blockIdx.x * kHeads, j = threadIdx.x;
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) s_q[h][j] = __half2float(q[(size_t)(v0 + h) * kDim + j]);
+    for (int h = 0; h < kHeads; ++h) s_q[h][j] = __half2float(q[(size_t)(v0 + h) * kDim + j]);
     __syncthreads();
     const float4* row = reinterpret_cast<const float4*>(Pi_k + (size_t)j * kDim);
-    float acc[kGroup] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 16
+    float acc[kHeads];
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) acc[h] = 0.f;
+#pragma unroll (kHeads > kGroup ? 8 : 16)
     for (int k4 = 0; k4 < kDim / 4; ++k4) {
         const float4 pv = __ldg(row + k4);
 #pragma unroll
-        for (int h = 0; h < kGroup; ++h) {
+        for (int h = 0; h < kHeads; ++h) {
             acc[h] = fmaf(pv.x, s_q[h][4 * k4 + 0], acc[h]);
             acc[h] = fmaf(pv.y, s_q[h][4 * k4 + 1], acc[h]);
             acc[h] = fmaf(pv.z, s_q[h][4 * k4 + 2], acc[h]);
@@ -190,7 +196,7 @@ __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const flo
         }
     }
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) qprime[(size_t)(v0 + h) * kDim + j] = acc[h];
+    for (int h = 0; h < kHeads; ++h) qprime[(size_t)(v0 + h) * kDim + j] = acc[h];
 }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -199,7 +205,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 // ---- main kernel -----------------------------------------------------------
 #include "tq_attn_kernel.cuh"
-#include "tq_attn_kernel_split.cuh"
 
 // ---- host side ---------------------------------------------------------------
 struct AttnPlan {
@@ -207,23 +212,13 @@ struct AttnPlan {
     size_t off_counters, off_qprime, off_partials, total;
 };
 
-// LEANKV_ATTN_SPLIT=1 selects the kernel with separate score and value warps per page stream.
-bool attn_split() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = std::getenv("LEANKV_ATTN_SPLIT");
-        v = (e != nullptr && e[0] == '1') ? 1 : 0;
-    }
-    return v == 1;
-}
-
 AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     AttnPlan pl;
     if (max_pages < 1) max_pages = 1;
     const long long pairs = (long long)B * Hkv;
     // One wave of resident CTAs; inputs too short to give every CTA kMinPagesPerCta pages get fewer
     // (the kernel applies the same rule to the page count it finds on the device).
-    const long long slots = (long long)sm_count() * (attn_split() ? 3 : attn_occupancy());
+    const long long slots = (long long)sm_count() * attn_occupancy();
     long long want = pairs * ((max_pages + kMinPagesPerCta - 1) / kMinPagesPerCta);
     if (want < 1) want = 1;
     pl.n_ctas = (int)(want < slots ? want : slots);
@@ -337,7 +332,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
         (q && !aligned16(Pi_k)) || !aligned16(Pi_v) || !aligned16(workspace))
         return LEANKV_EALIGN;
     if (B > 65535 || n_kv_heads > 65535) return LEANKV_ELIMIT;
-    if ((flags & ~LEANKV_ATTN_EARLY_FETCH) != 0) return LEANKV_EINVAL;
+    if ((flags & ~(LEANKV_ATTN_EARLY_FETCH | kAttnRowsFolded)) != 0) return LEANKV_EINVAL;
     const AttnPlan pl = make_plan(B, n_q_heads, n_kv_heads, max_pages_per_seq);
     if (workspace_bytes < pl.total) return LEANKV_EWORKSPACE;
     const Lut& lut = get_lut(centroids);
@@ -347,8 +342,13 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     const float* qprime = q_rot;
     if (q != nullptr) {
         float* dst = reinterpret_cast<float*>(ws + pl.off_qprime);
-        LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel, dim3(B * n_kv_heads), dim3(128), 0, st,
-                                      static_cast<const __half*>(q), Pi_k, dst));
+        const int n_pairs = B * n_kv_heads;
+        if (n_pairs >= 1024 && n_pairs % 4 == 0)
+            LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel<4 * kGroup>, dim3(n_pairs / 4), dim3(128), 0, st,
+                                          static_cast<const __half*>(q), Pi_k, dst));
+        else
+            LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel<kGroup>, dim3(n_pairs), dim3(128), 0, st,
+                                          static_cast<const __half*>(q), Pi_k, dst));
         qprime = dst;
     }
 
@@ -372,9 +372,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
-    if (attn_split())
-        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_split_kernel, dim3(pl.n_ctas), dim3(kSplitThreads), 0, st, p));
-    else if (attn_occupancy() == 4)
+    if (attn_occupancy() == 4)
         LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     else
         LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
@@ -400,10 +398,93 @@ extern "C" int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int 
                                              const float* Pi_v, const float* centroids, float scale,
                                              void* workspace, size_t workspace_bytes, int flags,
                                              void* stream) {
-    if (!q_rot) return LEANKV_EINVAL;
+    if (!q_rot || (flags & ~LEANKV_ATTN_EARLY_FETCH) != 0) return LEANKV_EINVAL;
     return attn_launch(nullptr, q_rot, out, B, n_q_heads, n_kv_heads, pool, n_pages, kv_indptr,
                        kv_page_indices, kv_last_page_len, max_pages_per_seq, nullptr, Pi_v, centroids, scale,
                        workspace, workspace_bytes, flags, stream);
+}
+
+// ---- causal attention of a chunk of prompt tokens over the packed pages ----------------------
+// Token t of the chunk (absolute position start_pos + t) is one row of a decode batch whose page list
+// is the first (start_pos + t) / 16 + 1 pages of the sequence and whose last page holds
+// (start_pos + t) % 16 + 1 tokens: the causal mask is the page table. The rows share pages, which
+// come from L2 after the first reader.
+struct PrefillPlan {
+    size_t attn_bytes, off_indptr, off_last, off_indices, total;
+    int max_pages;
+};
+
+static long long prefill_rows_pages(long long first_pos, long long n) {
+    // sum over pos in [first_pos, first_pos + n) of pos / 16 + 1
+    auto upto = [](long long m) {             // sum over pos in [0, m) of pos / 16 + 1
+        const long long full = m / kPage, rest = m % kPage;
+        return (long long)kPage * full * (full + 1) / 2 + rest * (full + 1);
+    };
+    return upto(first_pos + n) - upto(first_pos);
+}
+
+static PrefillPlan make_prefill_plan(int T, int start_pos, int Hq, int Hkv) {
+    PrefillPlan pp;
+    pp.max_pages = (start_pos + T + kPage - 1) / kPage;
+    pp.attn_bytes = make_plan(T, Hq, Hkv, pp.max_pages).total;
+    pp.off_indptr = round_up(pp.attn_bytes, 256);
+    pp.off_last = pp.off_indptr + round_up(sizeof(int32_t) * ((size_t)T + 1), 256);
+    pp.off_indices = pp.off_last + round_up(sizeof(int32_t) * (size_t)T, 256);
+    pp.total = pp.off_indices + round_up(sizeof(int32_t) * (size_t)prefill_rows_pages(start_pos, T), 256);
+    return pp;
+}
+
+__global__ void __launch_bounds__(128) tq_prefill_tables_kernel(const int32_t* __restrict__ seq_pages, int T,
+                                                                 int start_pos, int32_t* __restrict__ indptr,
+                                                                 int32_t* __restrict__ last_len,
+                                                                 int32_t* __restrict__ indices) {
+    pdl_begin();
+    // Table row b holds token b / 2 (b even) or T - 1 - b / 2 (b odd): short and long rows alternate.
+    const int b = blockIdx.x, i = b >> 1;
+    auto upto = [](long long m) {             // sum over pos in [0, m) of pos / 16 + 1
+        const long long full = m / kPage, rest = m % kPage;
+        return (long long)kPage * full * (full + 1) / 2 + rest * (full + 1);
+    };
+    // rows before 2i: tokens 0 .. i-1 and T-i .. T-1
+    long long first = (upto(start_pos + i) - upto(start_pos)) + (upto((long long)start_pos + T) - upto((long long)start_pos + T - i));
+    if (b & 1) first += (start_pos + i) / kPage + 1;
+    const int pos = start_pos + ((b & 1) ? T - 1 - i : i);
+    const int n = pos / kPage + 1;
+    if (threadIdx.x == 0) {
+        indptr[b] = (int)first;
+        last_len[b] = pos % kPage + 1;
+        if (b == T - 1) indptr[T] = (int)first + n;
+    }
+    for (int k = threadIdx.x; k < n; k += blockDim.x) indices[first + k] = seq_pages[k];
+}
+
+extern "C" size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, int n_q_heads,
+                                                         int n_kv_heads) {
+    if (T <= 0 || start_pos < 0 || n_q_heads <= 0 || n_kv_heads <= 0) return 0;
+    return make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads).total;
+}
+
+extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads,
+                                      int n_kv_heads, const void* pool, int n_pages,
+                                      const int32_t* seq_pages, const float* Pi_k, const float* Pi_v,
+                                      const float* centroids, float scale, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+    if (T < 0 || start_pos < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_pages <= 0) return LEANKV_EINVAL;
+    if (T == 0) return LEANKV_OK;
+    if (!q || !out || !pool || !seq_pages || !workspace) return LEANKV_EINVAL;
+    if (T > 65535 || (long long)start_pos + T > (1ll << 24)) return LEANKV_ELIMIT;
+    if (!aligned16(workspace)) return LEANKV_EALIGN;
+    const PrefillPlan pp = make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads);
+    if (workspace_bytes < pp.total) return LEANKV_EWORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    int32_t* indptr = reinterpret_cast<int32_t*>(ws + pp.off_indptr);
+    int32_t* last_len = reinterpret_cast<int32_t*>(ws + pp.off_last);
+    int32_t* indices = reinterpret_cast<int32_t*>(ws + pp.off_indices);
+    LEANKV_CUDA_TRY(launch_kernel(tq_prefill_tables_kernel, dim3(T), dim3(128), 0,
+                                  static_cast<cudaStream_t>(stream), seq_pages, T, start_pos, indptr, last_len,
+                                  indices));
+    return attn_launch(q, nullptr, out, T, n_q_heads, n_kv_heads, pool, n_pages, indptr, indices, last_len,
+                       pp.max_pages, Pi_k, Pi_v, centroids, scale, workspace, pp.attn_bytes, kAttnRowsFolded, stream);
 }
 
 extern "C" int leankv_tq_decode_attn_status(const void* workspace, int* status) {

@@ -86,10 +86,16 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     const int ip0 = ip(0);
     const long long F = (long long)H * (ip(p.B) - ip0);
     // sequences without pages produce zeros; CTAs share them out
+    // Rows of q / out that belong to table row b. A prefill chunk lists its tokens folded (first, last,
+    // second, last but one, ...) so that every stretch of the flat page list holds as many short rows as
+    // long ones; everything else uses the identity.
+    auto row_of = [&](int b) -> int {
+        return (p.flags & kAttnRowsFolded) ? ((b & 1) ? p.B - 1 - (b >> 1) : (b >> 1)) : b;
+    };
     for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
         if (ip(b + 1) - ip(b) <= 0) {
             if (!waited) { pdl_begin(); waited = true; }
-            __half* o = p.out + (size_t)b * Hq * kDim;
+            __half* o = p.out + (size_t)row_of(b) * Hq * kDim;
             for (int i = tid; i < Hq * kDim; i += kAttnThreads) o[i] = __float2half_rn(0.f);
         }
     }
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         float kscale;            // score per integer unit of (256 * HH + MID), before the key norm
         {
             const int head = g & 3;
-            const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
+            const float* qp = p.qprime + ((size_t)row_of(b) * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
             float4 v[8];
             float amax = 0.f;
 #pragma unroll
@@ -540,7 +546,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             }
             __syncthreads();
             if (warp == 0) {
-                __half* out_base = p.out + ((size_t)b * Hq + (size_t)kvh * kGroup) * kDim;
+                __half* out_base = p.out + ((size_t)row_of(b) * Hq + (size_t)kvh * kGroup) * kDim;
 #pragma unroll
                 for (int h = 0; h < kGroup; ++h) {
                     float4 v = make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);

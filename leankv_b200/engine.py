@@ -109,6 +109,7 @@ class DecodeEngine:
         self.Pi_v_t = [m.t().contiguous() for m in self.Pi_v]
         cents, bounds = get_codebook_tensors(128, 3, "cpu")
         self.centroids_host = cents.float().contiguous()
+        self._prefill_ws = None
         self.centroids = self.centroids_host.to(dev)
         self.bounds = bounds[1:-1].float().contiguous().to(dev)
 
@@ -493,24 +494,48 @@ class DecodeEngine:
             with torch.cuda.device(self.dev):
                 self._step_launches()
 
-    # ── prefill (dense) ──────────────────────────────────────────────────
+    # ── prefill ──────────────────────────────────────────────────────────
+
+    def _check_prefill_status(self) -> None:
+        st = ctypes.c_int(0)
+        _native.check(self.lib.leankv_tq_decode_attn_status(self._prefill_ws.data_ptr(), ctypes.byref(st)),
+                      "attn_status")
+        if st.value != 0:
+            raise RuntimeError(f"prefill attention reported status {st.value} "
+                               "(1 = a bounded wait ran out, 2 = page id outside the pool)")
 
     def _dense_forward(self, ids: torch.Tensor, write_cache: bool, collect: Optional[dict] = None,
-                       page_indices: Optional[torch.Tensor] = None):
-        """Prompt pass with library GEMMs. Returns the final hidden state of the last token.
-        ``page_indices``: the pages of the sequence being filled (default: the engine's single sequence)."""
+                       page_indices: Optional[torch.Tensor] = None, start_pos: int = 0,
+                       attention: str = "dense"):
+        """Pass over ``ids`` (a prompt, or the chunk of it that starts at ``start_pos``) with library
+        GEMMs for the projections. Returns the final hidden state of the last token.
+        ``page_indices``: the pages of the sequence being filled (default: the engine's single sequence).
+        ``attention``: "packed" = causal attention straight on the packed pages
+        (``leankv_tq_prefill_attn``; needs ``write_cache``), "dense" = de-quantize the whole sequence to
+        fp16 and call the library's attention (only for a chunk that starts at 0)."""
         from .turboquant.quantizer import MSEQuantized, TurboQuantMSE  # noqa: F401
 
         cfg, T = self.cfg, ids.numel()
         pages = self.page_indices if page_indices is None else page_indices
-        pos = torch.arange(T, device=self.dev).float()
+        if attention not in ("dense", "packed"):
+            raise ValueError("attention must be 'dense' or 'packed'")
+        if attention == "packed" and not write_cache:
+            raise ValueError("packed attention reads the pool: it needs write_cache")
+        if attention == "dense" and start_pos != 0:
+            raise ValueError("the dense route handles whole prompts only")
+        if attention == "packed":
+            need = self.lib.leankv_tq_prefill_attn_workspace_bytes(T, start_pos, self.nq, self.nkv)
+            if self._prefill_ws is None or self._prefill_ws.numel() < need:
+                self._prefill_ws = torch.zeros(need, dtype=torch.uint8, device=self.dev)
+            attn_out = torch.empty(T, self.nq, 128, dtype=torch.float16, device=self.dev)
+        pos = torch.arange(start_pos, start_pos + T, device=self.dev).float()
         ang = torch.outer(pos, self.inv_freq)
         emb = torch.cat((ang, ang), dim=-1)
         cos, sin = emb.cos().half().unsqueeze(1), emb.sin().half().unsqueeze(1)
         h = self.w["embed"][ids]
-        n_pages = (T + PAGE - 1) // PAGE
+        n_pages = (start_pos + T + PAGE - 1) // PAGE
         indptr = torch.tensor([0, n_pages], dtype=torch.int32, device=self.dev)
-        start = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        start = torch.full((1,), start_pos, dtype=torch.int32, device=self.dev)
 
         def note(l, name, t):
             if collect is not None:
@@ -533,12 +558,25 @@ class DecodeEngine:
                                                     self.max_pages, indptr.data_ptr(),
                                                     pages.data_ptr(), start.data_ptr(), self._st())
                 _native.check(rc, "pool_append")
-                kh, vh = self._dense_kv(l, T, pages)
+                if attention == "dense":
+                    kh, vh = self._dense_kv(l, T, pages)
             else:
                 kh, vh = self._roundtrip(kh, l, 0), self._roundtrip(vh, l, 1)
-            a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), kh, vh, is_causal=True,
-                                               enable_gqa=True)
-            a = a.squeeze(0).transpose(0, 1).reshape(T, self.nq * 128)
+            if attention == "packed":
+                qc = q.contiguous()
+                rc = self.lib.leankv_tq_prefill_attn(qc.data_ptr(), attn_out.data_ptr(), T, start_pos,
+                                                     self.nq, self.nkv, self.pools[l].data_ptr(),
+                                                     self.max_pages, pages.data_ptr(),
+                                                     self.Pi_k[l].data_ptr(), self.Pi_v[l].data_ptr(),
+                                                     self.centroids_host.data_ptr(), 1.0 / math.sqrt(128.0),
+                                                     self._prefill_ws.data_ptr(), self._prefill_ws.numel(),
+                                                     self._st())
+                _native.check(rc, "prefill_attn")
+                a = attn_out.reshape(T, self.nq * 128)
+            else:
+                a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), kh, vh, is_causal=True,
+                                                   enable_gqa=True)
+                a = a.squeeze(0).transpose(0, 1).reshape(T, self.nq * 128)
             note(l, "o_proj", a)
             o = a @ lw["wo_t"]
             self._allreduce(o)
@@ -612,16 +650,31 @@ class DecodeEngine:
         return thresholds
 
     @torch.no_grad()
-    def prefill(self, prompt_ids) -> int:
-        """Process the prompt, fill the pool, and leave the first generated token ready for ``step``."""
+    def prefill(self, prompt_ids, chunk: Optional[int] = None, attention: str = "packed") -> int:
+        """Process the prompt, fill the pool, and leave the first generated token ready for ``step``.
+        ``chunk``: tokens per pass (default: the whole prompt in one); every chunk is quantized into the
+        pool first and then attends to the packed pages of everything up to itself, so no fp16 K/V
+        of more than one chunk ever exists. ``attention="dense"`` (whole prompt only) de-quantizes the
+        sequence and uses the library's attention instead, as the reference does
+        (leankv/turboquant/cache.py:136-142)."""
         ids = torch.as_tensor(prompt_ids, device=self.dev).reshape(-1)
         T = ids.numel()
         if T < 1 or T >= self.max_seq_len:
             raise ValueError("prompt length must be in [1, max_seq_len)")
+        if chunk is None:
+            chunk = T
+        if chunk < 1:
+            raise ValueError("chunk must be positive")
+        if attention == "dense" and chunk < T:
+            raise ValueError("the dense route handles whole prompts only")
         with torch.cuda.device(self.dev):
             for p in self.pools:
                 p.zero_()
-            x = self._dense_forward(ids, write_cache=True)
+            for s0 in range(0, T, chunk):
+                x = self._dense_forward(ids[s0:s0 + chunk], write_cache=True, start_pos=s0,
+                                        attention=attention)
+            if attention == "packed":
+                self._check_prefill_status()
             logits = x @ self.w["lm_head_t"]
             tok = torch.argmax(logits.float()).reshape(1)
             self.token.copy_(tok)

@@ -1,5 +1,6 @@
 """Helpers shared by the GPU tests: raw C-ABI calls for the paged TurboQuant pool."""
 
+import ctypes
 import math
 
 import numpy as np
@@ -51,6 +52,26 @@ class RawPool:
         _native.check(rc, "leankv_tq_pool_unpack")
         torch.cuda.synchronize()
         return idx.cpu().numpy(), norms.cpu().numpy()
+
+    def prefill_attention(self, q, seq_pages, start_pos):
+        """q [T, Hq, 128] fp16: the chunk of prompt tokens at positions start_pos.. -> out [T, Hq, 128]."""
+        T, Hq, _ = q.shape
+        need = self.lib.leankv_tq_prefill_attn_workspace_bytes(T, start_pos, Hq, self.H)
+        ws = torch.zeros(need, dtype=torch.uint8, device=self.dev)
+        q = q.contiguous()
+        out = torch.empty_like(q)
+        pg = self.i32(seq_pages)
+        rc = self.lib.leankv_tq_prefill_attn(q.data_ptr(), out.data_ptr(), T, start_pos, Hq, self.H,
+                                             self.pool.data_ptr(), self.n_pages, pg.data_ptr(),
+                                             self.Pi_k.data_ptr(), self.Pi_v.data_ptr(),
+                                             self.centroids_host.data_ptr(), 1.0 / math.sqrt(128.0),
+                                             ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "leankv_tq_prefill_attn")
+        torch.cuda.synchronize()
+        st = ctypes.c_int(0)
+        _native.check(self.lib.leankv_tq_decode_attn_status(ws.data_ptr(), ctypes.byref(st)), "status")
+        assert st.value == 0
+        return out
 
     def attention(self, q, indptr, indices, last_len, max_pages=None):
         """q [B, Hq, 128] fp16 -> out [B, Hq, 128] fp16."""

