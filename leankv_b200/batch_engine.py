@@ -61,6 +61,7 @@ class BatchDecodeEngine(DecodeEngine):
         self.Pi_v_t = [m.t().contiguous() for m in self.Pi_v]
         cents, bounds = get_codebook_tensors(128, 3, "cpu")
         self.centroids_host = cents.float().contiguous()
+        self._prefill_ws = None
         self.centroids = self.centroids_host.to(dev)
         self.bounds = bounds[1:-1].float().contiguous().to(dev)
 
@@ -170,21 +171,33 @@ class BatchDecodeEngine(DecodeEngine):
     # ── prefill / generate ───────────────────────────────────────────────
 
     @torch.no_grad()
-    def prefill(self, prompts) -> torch.Tensor:
-        """``prompts``: int64 [B][T] (equal lengths). Fills every sequence's pages with a dense prompt
-        pass (one sequence at a time) and leaves the first generated token of each ready for ``step``."""
+    def prefill(self, prompts, attention: str = "packed", chunk: Optional[int] = None) -> torch.Tensor:
+        """``prompts``: int64 [B][T] (equal lengths). Fills every sequence's pages with a prompt pass
+        (library GEMMs, one sequence at a time, ``chunk`` tokens per pass) and leaves the first generated
+        token of each ready for ``step``. ``attention``: "packed" = causal attention on the packed pages,
+        "dense" = de-quantize + library attention (whole prompt per pass only); see
+        ``DecodeEngine.prefill``."""
         ids = torch.as_tensor(prompts, device=self.dev)
         if ids.dim() != 2 or ids.shape[0] != self.B:
             raise ValueError("prompts must be [batch][T]")
         T = ids.shape[1]
         if T < 1 or T >= self.max_seq_len:
             raise ValueError("prompt length must be in [1, max_seq_len)")
+        if chunk is None:
+            chunk = T
+        if chunk < 1 or (attention == "dense" and chunk < T):
+            raise ValueError("chunk must be positive; the dense route handles whole prompts only")
         with torch.cuda.device(self.dev):
             for p in self.pools:
                 p.zero_()
             last = []
             for b in range(self.B):
-                last.append(self._dense_forward(ids[b], write_cache=True, page_indices=self.block_table[b]))
+                for s0 in range(0, T, chunk):
+                    x = self._dense_forward(ids[b, s0:s0 + chunk], write_cache=True,
+                                            page_indices=self.block_table[b], start_pos=s0, attention=attention)
+                last.append(x)
+            if attention == "packed":
+                self._check_prefill_status()
             logits = torch.stack(last) @ self.w["lm_head_t"]
             tok = torch.argmax(logits.float(), dim=-1)
             self.tokens.copy_(tok)
