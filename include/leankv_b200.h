@@ -201,7 +201,11 @@ int leankv_tq_pool_unpack(const void* pool, int n_pages, int n_kv_heads,
  * the grid and the workspace (host value, >= the longest sequence's page count). centroids is read on the
  * host (the codebook is a compile-time-like constant of the cache): it is turned into
  * register look-up tables that travel as kernel arguments. The first 4 bytes of the
- * workspace are a status word (see leankv_tq_decode_attn_status). */
+ * workspace are a status word (see leankv_tq_decode_attn_status). The workspace must be zeroed
+ * before its first use; calls of one shape (B, heads, max_pages_per_seq) may then share it for
+ * ever (the arrival counters reset themselves). Its layout depends on the shape, so a workspace
+ * that has served another shape must be zeroed again (all but the status word) before it serves
+ * this one. */
 size_t leankv_tq_decode_attn_workspace_bytes(int B, int n_q_heads, int n_kv_heads,
                                              int max_pages_per_seq);
 int leankv_tq_decode_attn(const void* q, void* out, int B, int n_q_heads, int n_kv_heads,
@@ -246,9 +250,10 @@ int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
  * (start_pos + T + 15) / 16 of them. Row t of the chunk is computed by the decode kernel as one row of
  * a batch whose page list ends at position start_pos + t (the causal mask is the page table), so it
  * agrees with a decode step at that position up to the rounding of the partial merge (the split of
- * a row's pages over CTAs depends on the batch). The workspace rules of leankv_tq_decode_attn apply
- * (zeroed once, first word = status); two launches (page-table rows, query rotation) precede the
- * attention kernel. */
+ * a row's pages over CTAs depends on the batch). The workspace's first word is the status word and
+ * must be zero before the first use; the rest needs no preparation and one workspace may serve chunks
+ * of any length (the call clears its arrival counters itself). A memset node and two launches
+ * (page-table rows, query rotation) precede the attention kernel. */
 size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, int n_q_heads, int n_kv_heads);
 int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads, int n_kv_heads,
                            const void* pool, int n_pages, const int32_t* seq_pages, const float* Pi_k,

@@ -480,6 +480,13 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     int32_t* indptr = reinterpret_cast<int32_t*>(ws + pp.off_indptr);
     int32_t* last_len = reinterpret_cast<int32_t*>(ws + pp.off_last);
     int32_t* indices = reinterpret_cast<int32_t*>(ws + pp.off_indices);
+    // Chunks of different lengths lay the workspace out differently, so what one call left in its partial-sum
+    // or table area may lie where this call has its arrival counters: clear them (the status word stays).
+    {
+        const AttnPlan pl = make_plan(T, n_q_heads, n_kv_heads, pp.max_pages);
+        LEANKV_CUDA_TRY(cudaMemsetAsync(ws + pl.off_counters, 0, pl.off_qprime - pl.off_counters,
+                                        static_cast<cudaStream_t>(stream)));
+    }
     LEANKV_CUDA_TRY(launch_kernel(tq_prefill_tables_kernel, dim3(T), dim3(128), 0,
                                   static_cast<cudaStream_t>(stream), seq_pages, T, start_pos, indptr, last_len,
                                   indices));

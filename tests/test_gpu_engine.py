@@ -319,6 +319,8 @@ def test_prefill_in_chunks_over_packed_pages_matches_whole_prompt_and_dense_atte
     whole = engine.prefill_logits.float().clone()
     engine.prefill(prompt, chunk=64)
     chunked = engine.prefill_logits.float().clone()
+    engine.prefill(prompt)          # the workspace has served chunks of another length in between
+    assert torch.equal(engine.prefill_logits.float(), whole)
     assert rel_l2(whole.cpu(), dense.cpu()) < 2e-2
     assert rel_l2(chunked.cpu(), whole.cpu()) < 2e-2
     # layer 0's keys and values do not depend on attention at all: identical pools
