@@ -591,6 +591,35 @@ class DecodeEngine:
             h = h + d
         return _rmsnorm(h[-1], self.w["final_norm"], cfg.rms_eps)
 
+    @torch.no_grad()
+    def dense_step_reference(self, token: int, pos: int) -> torch.Tensor:
+        """Logits of the decode step that fed ``token`` at position ``pos``, recomputed with library
+        GEMMs and library attention over the pool as that step left it (positions 0 .. pos, de-quantized
+        to fp16). It reads the very codes the step wrote, so the two differ by rounding only, never by a
+        code that fell on the other side of a decision boundary. Thresholds are not applied: meaningful
+        for a step taken with TEAL off. For parity checks."""
+        cfg = self.cfg
+        with torch.cuda.device(self.dev):
+            ang = float(pos) * self.inv_freq
+            emb = torch.cat((ang, ang), dim=-1)
+            cos, sin = emb.cos().half().reshape(1, 1, 128), emb.sin().half().reshape(1, 1, 128)
+            h = self.w["embed"][token].reshape(1, -1)
+            for l, lw in enumerate(self.w["layers"]):
+                x = _rmsnorm(h, lw["ln1"], cfg.rms_eps)
+                q = _rope((x @ lw["wqkv_t"])[:, :self.nq * 128].reshape(1, self.nq, 128), cos, sin)
+                kh, vh = self._dense_kv(l, pos + 1)
+                a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), kh, vh, enable_gqa=True)
+                o = a.squeeze(0).transpose(0, 1).reshape(1, self.nq * 128) @ lw["wo_t"]
+                if self.tp_size > 1:
+                    torch.distributed.all_reduce(o, group=self.group)
+                h = h + o
+                x = _rmsnorm(h, lw["ln2"], cfg.rms_eps)
+                d = (F.silu(x @ lw["wgate_t"]) * (x @ lw["wup_t"])) @ lw["wdown_t"]
+                if self.tp_size > 1:
+                    torch.distributed.all_reduce(d, group=self.group)
+                h = h + d
+            return (_rmsnorm(h[0], self.w["final_norm"], cfg.rms_eps) @ self.w["lm_head_t"]).float()
+
     def _dense_kv(self, l: int, T: int, page_indices: Optional[torch.Tensor] = None):
         """fp16 K_hat, V_hat [1, nkv, T, 128] of layer ``l`` de-quantized from the pool."""
         outs = []
