@@ -59,6 +59,7 @@ int attn_occupancy() {
     }
     return occ;
 }
+constexpr int kClusterCtas = 8;               // CTAs per (sequence, kv head) pair in the cluster variant
 constexpr int kMinPagesPerCta = 4;            // short inputs use fewer CTAs rather than sub-page shares
 constexpr float kFixedMax = 32512.0f;         // largest |value| of the 16-bit fixed-point operands (127 * 256)
 constexpr int kSpinLimit = 1 << 20;
@@ -199,10 +200,6 @@ __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const flo
     for (int h = 0; h < kHeads; ++h) qprime[(size_t)(v0 + h) * kDim + j] = acc[h];
 }
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
 // ---- main kernel -----------------------------------------------------------
 #include "tq_attn_kernel.cuh"
 
@@ -211,6 +208,16 @@ struct AttnPlan {
     int n_ctas;
     size_t off_counters, off_qprime, off_partials, total;
 };
+
+// LEANKV_ATTN_CLUSTER=0 keeps a single sequence on the general kernel (partials through the workspace).
+bool attn_cluster() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("LEANKV_ATTN_CLUSTER");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
 
 AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
     AttnPlan pl;
@@ -372,10 +379,19 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
+    // A single sequence (every pair has the same page count) with few enough pages per CTA: one cluster
+    // per pair, merged through distributed shared memory instead of the workspace.
+    if (attn_cluster() && B == 1 && (flags & kAttnRowsFolded) == 0 &&
+        max_pages_per_seq <= kClusterCtas * kAttnWarps * 4 &&
+        n_kv_heads * kClusterCtas <= sm_count() * attn_occupancy()) {
+        LEANKV_CUDA_TRY(launch_cluster_kernel_ex(true, kClusterCtas, tq_decode_attn_kernel<4, true>,
+                                                 dim3(n_kv_heads * kClusterCtas), dim3(kAttnThreads), 0, st, p));
+        return LEANKV_OK;
+    }
     if (attn_occupancy() == 4)
-        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4, false>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     else
-        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5, false>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     return LEANKV_OK;
 }
 

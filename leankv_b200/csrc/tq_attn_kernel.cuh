@@ -30,7 +30,9 @@ constexpr float kNoRef = -1.0e30f;
 // core as floats without a conversion instruction.
 constexpr float kBiasF = 12582912.0f;
 
-template <int kOcc>   // resident CTAs per SM the register allocation is held to
+// kCluster: the CTAs of a (sequence, kv head) pair form one thread-block cluster of kClusterCtas (see the
+// end of the kernel); used for a single sequence, whose pairs all have the same number of pages.
+template <int kOcc, bool kCluster>   // kOcc: resident CTAs per SM the register allocation is held to
 __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(const AttnParams p) {
     // per-warp ring of kStages x (K chunk + V chunk)
     __shared__ __align__(128) uint8_t s_ring[kAttnWarps][kStages][2][kChunkBytes];
@@ -84,22 +86,45 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     }
     auto ip = [&](int i) -> int { return small_b ? s_ip[i] : p.indptr[i]; };
     const int ip0 = ip(0);
-    const long long F = (long long)H * (ip(p.B) - ip0);
-    // sequences without pages produce zeros; CTAs share them out
     // Rows of q / out that belong to table row b. A prefill chunk lists its tokens folded (first, last,
     // second, last but one, ...) so that every stretch of the flat page list holds as many short rows as
     // long ones; everything else uses the identity.
     auto row_of = [&](int b) -> int {
         return (p.flags & kAttnRowsFolded) ? ((b & 1) ? p.B - 1 - (b >> 1) : (b >> 1)) : b;
     };
-    for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
-        if (ip(b + 1) - ip(b) <= 0) {
+    long long F = 0, C = 1, f_lo = 0, f_hi = 0;
+    bool fits32 = true;
+    int b = 0, seq_pg0 = 0, n_b = 0, kvh = 0, pg = 0;
+    // floor(c * F / C) and its inverse; 32-bit arithmetic when the products fit (the usual case)
+    auto share_start = [&](long long c) -> long long {
+        return fits32 ? (long long)((unsigned)c * (unsigned)F / (unsigned)C) : c * F / C;
+    };
+    auto cta_of = [&](long long f) -> int {        // the CTA whose share holds flat page f
+        return fits32 ? (int)(((unsigned)(f + 1) * (unsigned)C + (unsigned)F - 1u) / (unsigned)F) - 1
+                      : (int)(((f + 1) * C + F - 1) / F) - 1;
+    };
+    unsigned crank = 0;                   // this CTA's rank in its cluster
+    if constexpr (kCluster) {
+        // cluster = pair; rank r takes pages [r n / kClusterCtas, (r + 1) n / kClusterCtas) of the pair's n
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+        const int pair = blockIdx.x / kClusterCtas;
+        b = pair / H;
+        kvh = pair - b * H;
+        seq_pg0 = ip(b);
+        n_b = max(ip(b + 1) - seq_pg0, 0);
+        pg = (int)((unsigned)n_b * crank / kClusterCtas);
+        f_hi = (int)((unsigned)n_b * (crank + 1) / kClusterCtas) - pg;     // the loop below runs over [0, f_hi)
+    } else {
+    F = (long long)H * (ip(p.B) - ip0);
+    // sequences without pages produce zeros; CTAs share them out
+    for (int bz = blockIdx.x; bz < p.B; bz += gridDim.x) {
+        if (ip(bz + 1) - ip(bz) <= 0) {
             if (!waited) { pdl_begin(); waited = true; }
-            __half* o = p.out + (size_t)row_of(b) * Hq * kDim;
+            __half* o = p.out + (size_t)row_of(bz) * Hq * kDim;
             for (int i = tid; i < Hq * kDim; i += kAttnThreads) o[i] = __float2half_rn(0.f);
         }
     }
-    long long C = gridDim.x;
+    C = gridDim.x;
     {
         // no more CTAs than give each about kMinPagesPerCta pages; whole multiples of the pair count, so that
         // equal-length sequences are cut into equal pieces that end at pair boundaries
@@ -114,19 +139,11 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         if (!waited) pdl_begin();
         return;
     }
-    // floor(c * F / C) and its inverse; 32-bit arithmetic when the products fit (the usual case)
-    const bool fits32 = (F + 1) * C + F < (1ll << 32);
-    auto share_start = [&](long long c) -> long long {
-        return fits32 ? (long long)((unsigned)c * (unsigned)F / (unsigned)C) : c * F / C;
-    };
-    auto cta_of = [&](long long f) -> int {        // the CTA whose share holds flat page f
-        return fits32 ? (int)(((unsigned)(f + 1) * (unsigned)C + (unsigned)F - 1u) / (unsigned)F) - 1
-                      : (int)(((f + 1) * C + F - 1) / F) - 1;
-    };
-    const long long f_lo = share_start(blockIdx.x), f_hi = share_start((long long)blockIdx.x + 1);
+    fits32 = (F + 1) * C + F < (1ll << 32);
+    f_lo = share_start(blockIdx.x);
+    f_hi = share_start((long long)blockIdx.x + 1);
 
     // sequence that holds flat page f_lo: the last b with H * (indptr[b] - indptr[0]) <= f_lo
-    int b;
     {
         int lo = 0, hi = p.B;
         while (hi - lo > 1) {
@@ -139,13 +156,13 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         }
         b = lo;
     }
-    int seq_pg0 = ip(b);
-    int n_b = ip(b + 1) - seq_pg0;
-    int kvh, pg;
+    seq_pg0 = ip(b);
+    n_b = ip(b + 1) - seq_pg0;
     {
         const long long r = f_lo - (long long)H * (seq_pg0 - ip0);    // < H * n_b
         kvh = fits32 ? (int)((unsigned)r / (unsigned)n_b) : (int)(r / n_b);
         pg = (int)(r - (long long)kvh * n_b);
+    }
     }
 
     const size_t page_stride = (size_t)2 * H * kChunkBytes;       // K chunk of a page -> next page
@@ -154,11 +171,12 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     unsigned phase = 0;              // bit s: parity the next wait on ring slot s looks for
     unsigned inflight = 0;           // bit s: a copy into ring slot s has been issued and not yet waited for
     bool failed = false;             // a bounded wait gave up: the warp stops using its ring
+    bool have_partial = false;       // cluster mode: the loop below left this CTA's partial result in shared memory
 
     for (long long f = f_lo; f < f_hi;) {
         const int seg_len = (int)min((long long)(n_b - pg), f_hi - f);
         if (seg_len <= 0) break;         // cannot happen for a consistent page table; never loop on an inconsistent one
-        const bool whole = seg_len == n_b;
+        const bool whole = !kCluster && seg_len == n_b;
         // ---- this warp's pages of the segment ----
         const int w_lo = pg + (int)(((long long)seg_len * warp) / kAttnWarps);
         const int w_hi = pg + (int)(((long long)seg_len * (warp + 1)) / kAttnWarps);
@@ -424,6 +442,18 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         }
         __syncthreads();                       // s_res / s_m / s_l may be overwritten from here on
 
+        if constexpr (kCluster) {
+            // this CTA's partial result stays in its shared memory for the other CTAs of the cluster
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) s_res[0][h][tid] = o[h];
+            if (tid < kGroup) {
+                s_m[0][tid] = mh[tid];
+                s_l[0][tid] = lh[tid];
+            }
+            have_partial = true;
+            break;
+        }
+
         bool finish = whole;
         if (!whole) {
             // partial slot: 1 if this pair started in an earlier part of this CTA's share (it is then
@@ -579,5 +609,97 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 } while (n_b <= 0 && b + 1 < p.B);
             }
         }
+    }
+
+    if constexpr (kCluster) {
+        // ---- merge inside the cluster, through distributed shared memory ----
+        // Every CTA holds the partial result of its pages in s_res[0] / s_m[0] / s_l[0]. After a cluster
+        // barrier each CTA reads all kClusterCtas partials, merges them in rank order (every CTA gets the
+        // same bits) and produces kDim / kClusterCtas of the output columns: out[:, c] = sum_i o[i] Pi_v[i][c].
+        // No partial result goes through global memory and the rotation work is spread over the cluster;
+        // each thread's 16 elements of Pi_v are fetched before the barrier.
+        if (!waited) { pdl_begin(); waited = true; }           // a CTA without pages has not waited yet
+        if (!have_partial) {
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) s_res[0][h][tid] = 0.f;
+            if (tid < kGroup) {
+                s_m[0][tid] = kNoRef;
+                s_l[0][tid] = 0.f;
+            }
+        }
+        constexpr int kCols = kDim / kClusterCtas;             // 16 output columns per CTA
+        constexpr int kRowsPerPart = kDim / (kAttnThreads / kCols);   // 16 rows of Pi_v per thread
+        const int jcol = tid & (kCols - 1), ipart = tid / kCols;
+        float pv[kRowsPerPart];
+        {
+            const float* src = p.Pi_v + (size_t)(ipart * kRowsPerPart) * kDim + crank * kCols + jcol;
+#pragma unroll
+            for (int ii = 0; ii < kRowsPerPart; ++ii) pv[ii] = __ldg(src + (size_t)ii * kDim);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+        float* s_ml = &s_res[1][0][0];                         // [kClusterCtas][2 * kGroup]: m then l of every rank
+        float* s_o = &s_res[2][0][0];                          // [kGroup][kDim] merged and normalised
+        float* s_red = &s_res[3][0][0];                        // [kAttnWarps][kGroup][kCols]
+        auto remote = [&](const void* local, unsigned rank) -> uint32_t {
+            uint32_t r;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+            return r;
+        };
+        auto ld_remote = [&](uint32_t addr) -> float {
+            float v;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+            return v;
+        };
+        float ov[kClusterCtas][kGroup];
+#pragma unroll
+        for (int k = 0; k < kClusterCtas; ++k)
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) ov[k][h] = ld_remote(remote(&s_res[0][h][tid], k));
+        if (tid < kClusterCtas * 2 * kGroup) {
+            const int k = tid / (2 * kGroup), w = tid % (2 * kGroup);
+            s_ml[tid] = ld_remote(remote(w < kGroup ? &s_m[0][w] : &s_l[0][w - kGroup], k));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < kGroup; ++h) {
+            float m = s_ml[h];
+#pragma unroll
+            for (int k = 1; k < kClusterCtas; ++k) m = fmaxf(m, s_ml[k * 2 * kGroup + h]);
+            float o = 0.f, l = 0.f;
+#pragma unroll
+            for (int k = 0; k < kClusterCtas; ++k) {
+                const float fc = ex2_approx(s_ml[k * 2 * kGroup + h] - m);
+                o = fmaf(fc, ov[k][h], o);
+                l = fmaf(fc, s_ml[k * 2 * kGroup + kGroup + h], l);
+            }
+            s_o[h * kDim + tid] = l > 0.f ? o * (p.inv_alpha / l) : 0.f;
+        }
+        // this CTA has finished reading its neighbours' shared memory; nobody may leave before all have
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        __syncthreads();
+        float r[kGroup] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ii = 0; ii < kRowsPerPart; ++ii) {
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) r[h] = fmaf(s_o[h * kDim + ipart * kRowsPerPart + ii], pv[ii], r[h]);
+        }
+        // a warp holds two parts (lanes 0..15 and 16..31): add them, then the four warps through shared memory
+#pragma unroll
+        for (int h = 0; h < kGroup; ++h) r[h] += __shfl_xor_sync(0xffffffffu, r[h], kCols);
+        if (lane < kCols) {
+#pragma unroll
+            for (int h = 0; h < kGroup; ++h) s_red[(warp * kGroup + h) * kCols + lane] = r[h];
+        }
+        __syncthreads();
+        if (tid < kGroup * kCols) {
+            const int h = tid / kCols, c = tid % kCols;
+            float v = s_red[h * kCols + c];
+#pragma unroll
+            for (int w = 1; w < kAttnWarps; ++w) v += s_red[(w * kGroup + h) * kCols + c];
+            p.out[((size_t)row_of(b) * Hq + (size_t)kvh * kGroup + h) * kDim + crank * kCols + c] = __float2half_rn(v);
+        }
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
 }
