@@ -50,9 +50,10 @@ inline cudaError_t launch_kernel_ex(bool early_ok, void (*kernel)(KArgs...), dim
     cfg.numAttrs = (mode == 1 || (mode == 2 && early_ok)) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
-// The same for a grid of thread-block clusters of `cluster_x` CTAs (grid.x a multiple of it).
+// The same for a grid of thread-block clusters of `cluster` CTAs (every grid dimension a multiple of the
+// cluster's).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_cluster_kernel_ex(bool early_ok, int cluster_x, void (*kernel)(KArgs...), dim3 grid,
+inline cudaError_t launch_cluster_kernel_ex(bool early_ok, dim3 cluster, void (*kernel)(KArgs...), dim3 grid,
                                             dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -61,9 +62,9 @@ inline cudaError_t launch_cluster_kernel_ex(bool early_ok, int cluster_x, void (
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)cluster_x;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;

@@ -384,7 +384,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     if (attn_cluster() && B == 1 && (flags & kAttnRowsFolded) == 0 &&
         max_pages_per_seq <= kClusterCtas * kAttnWarps * 4 &&
         n_kv_heads * kClusterCtas <= sm_count() * attn_occupancy()) {
-        LEANKV_CUDA_TRY(launch_cluster_kernel_ex(true, kClusterCtas, tq_decode_attn_kernel<4, true>,
+        LEANKV_CUDA_TRY(launch_cluster_kernel_ex(true, dim3(kClusterCtas), tq_decode_attn_kernel<4, true>,
                                                  dim3(n_kv_heads * kClusterCtas), dim3(kAttnThreads), 0, st, p));
         return LEANKV_OK;
     }
