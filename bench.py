@@ -1077,6 +1077,10 @@ def run_ours(args):
     if world == 1 and not args.small:
         legs = kernel_legs(dev, peak_gbs)
         codes_for_checker = legs.pop("_codes_for_checker", None)
+        for leg, cap in (("tq_decode_attn_rotated_b16_t4096", "tq_decode_attn_config3"),
+                         ("tq_bulk_quantize_append_b16_t4096", "tq_pool_append_tc_config3")):
+            if leg in legs:
+                legs[leg]["traffic"], legs[leg]["traffic_source"] = _captured_traffic(cap)
         g = legs["sparse_gemv_4096x14336"]
         line["roofline"] = {"bound": "hbm", "kernel": "sparse_gemv_kernel<false> (config 1: 4096 x 14336, 40 % sparse)",
                             "achieved": g["gbs"], "peak": peak_gbs, "unit": "GB/s", "frac": g["frac"],
