@@ -860,7 +860,7 @@ def decode_parity(eng, prompt, cfg, dev, world, rank, group, history, tp_steps: 
     packed_prefill_logits = eng.prefill_logits.float().clone()
     eng.step()
     torch.cuda.synchronize()
-    got = eng.logits.float().clone()
+    got = eng.full_logits().float().clone()
     # the same step with library GEMMs and library attention over the pool as the step left it: both sides
     # read the same 3-bit codes, so only rounding differs
     want = eng.dense_step_reference(first, len(prompt))
@@ -910,7 +910,7 @@ def decode_parity(eng, prompt, cfg, dev, world, rank, group, history, tp_steps: 
                 single.token.fill_(tok)
                 single.step()
                 torch.cuda.synchronize()
-                errs.append(rel(eng.logits.float(), single.logits.float()))
+                errs.append(rel(eng.full_logits().float(), single.logits.float()))
             eng.check_status()
             single.check_status()
             worst = torch.tensor([max(errs)], dtype=torch.float64, device=dev)

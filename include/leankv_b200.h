@@ -334,6 +334,15 @@ int leankv_sparse_gemv_allreduce_f16(const void* Wt, const void* x, void* y, int
                                      void* workspace, size_t workspace_bytes,
                                      unsigned long long* active_elems,
                                      const leankv_xchg_t* xchg, int slot, void* stream);
+/* leankv_decode_end for an output head split over the vocabulary: logits_local is this rank's slice
+ * (vocab_local entries starting at global index vocab_offset; vocab_local % 8 == 0). The ranks exchange
+ * their {best value, index} through `slot` of the receive areas (2 words per rank) and all store the same
+ * token (largest value, lowest index on ties). Being the last exchange of a step, the call also adds 1 to
+ * *xchg->epoch, so a decode step that ends with it needs no leankv_xchg_advance. A bounded wait that runs out
+ * sets *xchg->status like the GEMV's. */
+int leankv_decode_end_sharded(const void* logits_local, int vocab_local, int vocab_offset, long long* token,
+                              long long* history, int history_cap, int32_t* state,
+                              const leankv_xchg_t* xchg, int slot, void* stream);
 /* Device memory that other processes on this node can map (cudaMalloc + CUDA IPC):
  * alloc returns the pointer and a 64-byte handle to hand to the peers; open maps a peer's
  * handle into this process (enables peer access); close / free undo them. */

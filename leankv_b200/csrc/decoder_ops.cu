@@ -175,6 +175,97 @@ __global__ void __launch_bounds__(1024) decode_end_kernel(const __half* logits, 
     }
 }
 
+// The same for an output head that is split over the vocabulary among tensor-parallel ranks: every
+// rank finds the best of its own slice, sends {value, index} (two 64-bit words, each tagged with the
+// step's epoch like the partial sums of the row-parallel GEMV) to every rank's receive area, waits
+// (bounded) for all ranks' words, and takes the largest value, lowest index on ties: every rank
+// arrives at the same token. As the last exchange of a step it also moves the epoch on.
+struct ShardedEndParams {
+    const __half* logits;      // this rank's slice [vocab_local]
+    int vocab_local, vocab_offset;
+    long long* token;
+    long long* history;
+    int history_cap;
+    int* pos;
+    int* step_ptr;
+    int world, rank, limit;
+    unsigned long long* recv[LEANKV_MAX_RANKS];   // slot base in every rank's area: [world][2] words
+    int* epoch;
+    int* status;
+};
+
+__global__ void __launch_bounds__(1024) decode_end_sharded_kernel(const ShardedEndParams p) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    pdl_begin();
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    const int nvec = p.vocab_local >> 3;      // vocab_local % 8 == 0 (checked on the host)
+    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p.logits) + vi);
+        const __half* hp = reinterpret_cast<const __half*>(&a);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float v = __half2float(hp[q]);
+            if (v > best) { best = v; best_i = vi * 8 + q; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (s_v[w] > best || (s_v[w] == best && s_i[w] < best_i)) { best = s_v[w]; best_i = s_i[w]; }
+    if (best_i != 0x7fffffff) best_i += p.vocab_offset;
+
+    const unsigned int ep = (unsigned int)*reinterpret_cast<volatile int*>(p.epoch);
+    const unsigned long long tag = (unsigned long long)ep << 32;
+    for (int i = 0; i < p.world; ++i) {
+        int r = p.rank + i;
+        r = r >= p.world ? r - p.world : r;
+        unsigned long long* dst = p.recv[r] + 2 * p.rank;
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(tag | __float_as_uint(best)) : "memory");
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 1), "l"(tag | (unsigned int)best_i) : "memory");
+    }
+    const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
+    bool ok = live;
+    float top = -INFINITY;
+    int top_i = 0x7fffffff;
+    const unsigned long long* src = p.recv[p.rank];
+    for (int r = 0; r < p.world && live; ++r) {
+        unsigned long long wv = 0, wi = 0;
+        int it = 0;
+        for (;;) {
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(wv) : "l"(src + 2 * r) : "memory");
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(wi) : "l"(src + 2 * r + 1) : "memory");
+            if (((unsigned int)(wv >> 32) == ep && (unsigned int)(wi >> 32) == ep) || it >= p.limit) break;
+            __nanosleep(20);
+            ++it;
+        }
+        if ((unsigned int)(wv >> 32) != ep || (unsigned int)(wi >> 32) != ep) {
+            ok = false;
+            continue;
+        }
+        const float v = __uint_as_float((unsigned int)wv);
+        const int idx = (int)(unsigned int)wi;
+        if (v > top || (v == top && idx < top_i)) { top = v; top_i = idx; }
+    }
+    if (!ok && live) atomicOr(p.status, 1);
+    if (top_i == 0x7fffffff) top_i = 0;      // all-NaN rows, or a dead exchange
+    *p.token = top_i;
+    const int step = *p.step_ptr;
+    if (step < p.history_cap) p.history[step] = top_i;
+    *p.step_ptr = step + 1;
+    *p.pos = *p.pos + 1;
+    *p.epoch = (int)(ep + 1u);
+}
+
 // Batched step prologue: embedding rows of B tokens, and the flat page table of this step built from
 // a per-sequence block table. Sequence b caches pos[b] tokens and appends one: it uses
 // pos[b] / 16 + 1 pages, the first entries of block_table[b][0..max_pps). One CTA per sequence; each
@@ -283,6 +374,40 @@ extern "C" int leankv_decode_end(const void* logits, int vocab, long long* token
     LEANKV_CUDA_TRY(launch_kernel(decode_end_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream),
                                   static_cast<const __half*>(logits), vocab, token, history, history_cap,
                                   state + kPos, state + kStep));
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_decode_end_sharded(const void* logits_local, int vocab_local, int vocab_offset,
+                                         long long* token, long long* history, int history_cap, int32_t* state,
+                                         const leankv_xchg_t* xchg, int slot, void* stream) {
+    if (!logits_local || !token || !history || !state || !xchg || vocab_local <= 0 || vocab_offset < 0 ||
+        history_cap < 0)
+        return LEANKV_EINVAL;
+    if (vocab_local % 8 != 0 || !aligned16(logits_local)) return LEANKV_EALIGN;
+    if (xchg->world < 1 || xchg->world > LEANKV_MAX_RANKS || xchg->rank < 0 || xchg->rank >= xchg->world ||
+        slot < 0 || slot >= xchg->n_slots || 2 * xchg->world > xchg->world * xchg->max_cols || !xchg->epoch ||
+        !xchg->status || xchg->max_wait_iters < 1)
+        return LEANKV_EINVAL;
+    ShardedEndParams p{};
+    p.logits = static_cast<const __half*>(logits_local);
+    p.vocab_local = vocab_local;
+    p.vocab_offset = vocab_offset;
+    p.token = token;
+    p.history = history;
+    p.history_cap = history_cap;
+    p.pos = state + kPos;
+    p.step_ptr = state + kStep;
+    p.world = xchg->world;
+    p.rank = xchg->rank;
+    p.limit = xchg->max_wait_iters;
+    for (int r = 0; r < xchg->world; ++r) {
+        if (!xchg->recv[r] || (reinterpret_cast<uintptr_t>(xchg->recv[r]) & 7u) != 0) return LEANKV_EINVAL;
+        p.recv[r] = static_cast<unsigned long long*>(xchg->recv[r]) + (size_t)slot * xchg->world * xchg->max_cols;
+    }
+    p.epoch = const_cast<int*>(xchg->epoch);
+    p.status = xchg->status;
+    LEANKV_CUDA_TRY(launch_kernel(decode_end_sharded_kernel, dim3(1), dim3(1024), 0,
+                                  static_cast<cudaStream_t>(stream), p));
     return LEANKV_OK;
 }
 

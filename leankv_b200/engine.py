@@ -151,7 +151,16 @@ class DecodeEngine:
         if tp_size > 1 and os.environ.get("LEANKV_TP_EXCHANGE", "peer") != "nccl":
             from .peer_exchange import PeerExchange
 
-            self.xchg = PeerExchange(dev, tp_rank, tp_size, group, n_slots=2 * L, max_cols=cfg.hidden_size)
+            self.xchg = PeerExchange(dev, tp_rank, tp_size, group, n_slots=2 * L + 1, max_cols=cfg.hidden_size)
+        # Output head split over the vocabulary (needs the peer exchange for the arg-max): the decode step
+        # streams 1 / tp_size of it and the ranks exchange {best value, index}. The full matrix stays for the
+        # prompt pass and the parity references.
+        self.lm_head_local = None
+        if self.xchg is not None and cfg.vocab_size % (8 * tp_size) == 0 and \
+                os.environ.get("LEANKV_TP_LM_HEAD", "sharded") != "replicated":
+            vl = cfg.vocab_size // tp_size
+            self.vocab_local, self.vocab_offset = vl, tp_rank * vl
+            self.lm_head_local = self.w["lm_head_t"][:, self.vocab_offset:self.vocab_offset + vl].contiguous()
         self.set_thresholds(thresholds)
         self.graph = None
         self.launches_per_step = 0
@@ -427,13 +436,23 @@ class DecodeEngine:
                                               cfg.hidden_size, cfg.vocab_size, sp, st()), "decode_begin")
         self.launches_per_step += 1
         fused_norm = self.fused_norm
-        if self.xchg is not None and fused_norm:
-            self.xchg.advance(st())
+        sharded_head = self.lm_head_local is not None and fused_norm
+        if self.xchg is not None and fused_norm and not sharded_head:
+            self.xchg.advance(st())        # with a sharded head the step's last kernel moves the epoch on
             self.launches_per_step += 1
         if not fused_norm:
             self._norm(None, self.w["layers"][0]["ln1"])
         for l in range(cfg.num_layers):
             self._layer_launches(l)
+        if sharded_head:
+            mine = self.logits[self.vocab_offset:self.vocab_offset + self.vocab_local]
+            self._gemv(self.lm_head_local, self.h, mine, -1.0, norm_w=self.w["final_norm"])
+            _native.check(lib.leankv_decode_end_sharded(mine.data_ptr(), self.vocab_local, self.vocab_offset,
+                                                        self.token.data_ptr(), self.history.data_ptr(),
+                                                        self.history_cap, sp, ctypes.byref(self.xchg.c),
+                                                        2 * cfg.num_layers, st()), "decode_end_sharded")
+            self.launches_per_step += 1
+            return
         if fused_norm:
             self._gemv(self.w["lm_head_t"], self.h, self.logits, -1.0, norm_w=self.w["final_norm"])
         else:
@@ -466,6 +485,17 @@ class DecodeEngine:
                 # the in-kernel exchange waits a bounded time for its peers: start the replays together
                 torch.cuda.synchronize()
                 torch.distributed.barrier(group=self.group)
+
+    def full_logits(self) -> torch.Tensor:
+        """Logits of the last decode step over the whole vocabulary (fp16 [vocab]). With the output head
+        split over tensor-parallel ranks ``self.logits`` holds only this rank's slice up to date: the
+        slices are gathered here (a collective: every rank must call it)."""
+        if self.lm_head_local is None:
+            return self.logits
+        mine = self.logits[self.vocab_offset:self.vocab_offset + self.vocab_local].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(self.tp_size)]
+        torch.distributed.all_gather(parts, mine, group=self.group)
+        return torch.cat(parts)
 
     def status_words(self) -> tuple[int, int]:
         """(exchange status, attention status) read from the device: non-zero once a bounded wait inside

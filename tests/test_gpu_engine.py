@@ -330,3 +330,37 @@ def test_prefill_in_chunks_over_packed_pages_matches_whole_prompt_and_dense_atte
     assert torch.equal(engine.pools[0], pool_dense)
     with pytest.raises(ValueError):
         engine.prefill(prompt, chunk=64, attention="dense")
+
+
+def test_sharded_argmax_with_a_single_rank_exchanging_with_itself():
+    """``leankv_decode_end_sharded`` on one GPU: the rank's slice is the whole vocabulary shifted by an
+    offset; the token is the arg-max (lowest index on ties), position / step / history advance and the
+    exchange's epoch moves on by one per call."""
+    import ctypes
+
+    from leankv_b200 import _native
+    from leankv_b200.peer_exchange import PeerExchange
+
+    dev = _dev()
+    lib = _native.lib()
+    ex = PeerExchange(dev, 0, 1, None, n_slots=3, max_cols=256)
+    gen = torch.Generator().manual_seed(4)
+    logits = torch.randn(4096, generator=gen).half().to(dev)
+    logits[1234] = 9.0
+    logits[3000] = 9.0                      # a tie: the lower index wins
+    token = torch.zeros(1, dtype=torch.int64, device=dev)
+    history = torch.zeros(16, dtype=torch.int64, device=dev)
+    state = torch.zeros(8, dtype=torch.int32, device=dev)
+    state[0] = 41
+    st = torch.cuda.current_stream().cuda_stream
+    for call in range(3):
+        rc = lib.leankv_decode_end_sharded(logits.data_ptr(), 4096, 32768, token.data_ptr(), history.data_ptr(), 16,
+                                           state.data_ptr(), ctypes.byref(ex.c), 2, st)
+        _native.check(rc, "decode_end_sharded")
+        torch.cuda.synchronize()
+        assert int(token.item()) == 32768 + 1234
+        assert int(ex.epoch.item()) == 2 + call
+        assert state[:2].tolist() == [42 + call, 1 + call]
+        assert int(history[call].item()) == 32768 + 1234
+    assert not ex.timed_out()
+    ex.close()
