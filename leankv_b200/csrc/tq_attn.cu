@@ -59,7 +59,7 @@ int attn_occupancy() {
     }
     return occ;
 }
-constexpr int kClusterCtas = 8;               // CTAs per (sequence, kv head) pair in the cluster variant
+constexpr int kClusterMaxPages = 1024;        // 16384 tokens with 8 CTAs per pair (half that with 4): measured crossover near 32768
 constexpr int kMinPagesPerCta = 4;            // short inputs use fewer CTAs rather than sub-page shares
 constexpr float kFixedMax = 32512.0f;         // largest |value| of the 16-bit fixed-point operands (127 * 256)
 constexpr int kSpinLimit = 1 << 20;
@@ -217,6 +217,17 @@ bool attn_cluster() {
         v = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
     return v == 1;
+}
+
+// Largest page capacity (max_pages_per_seq) for which a single sequence uses the cluster variant; beyond it the
+// general kernel's many CTAs win over the cluster's shorter tail. LEANKV_ATTN_CLUSTER_MAX_PAGES overrides.
+int attn_cluster_max_pages() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("LEANKV_ATTN_CLUSTER_MAX_PAGES");
+        v = (e != nullptr && std::atoi(e) > 0) ? std::atoi(e) : kClusterMaxPages;
+    }
+    return v;
 }
 
 AttnPlan make_plan(int B, int Hq, int Hkv, int max_pages) {
@@ -379,19 +390,27 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
     p.counters = reinterpret_cast<int*>(ws + pl.off_counters);
     p.status = reinterpret_cast<int*>(ws);
-    // A single sequence (every pair has the same page count) with few enough pages per CTA: one cluster
-    // per pair, merged through distributed shared memory instead of the workspace.
-    if (attn_cluster() && B == 1 && (flags & kAttnRowsFolded) == 0 &&
-        max_pages_per_seq <= kClusterCtas * kAttnWarps * 4 &&
-        n_kv_heads * kClusterCtas <= sm_count() * attn_occupancy()) {
-        LEANKV_CUDA_TRY(launch_cluster_kernel_ex(true, dim3(kClusterCtas), tq_decode_attn_kernel<4, true>,
-                                                 dim3(n_kv_heads * kClusterCtas), dim3(kAttnThreads), 0, st, p));
-        return LEANKV_OK;
+    // Few enough (sequence, kv head) pairs that a cluster of 8 or 4 CTAs per pair fits into one wave: the
+    // pair's pages are split over its cluster and merged through distributed shared memory instead of the
+    // workspace. (Every pair gets the same number of CTAs whatever its length; batches with many pairs, and
+    // the folded rows of a prompt chunk, take the general kernel, whose flat split balances ragged lengths.)
+    if (attn_cluster() && (flags & kAttnRowsFolded) == 0) {
+        const long long pairs = (long long)B * n_kv_heads, slots = (long long)sm_count() * 4;
+        const int cs = pairs * 8 <= slots ? 8 : (pairs * 4 <= slots ? 4 : 0);
+        if (cs != 0 && max_pages_per_seq <= attn_cluster_max_pages() * cs / 8) {
+            if (cs == 8)
+                LEANKV_CUDA_TRY(launch_cluster_kernel_ex(true, dim3(8), tq_decode_attn_kernel<4, 8>,
+                                                         dim3((unsigned)pairs * 8), dim3(kAttnThreads), 0, st, p));
+            else
+                LEANKV_CUDA_TRY(launch_cluster_kernel_ex(true, dim3(4), tq_decode_attn_kernel<4, 4>,
+                                                         dim3((unsigned)pairs * 4), dim3(kAttnThreads), 0, st, p));
+            return LEANKV_OK;
+        }
     }
     if (attn_occupancy() == 4)
-        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4, false>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<4, 0>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     else
-        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5, false>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
+        LEANKV_CUDA_TRY(launch_kernel_ex(true, tq_decode_attn_kernel<5, 0>, dim3(pl.n_ctas), dim3(kAttnThreads), 0, st, p));
     return LEANKV_OK;
 }
 

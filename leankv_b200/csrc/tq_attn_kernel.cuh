@@ -30,10 +30,11 @@ constexpr float kNoRef = -1.0e30f;
 // core as floats without a conversion instruction.
 constexpr float kBiasF = 12582912.0f;
 
-// kCluster: the CTAs of a (sequence, kv head) pair form one thread-block cluster of kClusterCtas (see the
-// end of the kernel); used for a single sequence, whose pairs all have the same number of pages.
-template <int kOcc, bool kCluster>   // kOcc: resident CTAs per SM the register allocation is held to
+// kClusterCtas > 0: the CTAs of a (sequence, kv head) pair form one thread-block cluster of that many CTAs
+// (see the end of the kernel); used when a cluster per pair fits into one wave. 0: the general kernel.
+template <int kOcc, int kClusterCtas>   // kOcc: resident CTAs per SM the register allocation is held to
 __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(const AttnParams p) {
+    constexpr bool kCluster = kClusterCtas > 0;
     // per-warp ring of kStages x (K chunk + V chunk)
     __shared__ __align__(128) uint8_t s_ring[kAttnWarps][kStages][2][kChunkBytes];
     __shared__ __align__(8) uint64_t s_bar[kAttnWarps][kStages];
@@ -627,8 +628,9 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
                 s_l[0][tid] = 0.f;
             }
         }
-        constexpr int kCols = kDim / kClusterCtas;             // 16 output columns per CTA
-        constexpr int kRowsPerPart = kDim / (kAttnThreads / kCols);   // 16 rows of Pi_v per thread
+        constexpr int kCols = kDim / kClusterCtas;             // output columns per CTA (16 for 8 CTAs, 32 for 4)
+        constexpr int kRowsPerPart = kDim / (kAttnThreads / kCols);   // rows of Pi_v per thread (16 / 32)
+        static_assert(kCols == 16 || kCols == 32, "cluster of 8 or 4 CTAs");
         const int jcol = tid & (kCols - 1), ipart = tid / kCols;
         float pv[kRowsPerPart];
         {
@@ -685,9 +687,12 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
 #pragma unroll
             for (int h = 0; h < kGroup; ++h) r[h] = fmaf(s_o[h * kDim + ipart * kRowsPerPart + ii], pv[ii], r[h]);
         }
-        // a warp holds two parts (lanes 0..15 and 16..31): add them, then the four warps through shared memory
+        // with 16 columns a warp holds two parts (lanes 0..15 and 16..31): add them; then the four warps
+        // through shared memory
+        if (kCols == 16) {
 #pragma unroll
-        for (int h = 0; h < kGroup; ++h) r[h] += __shfl_xor_sync(0xffffffffu, r[h], kCols);
+            for (int h = 0; h < kGroup; ++h) r[h] += __shfl_xor_sync(0xffffffffu, r[h], 16);
+        }
         if (lane < kCols) {
 #pragma unroll
             for (int h = 0; h < kGroup; ++h) s_red[(warp * kGroup + h) * kCols + lane] = r[h];
