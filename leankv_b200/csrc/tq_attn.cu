@@ -495,7 +495,9 @@ __global__ void __launch_bounds__(128) tq_prefill_tables_kernel(const int32_t* _
 
 extern "C" size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, int n_q_heads,
                                                          int n_kv_heads) {
-    if (T <= 0 || start_pos < 0 || n_q_heads <= 0 || n_kv_heads <= 0) return 0;
+    if (T <= 0 || T > 65535 || start_pos < 0 || (long long)start_pos + T > (1ll << 24) || n_q_heads <= 0 ||
+        n_kv_heads <= 0 || prefill_rows_pages(start_pos, T) > 0x7fffffffll)
+        return 0;
     return make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads).total;
 }
 
@@ -508,6 +510,7 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     if (T == 0) return LEANKV_OK;
     if (!q || !out || !pool || !seq_pages || !workspace) return LEANKV_EINVAL;
     if (T > 65535 || (long long)start_pos + T > (1ll << 24)) return LEANKV_ELIMIT;
+    if (prefill_rows_pages(start_pos, T) > 0x7fffffffll) return LEANKV_ELIMIT;     // page-table offsets are int32
     if (!aligned16(workspace)) return LEANKV_EALIGN;
     const PrefillPlan pp = make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads);
     if (workspace_bytes < pp.total) return LEANKV_EWORKSPACE;

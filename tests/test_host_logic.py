@@ -305,3 +305,37 @@ def test_argument_validation_of_the_decode_and_exchange_entry_points():
     assert call(x, 0) == -1                      # receive area not 8-byte aligned
     assert lib.leankv_ipc_alloc(0, None, None) == -1 and lib.leankv_ipc_open(None, None) == -1
     assert lib.leankv_ipc_close(None) == -1 and lib.leankv_ipc_free(None) == -1
+
+
+def test_argument_validation_of_the_prefill_attention_and_sharded_argmax_entry_points():
+    """``leankv_tq_prefill_attn`` and ``leankv_decode_end_sharded`` reject bad arguments before any launch."""
+    _no_device_for_made_up_pointers()
+    lib = _native.lib()
+    fake, odd = 0x10000, 0x10002
+    need = lib.leankv_tq_prefill_attn_workspace_bytes(512, 0, 32, 8)
+    assert need > lib.leankv_tq_decode_attn_workspace_bytes(512, 32, 8, 32)      # decode workspace + the page-table rows
+    assert lib.leankv_tq_prefill_attn_workspace_bytes(0, 0, 32, 8) == 0
+    assert lib.leankv_tq_prefill_attn_workspace_bytes(70000, 0, 32, 8) == 0      # more rows than one call takes
+    assert lib.leankv_tq_prefill_attn_workspace_bytes(65535, (1 << 24) - 65535, 32, 8) == 0   # int32 page-table offsets
+    call = lambda T=512, start=0, ws=fake, nbytes=need, q=fake: lib.leankv_tq_prefill_attn(
+        q, fake, T, start, 32, 8, fake, 64, fake, fake, fake, fake, 0.088, ws, nbytes, None)
+    assert call(T=-1) == -1
+    assert call(start=-5) == -1
+    assert call(T=0) == 0                          # nothing to do
+    assert call(q=None) == -1
+    assert call(T=70000) == -6
+    assert call(ws=odd) == -2
+    assert call(nbytes=need - 1) == -3
+
+    x = _native.Xchg()
+    x.world, x.rank, x.n_slots, x.max_cols, x.max_wait_iters = 2, 0, 4, 4096, 100
+    x.recv[0], x.recv[1] = fake, fake
+    x.epoch, x.status = fake, fake
+    end = lambda xc, slot=3, vl=4096, logits=fake: lib.leankv_decode_end_sharded(
+        logits, vl, 4096, fake, fake, 8, fake, ctypes.byref(xc), slot, None)
+    assert end(x, slot=4) == -1                    # slot outside the area
+    assert end(x, vl=4100) == -2                   # slice length not a multiple of 8
+    assert end(x, logits=odd) == -2
+    assert end(x, logits=None) == -1
+    x.recv[1] = None
+    assert end(x) == -1                            # a peer's area is missing
