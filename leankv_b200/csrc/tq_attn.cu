@@ -36,6 +36,9 @@
 #include <cstring>
 #include <type_traits>
 
+#include <algorithm>
+#include <atomic>
+
 #include "common.cuh"
 #include "tq_layout.cuh"
 
@@ -202,6 +205,7 @@ __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const flo
 
 // ---- main kernel -----------------------------------------------------------
 #include "tq_attn_kernel.cuh"
+#include "tq_prefill_kernel.cuh"
 
 // ---- host side ---------------------------------------------------------------
 struct AttnPlan {
@@ -493,25 +497,55 @@ __global__ void __launch_bounds__(128) tq_prefill_tables_kernel(const int32_t* _
     for (int k = threadIdx.x; k < n; k += blockDim.x) indices[first + k] = seq_pages[k];
 }
 
+// LEANKV_PREFILL_ATTN=rows runs a chunk as decode rows (one page-table row per token) instead of the
+// query-tile kernel.
+static bool prefill_as_rows() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("LEANKV_PREFILL_ATTN");
+        v = (e != nullptr && e[0] == 'r') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+struct TilePlan {
+    int n_tiles, n_splits;
+    size_t off_qprime, off_opart, off_ml, total;
+};
+// The pages of a query tile are cut into up to 8 ranges of at least ~16 pages, handled by separate CTAs, unless
+// the (tile, kv head) pairs alone already make several waves: many short CTAs fill the SMs evenly although
+// causal tiles differ in length (measured at 512 tokens after 3584: 2 ranges 366 us, 8 ranges 312 us).
+static TilePlan make_tile_plan(int T, int start_pos, int Hq, int Hkv) {
+    TilePlan tp;
+    tp.n_tiles = (T + kPfTokens - 1) / kPfTokens;
+    const long long ctas = (long long)tp.n_tiles * Hkv, slots = (long long)sm_count() * 3;
+    long long s = ((long long)start_pos + T + kPage - 1) / kPage / 16;
+    if (ctas >= 4 * slots) s = 1;
+    if (s > 8) s = 8;
+    if (s < 1) s = 1;
+    tp.n_splits = (int)s;
+    const size_t n_vec = (size_t)T * Hq;
+    tp.off_qprime = 256;
+    tp.off_opart = tp.off_qprime + round_up(sizeof(float) * n_vec * kDim, 256);
+    tp.off_ml = tp.off_opart + round_up(sizeof(float) * n_vec * kDim * tp.n_splits, 256);
+    tp.total = tp.off_ml + round_up(sizeof(float) * n_vec * 2 * tp.n_splits, 256);
+    return tp;
+}
+
 extern "C" size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, int n_q_heads,
                                                          int n_kv_heads) {
     if (T <= 0 || T > 65535 || start_pos < 0 || (long long)start_pos + T > (1ll << 24) || n_q_heads <= 0 ||
         n_kv_heads <= 0 || prefill_rows_pages(start_pos, T) > 0x7fffffffll)
         return 0;
-    return make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads).total;
+    const size_t rows = make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads).total;
+    const size_t tiles = make_tile_plan(T, start_pos, n_q_heads, n_kv_heads).total;
+    return rows > tiles ? rows : tiles;
 }
 
-extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads,
-                                      int n_kv_heads, const void* pool, int n_pages,
-                                      const int32_t* seq_pages, const float* Pi_k, const float* Pi_v,
-                                      const float* centroids, float scale, void* workspace,
-                                      size_t workspace_bytes, void* stream) {
-    if (T < 0 || start_pos < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_pages <= 0) return LEANKV_EINVAL;
-    if (T == 0) return LEANKV_OK;
-    if (!q || !out || !pool || !seq_pages || !workspace) return LEANKV_EINVAL;
-    if (T > 65535 || (long long)start_pos + T > (1ll << 24)) return LEANKV_ELIMIT;
-    if (prefill_rows_pages(start_pos, T) > 0x7fffffffll) return LEANKV_ELIMIT;     // page-table offsets are int32
-    if (!aligned16(workspace)) return LEANKV_EALIGN;
+static int prefill_rows_launch(const void* q, void* out, int T, int start_pos, int n_q_heads, int n_kv_heads,
+                               const void* pool, int n_pages, const int32_t* seq_pages, const float* Pi_k,
+                               const float* Pi_v, const float* centroids, float scale, void* workspace,
+                               size_t workspace_bytes, void* stream) {
     const PrefillPlan pp = make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads);
     if (workspace_bytes < pp.total) return LEANKV_EWORKSPACE;
     char* ws = static_cast<char*>(workspace);
@@ -530,6 +564,73 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
                                   indices));
     return attn_launch(q, nullptr, out, T, n_q_heads, n_kv_heads, pool, n_pages, indptr, indices, last_len,
                        pp.max_pages, Pi_k, Pi_v, centroids, scale, workspace, pp.attn_bytes, kAttnRowsFolded, stream);
+}
+
+extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads,
+                                      int n_kv_heads, const void* pool, int n_pages,
+                                      const int32_t* seq_pages, const float* Pi_k, const float* Pi_v,
+                                      const float* centroids, float scale, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+    if (T < 0 || start_pos < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_pages <= 0) return LEANKV_EINVAL;
+    if (T == 0) return LEANKV_OK;
+    if (!q || !out || !pool || !seq_pages || !workspace || !Pi_k || !Pi_v || !centroids) return LEANKV_EINVAL;
+    if (n_q_heads != n_kv_heads * kGroup) return LEANKV_EUNSUPPORTED;
+    if (T > 65535 || (long long)start_pos + T > (1ll << 24)) return LEANKV_ELIMIT;
+    if (prefill_rows_pages(start_pos, T) > 0x7fffffffll) return LEANKV_ELIMIT;     // page-table offsets are int32
+    if (!aligned16(workspace) || !aligned16(q) || !aligned16(out) || !aligned16(pool) || !aligned16(Pi_k) ||
+        !aligned16(Pi_v))
+        return LEANKV_EALIGN;
+    if (workspace_bytes < leankv_tq_prefill_attn_workspace_bytes(T, start_pos, n_q_heads, n_kv_heads))
+        return LEANKV_EWORKSPACE;
+    if (prefill_as_rows())
+        return prefill_rows_launch(q, out, T, start_pos, n_q_heads, n_kv_heads, pool, n_pages, seq_pages, Pi_k,
+                                   Pi_v, centroids, scale, workspace, workspace_bytes, stream);
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const TilePlan tp = make_tile_plan(T, start_pos, n_q_heads, n_kv_heads);
+    char* ws = static_cast<char*>(workspace);
+    float* qprime = reinterpret_cast<float*>(ws + tp.off_qprime);
+    float* o_part = reinterpret_cast<float*>(ws + tp.off_opart);
+    float* ml_part = reinterpret_cast<float*>(ws + tp.off_ml);
+    const Lut& lut = get_lut(centroids);
+    static std::atomic<unsigned long long> attr_done{0};          // bit per device ordinal (< 64)
+    int dev = 0;
+    LEANKV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return LEANKV_ELIMIT;
+    if (((attr_done.load(std::memory_order_acquire) >> dev) & 1ull) == 0) {
+        LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kPfSmemBytes));
+        LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_rot_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kRotSmemBytes));
+        LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_rot_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kRotSmemBytes));
+        attr_done.fetch_or(1ull << dev, std::memory_order_release);
+    }
+    const int n_vec = T * n_q_heads;
+    const int rot_grid = std::min((n_vec + kRotRows - 1) / kRotRows, sm_count() * 2);
+    LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<true>, dim3(rot_grid), dim3(128), kRotSmemBytes, st, q,
+                                  static_cast<const float*>(nullptr), 0, Pi_k, static_cast<void*>(qprime), n_vec));
+    PrefillParams p{};
+    p.qprime = qprime;
+    p.qscale = scale * kLog2e;
+    p.o_part = o_part;
+    p.ml_part = ml_part;
+    p.n_splits = tp.n_splits;
+    p.pool = static_cast<const uint8_t*>(pool);
+    p.n_pages = n_pages;
+    p.H = n_kv_heads;
+    p.seq_pages = seq_pages;
+    p.T = T;
+    p.start_pos = start_pos;
+    p.tl0 = lut.tl0; p.tl1 = lut.tl1; p.th0 = lut.th0; p.th1 = lut.th1;
+    p.inv_alpha = 1.0f / lut.alpha;
+    p.status = reinterpret_cast<int*>(ws);
+    LEANKV_CUDA_TRY(launch_kernel(tq_prefill_attn_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
+                                  dim3(kAttnThreads), kPfSmemBytes, st, p));
+    LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<false>, dim3(rot_grid), dim3(128), kRotSmemBytes, st,
+                                  static_cast<const void*>(o_part), static_cast<const float*>(ml_part), tp.n_splits,
+                                  Pi_v, out, n_vec));
+    return LEANKV_OK;
 }
 
 extern "C" int leankv_tq_decode_attn_status(const void* workspace, int* status) {

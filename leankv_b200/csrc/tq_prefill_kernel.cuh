@@ -1,0 +1,485 @@
+// Causal attention of a chunk of prompt tokens over the packed pages, one query tile per CTA
+// (included by tq_attn.cu, inside namespace leankv::{anonymous}).
+//
+// A CTA takes 16 consecutive query tokens of one kv head: 64 rows (token, GQA head), 16 per warp.
+// It walks the sequence's pages up to the tile's last token; each page is fetched once (bulk copy,
+// ring of 3), de-quantized once into shared memory as fp16 operands by the 128 threads (one 32-code
+// unit each, the same byte-permute look-ups as the decode kernel) and then used by all four warps:
+//   scores  S[16 rows][16 tokens] = Q''[16][128] . Khat^T    (mma.m16n8k16, Q'' = hi + lo fp16 halves
+//                                                             of the rotated, pre-scaled query)
+//   output  O[16 rows][128]      += P[16][16] . Vhat[16][128] (probabilities times value norms in fp16)
+// with the usual online softmax per row in registers. So a page costs one de-quantization per 16
+// query tokens instead of one per token, which is what the decode kernel run on prompt rows pays.
+// When a tile has many pages they are cut into ranges handled by separate CTAs (grid z). Each CTA leaves its
+// partial result in the rotated space (fp32 sums, maximum, denominator); tq_rot_rows_kernel<false> merges the
+// ranges, normalises and applies Pi_V.
+
+struct PrefillParams {
+    const float* qprime;       // [T][Hq][128] rotated queries (Pi_K q), fp32
+    float qscale;              // softmax scale * log2(e)
+    float* o_part;             // [n_splits][T][Hq][128] un-normalised partial results in the rotated space
+    float* ml_part;            // [n_splits][T][Hq][2]: running maximum (log2 units) and denominator of each partial
+    int n_splits;              // the pages of a query tile are cut into this many ranges (grid z)
+    const uint8_t* pool;
+    int n_pages, H;
+    const int32_t* seq_pages;  // the sequence's page ids in order
+    int T, start_pos;
+    uint32_t tl0, tl1, th0, th1;
+    float inv_alpha;
+    int* status;
+};
+
+constexpr int kPfTokens = 16;                  // query tokens per CTA
+constexpr int kPfRows = kPfTokens * kGroup;    // 64 rows
+constexpr int kPfStride = kDim + 8;            // halfs per row of the Q / K tiles (bank-conflict-free fragments)
+constexpr int kPfVtStride = 24;                // halfs per row of the transposed V tile (16 tokens + padding)
+constexpr int kPfStages = 3;
+constexpr size_t kPfSmemBytes = (size_t)2 * kPfRows * kPfStride * 2      // Q'' hi and lo
+                                + 2 * (size_t)kPage * kPfStride * 2       // K tiles [token][coord], two buffers
+                                + 2 * (size_t)kDim * kPfVtStride * 2      // V tiles [coord][token], two buffers
+                                + (size_t)kPfStages * 2 * kChunkBytes     // raw chunks
+                                + 2 * 2 * kPage * sizeof(float)           // norms / alpha of K and V, two buffers
+                                + kPfStages * 8;                          // mbarriers
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const PrefillParams p) {
+    extern __shared__ __align__(128) uint8_t pf_smem[];
+    uint8_t* s_raw = pf_smem;                                                   // [stages][K chunk | V chunk]
+    __half* s_qh = reinterpret_cast<__half*>(s_raw + kPfStages * 2 * kChunkBytes);
+    __half* s_ql = s_qh + kPfRows * kPfStride;
+    // operands of a page, double-buffered: K tile, transposed V tile, norms / alpha per token
+    constexpr int kKTile = kPage * kPfStride, kVTile = kDim * kPfVtStride;
+    __half* s_k = s_ql + kPfRows * kPfStride;                                   // [2][kKTile]
+    __half* s_vt = s_k + 2 * kKTile;                                            // [2][kVTile]
+    float* s_kn = reinterpret_cast<float*>(s_vt + 2 * kVTile);                  // [2][kPage]
+    float* s_vn = s_kn + 2 * kPage;                                             // [2][kPage]
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_vn + 2 * kPage);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int H = p.H, Hq = H * kGroup;
+    const int n_tiles = (p.T + kPfTokens - 1) / kPfTokens;
+    const int tile = n_tiles - 1 - (int)blockIdx.x;          // the tiles with the most pages start first
+    const int kvh = blockIdx.y;
+    const int tok0 = tile * kPfTokens;                       // first query token of the tile (chunk-relative)
+    const int last_tok = min(tok0 + kPfTokens, p.T) - 1;
+    const int n_all = (p.start_pos + last_tok) / kPage + 1;  // pages the tile's last token sees
+    const int pg_lo = (int)((long long)n_all * blockIdx.z / p.n_splits);
+    const int n_pg = (int)((long long)n_all * (blockIdx.z + 1) / p.n_splits) - pg_lo;   // this CTA's share of them
+
+    const uint32_t bar0 = smem_u32(s_bar);
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kPfStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_begin();
+    __syncthreads();
+
+    const size_t page_stride = (size_t)2 * H * kChunkBytes, kv_stride = (size_t)H * kChunkBytes;
+    const uint8_t* pool_kvh = p.pool + (size_t)kvh * kChunkBytes;
+    bool bad_page = false;
+    auto issue = [&](int pg) {                               // thread 0 only
+        int id = p.seq_pages[pg_lo + pg];
+        if (id < 0 || id >= p.n_pages) {
+            id = 0;
+            bad_page = true;
+        }
+        const int s = pg % kPfStages;
+        const uint8_t* src = pool_kvh + (size_t)id * page_stride;
+        const uint32_t dst = smem_u32(s_raw + (size_t)s * 2 * kChunkBytes);
+        mbar_expect_tx(bar0 + 8 * s, 2 * kChunkBytes);
+        bulk_g2s(dst, src, kChunkBytes, bar0 + 8 * s);
+        bulk_g2s(dst + kChunkBytes, src + kv_stride, kChunkBytes, bar0 + 8 * s);
+    };
+    if (tid == 0)
+        for (int pg = 0; pg < min(kPfStages, n_pg); ++pg) issue(pg);
+
+    // ---- the tile's queries: rotated, scaled, split into fp16 high and low halves ----
+    for (int i = tid; i < kPfRows * (kDim / 4); i += kAttnThreads) {
+        const int r = i / (kDim / 4), c4 = i % (kDim / 4);
+        const int tok = tok0 + (r >> 2), head = r & 3;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tok < p.T)
+            v = *reinterpret_cast<const float4*>(p.qprime + ((size_t)tok * Hq + (size_t)kvh * kGroup + head) * kDim + 4 * c4);
+        const float x[4] = {v.x * p.qscale, v.y * p.qscale, v.z * p.qscale, v.w * p.qscale};
+        __half hi[4], lo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            hi[k] = __float2half_rn(x[k]);
+            lo[k] = __float2half_rn(x[k] - __half2float(hi[k]));
+        }
+        *reinterpret_cast<uint2*>(s_qh + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(hi);
+        *reinterpret_cast<uint2*>(s_ql + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(lo);
+    }
+
+    // this lane's two rows of the warp's 16: (token, head) of rows g and g + 8
+    const int qpos0 = p.start_pos + tok0 + 4 * warp + (g >> 2);          // position of row g's token
+    const int qpos1 = qpos0 + 2;                                         // row g + 8: two tokens further
+    float m0 = kNoRef, m1 = kNoRef, l0 = 0.f, l1 = 0.f;
+    float acc[16][4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    __syncthreads();                                                     // the query tile is in shared memory
+    // the warp's query rows as A operands, held in registers for the whole page loop
+    uint32_t qa_h[kDim / 16][4], qa_l[kDim / 16][4];
+    {
+        const __half* qh_row0 = s_qh + (16 * warp + g) * kPfStride + 2 * t;
+        const __half* ql_row0 = s_ql + (16 * warp + g) * kPfStride + 2 * t;
+#pragma unroll
+        for (int ks = 0; ks < kDim / 16; ++ks) {
+            qa_h[ks][0] = *reinterpret_cast<const uint32_t*>(qh_row0 + 16 * ks);
+            qa_h[ks][1] = *reinterpret_cast<const uint32_t*>(qh_row0 + 8 * kPfStride + 16 * ks);
+            qa_h[ks][2] = *reinterpret_cast<const uint32_t*>(qh_row0 + 16 * ks + 8);
+            qa_h[ks][3] = *reinterpret_cast<const uint32_t*>(qh_row0 + 8 * kPfStride + 16 * ks + 8);
+            qa_l[ks][0] = *reinterpret_cast<const uint32_t*>(ql_row0 + 16 * ks);
+            qa_l[ks][1] = *reinterpret_cast<const uint32_t*>(ql_row0 + 8 * kPfStride + 16 * ks);
+            qa_l[ks][2] = *reinterpret_cast<const uint32_t*>(ql_row0 + 16 * ks + 8);
+            qa_l[ks][3] = *reinterpret_cast<const uint32_t*>(ql_row0 + 8 * kPfStride + 16 * ks + 8);
+        }
+    }
+    // ldmatrix row addresses of this lane (bytes, shared window): matrix L >> 3, row L & 7
+    const uint32_t k_frag_addr =
+        smem_u32(s_k + (8 * (lane >> 4) + (lane & 7)) * kPfStride + 8 * ((lane >> 3) & 1));
+    const uint32_t v_frag_addr =
+        smem_u32(s_vt + (8 * (lane >> 4) + (lane & 7)) * kPfVtStride + 8 * ((lane >> 3) & 1));
+    bool failed = false;
+    int fail_pg = 0;
+
+    // De-quantize page pg of this CTA's range into operand buffer pg & 1: thread = one unit of 32 codes
+    // (64 K units, 64 V units). Returns false if the page's copy did not arrive within the bound.
+    auto dequant = [&](int pg) -> bool {
+        const int s = pg % kPfStages, buf = pg & 1;
+        if (!mbar_wait_bounded(bar0 + 8 * s, (uint32_t)((pg / kPfStages) & 1))) return false;
+        const uint8_t* raw = s_raw + (size_t)s * 2 * kChunkBytes;
+        const bool is_v = tid >= 64;
+        const int ui = tid & 63;
+        const Unit u = load_unit(reinterpret_cast<const uint32_t*>(raw + (is_v ? kChunkBytes : 0)), ui);
+        uint32_t h2[16];                     // 32 fp16 values alpha * c[code], two per register, code order
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t sa = u.s[w], sb = sa >> 16;
+            const uint32_t la = __byte_perm(p.tl0, p.tl1, sa), ha = __byte_perm(p.th0, p.th1, sa);
+            const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb), hb = __byte_perm(p.th0, p.th1, sb);
+            h2[4 * w + 0] = __byte_perm(la, ha, 0x5140);
+            h2[4 * w + 1] = __byte_perm(la, ha, 0x7362);
+            h2[4 * w + 2] = __byte_perm(lb, hb, 0x5140);
+            h2[4 * w + 3] = __byte_perm(lb, hb, 0x7362);
+        }
+        if (!is_v) {
+            // K unit ui = 4 * token + quarter: coordinates 32 * quarter .. + 31 of the token, in order
+            uint4* dst = reinterpret_cast<uint4*>(s_k + buf * kKTile + (ui >> 2) * kPfStride + 32 * (ui & 3));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
+        } else {
+            // V unit: coordinates 16 * grp .. + 15 of tokens 2 * pair and 2 * pair + 1, code 2 * c + parity:
+            // register i holds the pair's two tokens of coordinate 16 * grp + i
+            const int grp = (ui & 31) >> 2, pair = (ui & 3) + ((ui >> 5) << 2);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                *reinterpret_cast<uint32_t*>(s_vt + buf * kVTile + (16 * grp + i) * kPfVtStride + 2 * pair) = h2[i];
+        }
+        if (tid < 2 * kPage) {
+            const __half* nrm = reinterpret_cast<const __half*>(raw + (tid >= kPage ? kChunkBytes : 0) + kNormOffsetBytes);
+            (tid >= kPage ? s_vn : s_kn)[buf * kPage + (tid & (kPage - 1))] = __half2float(nrm[tid & (kPage - 1)]) * p.inv_alpha;
+        }
+        return true;
+    };
+
+    // One barrier per page: it publishes the operands of page pg (written before it) and, since every warp
+    // reaches it only after its work on page pg - 1, frees the other buffer for page pg + 1.
+    bool got = n_pg > 0 ? dequant(0) : true;
+    for (int pg = 0; pg < n_pg; ++pg) {
+        if (__syncthreads_or(!got)) {
+            failed = true;
+            fail_pg = pg;
+            break;
+        }
+        if (tid == 0 && pg + kPfStages < n_pg) issue(pg + kPfStages);      // page pg's raw chunk has been consumed
+        const int buf = pg & 1;
+        const float* kn = s_kn + buf * kPage;
+        const float* vn = s_vn + buf * kPage;
+        const uint32_t k_frag = k_frag_addr + (uint32_t)(buf * kKTile * 2);
+        const uint32_t v_frag = v_frag_addr + (uint32_t)(buf * kVTile * 2);
+
+        // ---- scores of this warp's 16 rows against the page's 16 tokens ----
+        float sc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < kDim / 16; ++ks) {
+            // one ldmatrix brings the B fragments of both token tiles: matrices (tile 0, k low), (tile 0, k high),
+            // (tile 1, k low), (tile 1, k high); lane L supplies row L & 7 of matrix L >> 3
+            uint32_t kb[4];
+            ldmatrix_x4(kb, k_frag + 2 * 16 * ks);
+            mma_16816(sc[0], qa_h[ks][0], qa_h[ks][1], qa_h[ks][2], qa_h[ks][3], kb[0], kb[1]);
+            mma_16816(sc[0], qa_l[ks][0], qa_l[ks][1], qa_l[ks][2], qa_l[ks][3], kb[0], kb[1]);
+            mma_16816(sc[1], qa_h[ks][0], qa_h[ks][1], qa_h[ks][2], qa_h[ks][3], kb[2], kb[3]);
+            mma_16816(sc[1], qa_l[ks][0], qa_l[ks][1], qa_l[ks][2], qa_l[ks][3], kb[2], kb[3]);
+        }
+        // key norm, causal mask (key position <= query position; every such position holds a token)
+        const int kbase = (pg_lo + pg) * kPage;
+        float rmax0 = kNoRef, rmax1 = kNoRef;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int tok = 8 * j + 2 * t + c;
+                const float knt = kn[tok];
+                const float v0 = kbase + tok <= qpos0 ? sc[j][c] * knt : kNoRef;
+                const float v1 = kbase + tok <= qpos1 ? sc[j][2 + c] * knt : kNoRef;
+                sc[j][c] = v0;
+                sc[j][2 + c] = v1;
+                rmax0 = fmaxf(rmax0, v0);
+                rmax1 = fmaxf(rmax1, v1);
+            }
+        }
+        rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 1));
+        rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 2));
+        rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 1));
+        rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 2));
+        const float mn0 = fmaxf(m0, rmax0), mn1 = fmaxf(m1, rmax1);
+        const float f0 = ex2_approx(m0 - mn0), f1 = ex2_approx(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        // probabilities; a masked entry is exactly 0 (kNoRef - m underflows), also while a row has seen nothing
+        float pr[2][4];
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                pr[j][c] = sc[j][c] > 0.5f * kNoRef ? ex2_approx(sc[j][c] - m0) : 0.f;
+                pr[j][2 + c] = sc[j][2 + c] > 0.5f * kNoRef ? ex2_approx(sc[j][2 + c] - m1) : 0.f;
+                sum0 += pr[j][c];
+                sum1 += pr[j][2 + c];
+            }
+        }
+        l0 = l0 * f0 + sum0;                     // per-lane partial sums; the quad is added up at the end
+        l1 = l1 * f1 + sum1;
+        if (__any_sync(0xffffffffu, f0 != 1.0f || f1 != 1.0f)) {          // a row's maximum moved: rescale its sums
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                acc[j][0] *= f0; acc[j][1] *= f0;
+                acc[j][2] *= f1; acc[j][3] *= f1;
+            }
+        }
+        // P (times value norm / alpha) as the A operand: tokens 2t, 2t+1 (tile 0) and 2t+8, 2t+9 (tile 1)
+        const float vn0 = vn[2 * t], vn1 = vn[2 * t + 1], vn8 = vn[2 * t + 8], vn9 = vn[2 * t + 9];
+        const uint32_t a0 = pack_h2(pr[0][0] * vn0, pr[0][1] * vn1);
+        const uint32_t a1 = pack_h2(pr[0][2] * vn0, pr[0][3] * vn1);
+        const uint32_t a2 = pack_h2(pr[1][0] * vn8, pr[1][1] * vn9);
+        const uint32_t a3 = pack_h2(pr[1][2] * vn8, pr[1][3] * vn9);
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            // matrices (coords 8j.., tokens 0-7), (8j.., tokens 8-15), (8(j+1).., 0-7), (8(j+1).., 8-15)
+            uint32_t vb[4];
+            ldmatrix_x4(vb, v_frag + 2 * 8 * j * kPfVtStride);
+            mma_16816(acc[j], a0, a1, a2, a3, vb[0], vb[1]);
+            mma_16816(acc[j + 1], a0, a1, a2, a3, vb[2], vb[3]);
+        }
+        if (pg + 1 < n_pg) got = dequant(pg + 1);        // into the other buffer, while slower warps finish page pg
+    }
+    if (failed || bad_page) {
+        if (tid == 0) atomicOr(p.status, failed ? kStatusWaitTimeout : kStatusBadPage);
+        if (failed) {
+            // give the copies that were issued and not consumed a bounded chance to land before the CTA's
+            // shared memory is handed to another CTA
+            for (int q = fail_pg; q < min(fail_pg + kPfStages, n_pg); ++q)
+                mbar_wait_bounded(bar0 + 8 * (q % kPfStages), (uint32_t)((q / kPfStages) & 1));
+            return;
+        }
+    }
+
+    // ---- this range's partial result, in the rotated space: sums, running maximum, denominator ----
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int tokA = tok0 + 4 * warp + (g >> 2), tokB = tokA + 2, head = g & 3;
+    const size_t n_vec = (size_t)p.T * Hq;
+    const size_t vA = (size_t)tokA * Hq + (size_t)kvh * kGroup + head, vB = (size_t)tokB * Hq + (size_t)kvh * kGroup + head;
+    float* oA = p.o_part + ((size_t)blockIdx.z * n_vec + vA) * kDim + 2 * t;
+    float* oB = p.o_part + ((size_t)blockIdx.z * n_vec + vB) * kDim + 2 * t;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (tokA < p.T) *reinterpret_cast<float2*>(oA + 8 * j) = make_float2(acc[j][0], acc[j][1]);
+        if (tokB < p.T) *reinterpret_cast<float2*>(oB + 8 * j) = make_float2(acc[j][2], acc[j][3]);
+    }
+    if (t == 0) {
+        if (tokA < p.T) *reinterpret_cast<float2*>(p.ml_part + ((size_t)blockIdx.z * n_vec + vA) * 2) = make_float2(m0, l0);
+        if (tokB < p.T) *reinterpret_cast<float2*>(p.ml_part + ((size_t)blockIdx.z * n_vec + vB) * 2) = make_float2(m1, l1);
+    }
+}
+
+// Rotation of many vectors by one 128 x 128 matrix on the tensor cores: the matrix is split into fp16 high
+// and low halves held in shared memory (B operands, via ldmatrix), the vectors likewise (A operands), and
+// out = a_h.M_h + a_h.M_l (+ a_l.M_h when the input is not exactly fp16) with fp32 accumulation: the dropped
+// low x low term is below 2^-22 of |a||M|. A CTA takes 64 vectors at a time, 16 per warp.
+//   kForward:  out[v][j] = sum_k M[j][k] * in[v][k]     (query rotation, M = Pi_K; in fp16 (exact), out fp32)
+//   !kForward: out[v][j] = sum_i in[v][i] * M[i][j]     (inverse value rotation, M = Pi_V; in = the page ranges'
+//              partial results of the prefill kernel, merged and normalised here; out fp16)
+constexpr int kRotRows = 64;
+constexpr int kRotMaxSplits = 8;
+constexpr size_t kRotSmemBytes = (size_t)2 * kDim * kPfStride * 2 + (size_t)2 * kRotRows * kPfStride * 2 +
+                                 (size_t)kRotRows * kRotMaxSplits * sizeof(float);
+
+template <bool kForward>
+__global__ void __launch_bounds__(128) tq_rot_rows_kernel(const void* in, const float* ml_part, int n_splits,
+                                                         const float* M, void* out, int n_vec) {
+    extern __shared__ __align__(128) uint8_t rot_smem[];
+    __half* s_bh = reinterpret_cast<__half*>(rot_smem);          // [n = out coord][k]: high halves of B
+    __half* s_bl = s_bh + kDim * kPfStride;
+    __half* s_ah = s_bl + kDim * kPfStride;                      // [row][k]: high halves of the input rows
+    __half* s_al = s_ah + kRotRows * kPfStride;
+    float* s_w = reinterpret_cast<float*>(s_al + kRotRows * kPfStride);   // [row][range]: merge weights
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    // The matrix is a constant of the cache: stage it before the dependency wait. B[k][n] is M[n][k] for the
+    // forward rotation (rows of M as they are) and M[k][n] for the inverse one (transposed copy).
+    if (kForward) {
+        for (int i = tid; i < kDim * (kDim / 4); i += 128) {
+            const int r = i / (kDim / 4), c4 = i % (kDim / 4);
+            const float4 w = __ldg(reinterpret_cast<const float4*>(M + (size_t)r * kDim) + c4);
+            const float x[4] = {w.x, w.y, w.z, w.w};
+            __half hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                hi[e] = __float2half_rn(x[e]);
+                lo[e] = __float2half_rn(x[e] - __half2float(hi[e]));
+            }
+            *reinterpret_cast<uint2*>(s_bh + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(hi);
+            *reinterpret_cast<uint2*>(s_bl + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(lo);
+        }
+    } else {
+        // thread n builds row n of the copy from column n of M (coalesced reads, two k per 32-bit store)
+#pragma unroll 8
+        for (int k2 = 0; k2 < kDim / 2; ++k2) {
+            const float w0 = __ldg(M + (size_t)(2 * k2) * kDim + tid), w1 = __ldg(M + (size_t)(2 * k2 + 1) * kDim + tid);
+            const __half h0 = __float2half_rn(w0), h1 = __float2half_rn(w1);
+            *reinterpret_cast<__half2*>(s_bh + tid * kPfStride + 2 * k2) = __halves2half2(h0, h1);
+            *reinterpret_cast<__half2*>(s_bl + tid * kPfStride + 2 * k2) =
+                __floats2half2_rn(w0 - __half2float(h0), w1 - __half2float(h1));
+        }
+    }
+    pdl_begin();
+    const uint32_t b_frag = (uint32_t)((8 * (lane >> 4) + (lane & 7)) * kPfStride + 8 * ((lane >> 3) & 1)) * 2;
+    for (int v0 = blockIdx.x * kRotRows; v0 < n_vec; v0 += gridDim.x * kRotRows) {
+        __syncthreads();                           // the matrix is staged / the previous tile has been consumed
+        // ---- the tile's input rows as fp16 high and low halves ----
+        if (!kForward) {
+            // weights that merge the page ranges' partial results of a row: scale to the common maximum and
+            // divide by the merged denominator (the value norms already carry 1 / alpha); one thread per row
+            if (tid < kRotRows) {
+                const int v = v0 + tid;
+                float mz[kRotMaxSplits], lz[kRotMaxSplits];
+                float m = kNoRef;
+#pragma unroll
+                for (int z = 0; z < kRotMaxSplits; ++z) {
+                    mz[z] = kNoRef;
+                    lz[z] = 0.f;
+                    if (z < n_splits && v < n_vec) {
+                        const float2 ml = *reinterpret_cast<const float2*>(ml_part + ((size_t)z * n_vec + v) * 2);
+                        mz[z] = ml.x;
+                        lz[z] = ml.y;
+                    }
+                    m = fmaxf(m, mz[z]);
+                }
+                float l = 0.f;
+#pragma unroll
+                for (int z = 0; z < kRotMaxSplits; ++z) {
+                    mz[z] = ex2_approx(mz[z] - m);
+                    l = fmaf(mz[z], lz[z], l);
+                }
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+                for (int z = 0; z < kRotMaxSplits; ++z) s_w[tid * kRotMaxSplits + z] = mz[z] * inv;
+            }
+            __syncthreads();
+        }
+#pragma unroll 4
+        for (int i = tid; i < kRotRows * (kDim / 4); i += 128) {
+            const int r = i / (kDim / 4), c4 = i % (kDim / 4);
+            const int v = v0 + r;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (v < n_vec) {
+                if (kForward) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(in) + (size_t)v * kDim + 4 * c4);
+                    const float2 p0 = h2_to_f2(raw.x), p1 = h2_to_f2(raw.y);
+                    x[0] = p0.x; x[1] = p0.y; x[2] = p1.x; x[3] = p1.y;
+                } else {
+                    const float* o_part = static_cast<const float*>(in);
+                    for (int z = 0; z < n_splits; ++z) {
+                        const float f = s_w[r * kRotMaxSplits + z];
+                        const float4 o = *reinterpret_cast<const float4*>(o_part + ((size_t)z * n_vec + v) * kDim + 4 * c4);
+                        x[0] = fmaf(f, o.x, x[0]); x[1] = fmaf(f, o.y, x[1]);
+                        x[2] = fmaf(f, o.z, x[2]); x[3] = fmaf(f, o.w, x[3]);
+                    }
+                }
+            }
+            __half hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                hi[e] = __float2half_rn(x[e]);
+                lo[e] = __float2half_rn(x[e] - __half2float(hi[e]));
+            }
+            *reinterpret_cast<uint2*>(s_ah + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(hi);
+            if (!kForward) *reinterpret_cast<uint2*>(s_al + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(lo);
+        }
+        __syncthreads();
+        float acc[16][4];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        const __half* ah_row = s_ah + (16 * warp + g) * kPfStride + 2 * t;
+        const __half* al_row = s_al + (16 * warp + g) * kPfStride + 2 * t;
+#pragma unroll
+        for (int ks = 0; ks < kDim / 16; ++ks) {
+            uint32_t ah[4], al[4] = {0u, 0u, 0u, 0u};
+            ah[0] = *reinterpret_cast<const uint32_t*>(ah_row + 16 * ks);
+            ah[1] = *reinterpret_cast<const uint32_t*>(ah_row + 8 * kPfStride + 16 * ks);
+            ah[2] = *reinterpret_cast<const uint32_t*>(ah_row + 16 * ks + 8);
+            ah[3] = *reinterpret_cast<const uint32_t*>(ah_row + 8 * kPfStride + 16 * ks + 8);
+            if (!kForward) {
+                al[0] = *reinterpret_cast<const uint32_t*>(al_row + 16 * ks);
+                al[1] = *reinterpret_cast<const uint32_t*>(al_row + 8 * kPfStride + 16 * ks);
+                al[2] = *reinterpret_cast<const uint32_t*>(al_row + 16 * ks + 8);
+                al[3] = *reinterpret_cast<const uint32_t*>(al_row + 8 * kPfStride + 16 * ks + 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+                // matrices (n tile j, k low), (j, k high), (j + 1, k low), (j + 1, k high)
+                uint32_t bh[4], bl[4];
+                const uint32_t off = b_frag + (uint32_t)(8 * j * kPfStride + 16 * ks) * 2;
+                ldmatrix_x4(bh, smem_u32(s_bh) + off);
+                ldmatrix_x4(bl, smem_u32(s_bl) + off);
+                mma_16816(acc[j], ah[0], ah[1], ah[2], ah[3], bh[0], bh[1]);
+                mma_16816(acc[j], ah[0], ah[1], ah[2], ah[3], bl[0], bl[1]);
+                mma_16816(acc[j + 1], ah[0], ah[1], ah[2], ah[3], bh[2], bh[3]);
+                mma_16816(acc[j + 1], ah[0], ah[1], ah[2], ah[3], bl[2], bl[3]);
+                if (!kForward) {
+                    mma_16816(acc[j], al[0], al[1], al[2], al[3], bh[0], bh[1]);
+                    mma_16816(acc[j + 1], al[0], al[1], al[2], al[3], bh[2], bh[3]);
+                }
+            }
+        }
+        // rows g and g + 8 of the warp's 16; columns 8 j + 2 t, + 1
+        const int vA = v0 + 16 * warp + g, vB = vA + 8;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (kForward) {
+                float* o = static_cast<float*>(out);
+                if (vA < n_vec) *reinterpret_cast<float2*>(o + (size_t)vA * kDim + 8 * j + 2 * t) = make_float2(acc[j][0], acc[j][1]);
+                if (vB < n_vec) *reinterpret_cast<float2*>(o + (size_t)vB * kDim + 8 * j + 2 * t) = make_float2(acc[j][2], acc[j][3]);
+            } else {
+                __half* o = static_cast<__half*>(out);
+                if (vA < n_vec) *reinterpret_cast<__half2*>(o + (size_t)vA * kDim + 8 * j + 2 * t) = __floats2half2_rn(acc[j][0], acc[j][1]);
+                if (vB < n_vec) *reinterpret_cast<__half2*>(o + (size_t)vB * kDim + 8 * j + 2 * t) = __floats2half2_rn(acc[j][2], acc[j][3]);
+            }
+        }
+    }
+}

@@ -358,11 +358,32 @@ def test_prefill_attention_on_packed_pages_is_causal_and_matches_decode_steps_an
     for t in (0, 15, 16, 77, T - 1):
         n = t + 1
         one = rp.attention(q[t:t + 1], [0, (n + 15) // 16], pages[:(n + 15) // 16], [(n - 1) % 16 + 1])
-        assert rel_l2(full[t].cpu(), one[0].cpu()) < 2e-4, t
+        assert rel_l2(full[t].cpu(), one[0].cpu()) < 5e-4, t
     # a later chunk alone gives the same rows
     for start in (37, 64, 148):
         part = rp.prefill_attention(q[start:], pages, start)
-        assert rel_l2(part.cpu(), full[start:].cpu()) < 2e-4, start
+        assert rel_l2(part.cpu(), full[start:].cpu()) < 5e-4, start
+
+
+def test_prefill_attention_of_a_late_chunk_splits_the_page_range_over_ctas():
+    """A short chunk far into a long sequence: few query tiles, many pages each, so the kernel cuts every
+    tile's pages into ranges handled by separate CTAs and merges the partial results."""
+    dev = _dev()
+    H, ctx, T = 2, 1000, 52
+    gen = torch.Generator().manual_seed(35)
+    n_tok = ctx + T
+    n_pages = (n_tok + 15) // 16 + 1
+    pages = torch.randperm(n_pages, generator=gen).tolist()[:(n_tok + 15) // 16]
+    rp = RawPool(n_pages, H, dev)
+    k = (torch.randn(1, H, n_tok, 128, generator=gen) * 1.5).half().to(dev)
+    v = torch.randn(1, H, n_tok, 128, generator=gen).half().to(dev)
+    rp.append(k, v, [0, len(pages)], pages, [0])
+    q = torch.randn(T, 4 * H, 128, generator=gen).half().to(dev)
+    got = rp.prefill_attention(q, pages, ctx)
+    lens = [ctx + t + 1 for t in range(T)]
+    want = oracle_attention_from_pool(rp, q, [pages[:(n + 15) // 16] for n in lens], lens)
+    for t in range(T):
+        assert rel_l2(got[t].cpu(), want[t]) < ATTN_TOL, t
 
 
 def test_rotated_attention_plain_call_directly_after_a_multi_page_append():
