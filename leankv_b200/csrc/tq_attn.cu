@@ -71,7 +71,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 // status bits written to the workspace status word
 constexpr int kStatusWaitTimeout = 1;
 constexpr int kStatusBadPage = 2;
-constexpr int kAttnRowsFolded = 1 << 16;     // internal launch flag (see row_of in the kernel)
 
 struct AttnParams {
     const float* qprime;      // [B][Hq][128] rotated query Pi_k q
@@ -354,7 +353,7 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
         (q && !aligned16(Pi_k)) || !aligned16(Pi_v) || !aligned16(workspace))
         return LEANKV_EALIGN;
     if (B > 65535 || n_kv_heads > 65535) return LEANKV_ELIMIT;
-    if ((flags & ~(LEANKV_ATTN_EARLY_FETCH | kAttnRowsFolded)) != 0) return LEANKV_EINVAL;
+    if ((flags & ~LEANKV_ATTN_EARLY_FETCH) != 0) return LEANKV_EINVAL;
     const AttnPlan pl = make_plan(B, n_q_heads, n_kv_heads, max_pages_per_seq);
     if (workspace_bytes < pl.total) return LEANKV_EWORKSPACE;
     const Lut& lut = get_lut(centroids);
@@ -364,13 +363,8 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     const float* qprime = q_rot;
     if (q != nullptr) {
         float* dst = reinterpret_cast<float*>(ws + pl.off_qprime);
-        const int n_pairs = B * n_kv_heads;
-        if (n_pairs >= 1024 && n_pairs % 4 == 0)
-            LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel<4 * kGroup>, dim3(n_pairs / 4), dim3(128), 0, st,
-                                          static_cast<const __half*>(q), Pi_k, dst));
-        else
-            LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel<kGroup>, dim3(n_pairs), dim3(128), 0, st,
-                                          static_cast<const __half*>(q), Pi_k, dst));
+        LEANKV_CUDA_TRY(launch_kernel(tq_qrot_kernel<kGroup>, dim3(B * n_kv_heads), dim3(128), 0, st,
+                                      static_cast<const __half*>(q), Pi_k, dst));
         qprime = dst;
     }
 
@@ -396,9 +390,9 @@ static int attn_launch(const void* q, const float* q_rot, void* out, int B, int 
     p.status = reinterpret_cast<int*>(ws);
     // Few enough (sequence, kv head) pairs that a cluster of 8 or 4 CTAs per pair fits into one wave: the
     // pair's pages are split over its cluster and merged through distributed shared memory instead of the
-    // workspace. (Every pair gets the same number of CTAs whatever its length; batches with many pairs, and
-    // the folded rows of a prompt chunk, take the general kernel, whose flat split balances ragged lengths.)
-    if (attn_cluster() && (flags & kAttnRowsFolded) == 0) {
+    // workspace. (Every pair gets the same number of CTAs whatever its length; batches with many pairs take the
+    // general kernel, whose flat split balances ragged lengths.)
+    if (attn_cluster()) {
         const long long pairs = (long long)B * n_kv_heads, slots = (long long)sm_count() * 4;
         const int cs = pairs * 8 <= slots ? 8 : (pairs * 4 <= slots ? 4 : 0);
         if (cs != 0 && max_pages_per_seq <= attn_cluster_max_pages() * cs / 8) {
@@ -443,69 +437,14 @@ extern "C" int leankv_tq_decode_attn_rotated(const float* q_rot, void* out, int 
                        workspace, workspace_bytes, flags, stream);
 }
 
-// ---- causal attention of a chunk of prompt tokens over the packed pages ----------------------
-// Token t of the chunk (absolute position start_pos + t) is one row of a decode batch whose page list
-// is the first (start_pos + t) / 16 + 1 pages of the sequence and whose last page holds
-// (start_pos + t) % 16 + 1 tokens: the causal mask is the page table. The rows share pages, which
-// come from L2 after the first reader.
-struct PrefillPlan {
-    size_t attn_bytes, off_indptr, off_last, off_indices, total;
-    int max_pages;
-};
-
+// ---- causal attention of a chunk of prompt tokens over the packed pages (tq_prefill_kernel.cuh) ----
 static long long prefill_rows_pages(long long first_pos, long long n) {
-    // sum over pos in [first_pos, first_pos + n) of pos / 16 + 1
-    auto upto = [](long long m) {             // sum over pos in [0, m) of pos / 16 + 1
+    // sum over pos in [first_pos, first_pos + n) of pos / 16 + 1: page visits of the chunk's tokens
+    auto upto = [](long long m) {
         const long long full = m / kPage, rest = m % kPage;
         return (long long)kPage * full * (full + 1) / 2 + rest * (full + 1);
     };
     return upto(first_pos + n) - upto(first_pos);
-}
-
-static PrefillPlan make_prefill_plan(int T, int start_pos, int Hq, int Hkv) {
-    PrefillPlan pp;
-    pp.max_pages = (start_pos + T + kPage - 1) / kPage;
-    pp.attn_bytes = make_plan(T, Hq, Hkv, pp.max_pages).total;
-    pp.off_indptr = round_up(pp.attn_bytes, 256);
-    pp.off_last = pp.off_indptr + round_up(sizeof(int32_t) * ((size_t)T + 1), 256);
-    pp.off_indices = pp.off_last + round_up(sizeof(int32_t) * (size_t)T, 256);
-    pp.total = pp.off_indices + round_up(sizeof(int32_t) * (size_t)prefill_rows_pages(start_pos, T), 256);
-    return pp;
-}
-
-__global__ void __launch_bounds__(128) tq_prefill_tables_kernel(const int32_t* __restrict__ seq_pages, int T,
-                                                                 int start_pos, int32_t* __restrict__ indptr,
-                                                                 int32_t* __restrict__ last_len,
-                                                                 int32_t* __restrict__ indices) {
-    pdl_begin();
-    // Table row b holds token b / 2 (b even) or T - 1 - b / 2 (b odd): short and long rows alternate.
-    const int b = blockIdx.x, i = b >> 1;
-    auto upto = [](long long m) {             // sum over pos in [0, m) of pos / 16 + 1
-        const long long full = m / kPage, rest = m % kPage;
-        return (long long)kPage * full * (full + 1) / 2 + rest * (full + 1);
-    };
-    // rows before 2i: tokens 0 .. i-1 and T-i .. T-1
-    long long first = (upto(start_pos + i) - upto(start_pos)) + (upto((long long)start_pos + T) - upto((long long)start_pos + T - i));
-    if (b & 1) first += (start_pos + i) / kPage + 1;
-    const int pos = start_pos + ((b & 1) ? T - 1 - i : i);
-    const int n = pos / kPage + 1;
-    if (threadIdx.x == 0) {
-        indptr[b] = (int)first;
-        last_len[b] = pos % kPage + 1;
-        if (b == T - 1) indptr[T] = (int)first + n;
-    }
-    for (int k = threadIdx.x; k < n; k += blockDim.x) indices[first + k] = seq_pages[k];
-}
-
-// LEANKV_PREFILL_ATTN=rows runs a chunk as decode rows (one page-table row per token) instead of the
-// query-tile kernel.
-static bool prefill_as_rows() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = std::getenv("LEANKV_PREFILL_ATTN");
-        v = (e != nullptr && e[0] == 'r') ? 1 : 0;
-    }
-    return v == 1;
 }
 
 struct TilePlan {
@@ -537,33 +476,7 @@ extern "C" size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, i
     if (T <= 0 || T > 65535 || start_pos < 0 || (long long)start_pos + T > (1ll << 24) || n_q_heads <= 0 ||
         n_kv_heads <= 0 || prefill_rows_pages(start_pos, T) > 0x7fffffffll)
         return 0;
-    const size_t rows = make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads).total;
-    const size_t tiles = make_tile_plan(T, start_pos, n_q_heads, n_kv_heads).total;
-    return rows > tiles ? rows : tiles;
-}
-
-static int prefill_rows_launch(const void* q, void* out, int T, int start_pos, int n_q_heads, int n_kv_heads,
-                               const void* pool, int n_pages, const int32_t* seq_pages, const float* Pi_k,
-                               const float* Pi_v, const float* centroids, float scale, void* workspace,
-                               size_t workspace_bytes, void* stream) {
-    const PrefillPlan pp = make_prefill_plan(T, start_pos, n_q_heads, n_kv_heads);
-    if (workspace_bytes < pp.total) return LEANKV_EWORKSPACE;
-    char* ws = static_cast<char*>(workspace);
-    int32_t* indptr = reinterpret_cast<int32_t*>(ws + pp.off_indptr);
-    int32_t* last_len = reinterpret_cast<int32_t*>(ws + pp.off_last);
-    int32_t* indices = reinterpret_cast<int32_t*>(ws + pp.off_indices);
-    // Chunks of different lengths lay the workspace out differently, so what one call left in its partial-sum
-    // or table area may lie where this call has its arrival counters: clear them (the status word stays).
-    {
-        const AttnPlan pl = make_plan(T, n_q_heads, n_kv_heads, pp.max_pages);
-        LEANKV_CUDA_TRY(cudaMemsetAsync(ws + pl.off_counters, 0, pl.off_qprime - pl.off_counters,
-                                        static_cast<cudaStream_t>(stream)));
-    }
-    LEANKV_CUDA_TRY(launch_kernel(tq_prefill_tables_kernel, dim3(T), dim3(128), 0,
-                                  static_cast<cudaStream_t>(stream), seq_pages, T, start_pos, indptr, last_len,
-                                  indices));
-    return attn_launch(q, nullptr, out, T, n_q_heads, n_kv_heads, pool, n_pages, indptr, indices, last_len,
-                       pp.max_pages, Pi_k, Pi_v, centroids, scale, workspace, pp.attn_bytes, kAttnRowsFolded, stream);
+    return make_tile_plan(T, start_pos, n_q_heads, n_kv_heads).total;
 }
 
 extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads,
@@ -582,10 +495,6 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
         return LEANKV_EALIGN;
     if (workspace_bytes < leankv_tq_prefill_attn_workspace_bytes(T, start_pos, n_q_heads, n_kv_heads))
         return LEANKV_EWORKSPACE;
-    if (prefill_as_rows())
-        return prefill_rows_launch(q, out, T, start_pos, n_q_heads, n_kv_heads, pool, n_pages, seq_pages, Pi_k,
-                                   Pi_v, centroids, scale, workspace, workspace_bytes, stream);
-
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const TilePlan tp = make_tile_plan(T, start_pos, n_q_heads, n_kv_heads);
     char* ws = static_cast<char*>(workspace);

@@ -87,12 +87,6 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     }
     auto ip = [&](int i) -> int { return small_b ? s_ip[i] : p.indptr[i]; };
     const int ip0 = ip(0);
-    // Rows of q / out that belong to table row b. A prefill chunk lists its tokens folded (first, last,
-    // second, last but one, ...) so that every stretch of the flat page list holds as many short rows as
-    // long ones; everything else uses the identity.
-    auto row_of = [&](int b) -> int {
-        return (p.flags & kAttnRowsFolded) ? ((b & 1) ? p.B - 1 - (b >> 1) : (b >> 1)) : b;
-    };
     long long F = 0, C = 1, f_lo = 0, f_hi = 0;
     bool fits32 = true;
     int b = 0, seq_pg0 = 0, n_b = 0, kvh = 0, pg = 0;
@@ -121,7 +115,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
     for (int bz = blockIdx.x; bz < p.B; bz += gridDim.x) {
         if (ip(bz + 1) - ip(bz) <= 0) {
             if (!waited) { pdl_begin(); waited = true; }
-            __half* o = p.out + (size_t)row_of(bz) * Hq * kDim;
+            __half* o = p.out + (size_t)bz * Hq * kDim;
             for (int i = tid; i < Hq * kDim; i += kAttnThreads) o[i] = __float2half_rn(0.f);
         }
     }
@@ -231,7 +225,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
         float kscale;            // score per integer unit of (256 * HH + MID), before the key norm
         {
             const int head = g & 3;
-            const float* qp = p.qprime + ((size_t)row_of(b) * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
+            const float* qp = p.qprime + ((size_t)b * Hq + (size_t)kvh * kGroup + head) * kDim + 32 * t;
             float4 v[8];
             float amax = 0.f;
 #pragma unroll
@@ -577,7 +571,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             }
             __syncthreads();
             if (warp == 0) {
-                __half* out_base = p.out + ((size_t)row_of(b) * Hq + (size_t)kvh * kGroup) * kDim;
+                __half* out_base = p.out + ((size_t)b * Hq + (size_t)kvh * kGroup) * kDim;
 #pragma unroll
                 for (int h = 0; h < kGroup; ++h) {
                     float4 v = make_float4(r[h][0], r[h][1], r[h][2], r[h][3]);
@@ -703,7 +697,7 @@ __global__ void __launch_bounds__(kAttnThreads, kOcc) tq_decode_attn_kernel(cons
             float v = s_red[h * kCols + c];
 #pragma unroll
             for (int w = 1; w < kAttnWarps; ++w) v += s_red[(w * kGroup + h) * kCols + c];
-            p.out[((size_t)row_of(b) * Hq + (size_t)kvh * kGroup + h) * kDim + crank * kCols + c] = __float2half_rn(v);
+            p.out[((size_t)b * Hq + (size_t)kvh * kGroup + h) * kDim + crank * kCols + c] = __float2half_rn(v);
         }
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
