@@ -12,7 +12,8 @@
 namespace leankv {
 namespace {
 
-// Decode state words (int32, device): see leankv_decode_state_t in the header.
+// Decode state words (int32[8], device), as the header describes them beside leankv_decode_begin: position,
+// step count, and the one-sequence page table (kv_indptr[0..1], kv_last_page_len, start position).
 enum { kPos = 0, kStep = 1, kIndptr0 = 2, kIndptr1 = 3, kLastLen = 4, kStartPos = 5 };
 
 __device__ __forceinline__ float block_sum(float v, float* s_tmp) {

@@ -11,8 +11,14 @@ splits q/k/v/gate/up by output columns and o/down by input rows; the two sums pe
 inside the row-parallel GEMV kernels over peer memory (``LEANKV_TP_EXCHANGE=nccl`` selects a separate
 NCCL all-reduce launch after o_proj and down_proj instead).
 
-Prefill (prompt processing) is dense, like the reference's kernel mode
-(``leankv/teal/patching.py:178-180``): library GEMMs + SDPA over the de-quantized pages.
+Under tensor parallelism the output head is split over the vocabulary and the ranks exchange their
+arg-max inside the step's last kernel.
+
+Prefill (prompt processing) uses dense projections, like the reference's kernel mode
+(``leankv/teal/patching.py:178-180``: library GEMMs), whole or in chunks; every chunk is quantized
+into the pool first and its causal attention then runs on the packed pages
+(``leankv_tq_prefill_attn``), so no fp16 copy of the sequence is ever formed. ``attention="dense"``
+keeps the reference's route (de-quantize + library attention).
 """
 
 from __future__ import annotations
