@@ -873,6 +873,16 @@ def decode_parity(eng, prompt, cfg, dev, world, rank, group, history, tp_steps: 
     out["prefill_packed_vs_dense_attention_rel_l2"] = rel(packed_prefill_logits, eng.prefill_logits.float())
     eng.prefill(prompt, chunk=128)
     out["prefill_chunks_of_128_vs_whole_rel_l2"] = rel(eng.prefill_logits.float(), packed_prefill_logits)
+    # wall time of the prompt pass by route (device-synchronised; library GEMMs for the projections in both)
+    for name, kw in (("packed", {}), ("dense", {"attention": "dense"})):
+        eng.prefill(prompt, **kw)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.prefill(prompt, **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        out[f"prefill_ms_{name}"] = e0.elapsed_time(e1)
     eng.set_thresholds(saved)
     if world == 1:
         return out
@@ -1064,7 +1074,9 @@ def run_ours(args):
                  "parity_note": "logits of the first decode step with TEAL off vs the same step recomputed with library "
                                 "GEMMs and library attention over the de-quantized pool, full model shape",
                  "prefill_packed_vs_dense_attention_rel_l2": parity["prefill_packed_vs_dense_attention_rel_l2"],
-                 "prefill_chunks_of_128_vs_whole_rel_l2": parity["prefill_chunks_of_128_vs_whole_rel_l2"]},
+                 "prefill_chunks_of_128_vs_whole_rel_l2": parity["prefill_chunks_of_128_vs_whole_rel_l2"],
+                 "prefill_ms_packed_pages": parity["prefill_ms_packed"],
+                 "prefill_ms_dequantize_route": parity["prefill_ms_dense"]},
     }
     if world > 1:
         line["tp_parity"] = parity["tp"]

@@ -48,13 +48,14 @@ def optimize_model(model, teal_sparsity: Optional[float] = None,
                    teal_thresholds_path: Optional[str] = None,
                    turboquant_bits: Optional[int] = None, use_paged_cache: bool = False,
                    page_size: int = 16, max_pages: int = 2048, use_triton: bool = False,
-                   fused_attention: bool = False):
+                   fused_attention: bool = False, fused_prefill: bool = False):
     """Apply TEAL and/or build a TurboQuant cache; returns ``(model, cache)``.
 
     ``use_triton`` (an addition: the reference's ``optimize_model`` cannot select its kernel
     path, ``combined.py:83-87``) forwards to ``apply_teal`` and selects the CUDA sparse GEMV.
     ``fused_attention`` (an addition, paged cache only) registers the HF attention function of
-    ``turboquant/hf_attention.py`` so that decode steps of ``model.generate`` run on the packed pages.
+    ``turboquant/hf_attention.py`` so that decode steps of ``model.generate`` run on the packed pages;
+    with ``fused_prefill`` prompt passes do too (causal masks only).
     """
     if teal_sparsity is not None or teal_thresholds_path is not None:
         apply_teal(model, sparsity=teal_sparsity, thresholds_path=teal_thresholds_path,
@@ -79,7 +80,7 @@ def optimize_model(model, teal_sparsity: Optional[float] = None,
         if fused_attention:
             from .turboquant.hf_attention import enable_paged_attention
 
-            enable_paged_attention(model, cache)
+            enable_paged_attention(model, cache, fused_prefill=fused_prefill)
             print("[LeanKV] decode attention runs on the packed pages")
     elif turboquant_bits is not None:
         cache = TurboQuantCache(bits=turboquant_bits, head_dim=head_dim, num_layers=num_layers,

@@ -68,6 +68,8 @@ class PagedKVCache:
         self._free_count = max_pages          # host mirror of the free stack's height
         self._workspace = None
         self.fused_decode = False             # set by hf_attention.enable_paged_attention
+        self.fused_prefill = False            # likewise: prompt passes attend on the packed pages too
+        self._prefill_ws = None
         self._alloc_tables(0)
 
     # ── page table (device) ─────────────────────────────────────────────
@@ -159,9 +161,10 @@ class PagedKVCache:
 
         With ``fused_decode`` set (``hf_attention.enable_paged_attention``) a one-token update only
         appends and hands the new token's own K/V back as a placeholder: the registered attention
-        function answers from the packed pages and never looks at it."""
+        function answers from the packed pages and never looks at it. With ``fused_prefill`` set as
+        well the same holds for prompt chunks (``prefill_attention``)."""
         self.append(layer_idx, key_states, value_states)
-        if self.fused_decode and key_states.shape[2] == 1:
+        if self.fused_decode and (key_states.shape[2] == 1 or self.fused_prefill):
             return key_states, value_states
         return self._gather_kv(layer_idx, key_states.shape[0])
 
@@ -253,17 +256,50 @@ class PagedKVCache:
         _native.check(rc, "leankv_tq_decode_attn")
         return out if query.dtype == torch.float16 else out.to(query.dtype)
 
+    def prefill_attention(self, layer_idx: int, query: torch.Tensor) -> torch.Tensor:
+        """Causal attention of the chunk that ``update`` / ``append`` has just added, over the packed
+        pages of everything up to each token: ``query`` ``[B, Hq, T, D]`` -> ``[B, Hq, T, D]``. The T tokens
+        are the last T of every sequence. Replaces ``update`` (de-quantize the history) + eager attention
+        on a prompt pass (leankv/turboquant/cache.py:136-142)."""
+        _native.require_cuda(query, "query")
+        batch, _, t_new, _ = query.shape
+        lib = _native.lib()
+        out = torch.empty(batch, t_new, self.num_q_heads, self.head_dim, dtype=torch.float16, device=self._device)
+        kq, vq = self.key_quantizers[layer_idx], self.val_quantizers[layer_idx]
+        with torch.cuda.device(self._device):
+            for b in range(batch):
+                n = self._seq_lengths[b]
+                start = n - t_new
+                if start < 0:
+                    raise RuntimeError("prefill_attention: the chunk has not been appended to this sequence")
+                need = lib.leankv_tq_prefill_attn_workspace_bytes(t_new, start, self.num_q_heads, self.num_kv_heads)
+                if self._prefill_ws is None or self._prefill_ws.numel() < need:
+                    self._prefill_ws = torch.zeros(need, dtype=torch.uint8, device=self._device)
+                q = query[b].transpose(0, 1).to(torch.float16).contiguous()          # [T, Hq, D]
+                pages = self._block_table[b, :math.ceil(n / PAGE)]
+                rc = lib.leankv_tq_prefill_attn(
+                    q.data_ptr(), out[b].data_ptr(), t_new, start, self.num_q_heads, self.num_kv_heads,
+                    self.kv_data[layer_idx].data_ptr(), self.max_pages, pages.data_ptr(),
+                    kq._consts()[0].data_ptr(), vq._consts()[0].data_ptr(), self._centroids_host.data_ptr(),
+                    1.0 / math.sqrt(self.head_dim), self._prefill_ws.data_ptr(), self._prefill_ws.numel(),
+                    _native.current_stream())
+                _native.check(rc, "leankv_tq_prefill_attn")
+        out = out.transpose(1, 2)
+        return out if query.dtype == torch.float16 else out.to(query.dtype)
+
     def kernel_status(self) -> int:
-        """Status word of the attention kernel's bounded waits (0 = clean)."""
-        if self._workspace is None:
-            return 0
+        """Status words of the attention kernels' bounded waits, decode and prefill OR-ed (0 = clean)."""
         import ctypes
 
-        val = ctypes.c_int(0)
-        _native.check(_native.lib().leankv_tq_decode_attn_status(self._workspace.data_ptr(),
-                                                                 ctypes.byref(val)),
-                      "leankv_tq_decode_attn_status")
-        return val.value
+        status = 0
+        for ws in (self._workspace, self._prefill_ws):
+            if ws is None:
+                continue
+            val = ctypes.c_int(0)
+            _native.check(_native.lib().leankv_tq_decode_attn_status(ws.data_ptr(), ctypes.byref(val)),
+                          "leankv_tq_decode_attn_status")
+            status |= val.value
+        return status
 
     # ── HF cache surface ───────────────────────────────────────────────
 

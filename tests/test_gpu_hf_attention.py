@@ -62,3 +62,41 @@ def test_fused_decode_matches_dense_route_and_generate_runs(capsys):
     assert cache2.get_seq_length() == 37 + 11
     reset_optimizations(model)
     assert model.config._attn_implementation != "leankv_paged"
+
+
+def test_fused_prefill_runs_prompt_chunks_on_the_packed_pages():
+    """With ``fused_prefill`` a prompt pass only appends and attends on the packed pages: logits of the
+    prompt, of a second chunk fed on top of it, and of decode steps after both, against the dense route."""
+    model = _model()
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, 512, (2, 45), generator=g).to("cuda:0")
+    more = torch.randint(0, 512, (2, 21), generator=g).to("cuda:0")       # a second chunk: starts mid-page
+    forced = [torch.randint(0, 512, (2,), generator=g) for _ in range(4)]
+
+    def run(cache):
+        with torch.no_grad():
+            a = model(ids, past_key_values=cache, use_cache=True).logits.float().cpu()
+            b = model(more, past_key_values=cache, use_cache=True).logits.float().cpu()
+        return [a, b] + _steps_only(model, cache, forced)
+
+    def _steps_only(model, cache, forced):
+        outs = []
+        with torch.no_grad():
+            for tok in forced:
+                outs.append(model(tok.reshape(-1, 1).to("cuda:0"), past_key_values=cache,
+                                  use_cache=True).logits[:, -1].float().cpu())
+        return outs
+
+    _, dense_cache = optimize_model(model, use_paged_cache=True, max_pages=64)
+    want = run(dense_cache)
+    reset_optimizations(model)
+    _, cache = optimize_model(model, use_paged_cache=True, max_pages=64, fused_attention=True, fused_prefill=True)
+    assert cache.fused_prefill
+    got = run(cache)
+    assert cache.kernel_status() == 0
+    errs = [rel_l2(a, b) for a, b in zip(got, want)]
+    print("fused prefill vs dense-route logits rel-L2:", [f"{e:.1e}" for e in errs])
+    assert max(errs) < 1e-2
+    assert cache.get_seq_length() == 45 + 21 + 4
+    reset_optimizations(model)
+    assert not cache.fused_prefill

@@ -145,3 +145,21 @@ def test_mask_that_hides_cached_positions_is_refused():
         hf_attention.paged_attention_forward(M(), q, q, q, additive)
     assert not hf_attention._masks_something(torch.ones(2, 1, 1, 5, dtype=torch.bool))
     assert not hf_attention._masks_something(torch.zeros(2, 1, 1, 5))
+
+
+def test_plain_causal_mask_detection():
+    """The prefill kernel applies the causal mask only; anything that hides more must be told apart."""
+    from leankv_b200.turboquant.hf_attention import _is_plain_causal
+
+    t_q, t_kv = 5, 12
+    i = torch.arange(t_q).unsqueeze(1)
+    j = torch.arange(t_kv).unsqueeze(0)
+    causal = (j <= t_kv - t_q + i).reshape(1, 1, t_q, t_kv)
+    assert _is_plain_causal(causal, t_q)
+    additive = torch.zeros(1, 1, t_q, t_kv).masked_fill(~causal, float("-inf"))
+    assert _is_plain_causal(additive, t_q)
+    padded = causal.clone()
+    padded[..., 0] = False                                   # a left-padded position
+    assert not _is_plain_causal(padded, t_q)
+    window = causal & (j > t_kv - t_q + i - 4).reshape(1, 1, t_q, t_kv)
+    assert not _is_plain_causal(window, t_q)
