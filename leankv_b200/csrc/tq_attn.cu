@@ -516,9 +516,10 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
         attr_done.fetch_or(1ull << dev, std::memory_order_release);
     }
     const int n_vec = T * n_q_heads;
-    const int rot_grid = std::min((n_vec + kRotRows - 1) / kRotRows, sm_count() * 2);
-    LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<true>, dim3(rot_grid), dim3(128), kRotSmemBytes, st, q,
-                                  static_cast<const float*>(nullptr), 0, Pi_k, static_cast<void*>(qprime), n_vec));
+    const int rot_grid = (n_vec + kRotRows - 1) / kRotRows;
+    LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<true>, dim3(rot_grid), dim3(kRotThreads), kRotSmemBytes, st, q,
+                                  static_cast<const float*>(nullptr), 0, Pi_k, static_cast<void*>(qprime), n_vec,
+                                  reinterpret_cast<int*>(ws)));
     PrefillParams p{};
     p.qprime = qprime;
     p.qscale = scale * kLog2e;
@@ -536,9 +537,9 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     p.status = reinterpret_cast<int*>(ws);
     LEANKV_CUDA_TRY(launch_kernel(tq_prefill_attn_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
                                   dim3(kAttnThreads), kPfSmemBytes, st, p));
-    LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<false>, dim3(rot_grid), dim3(128), kRotSmemBytes, st,
+    LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<false>, dim3(rot_grid), dim3(kRotThreads), kRotSmemBytes, st,
                                   static_cast<const void*>(o_part), static_cast<const float*>(ml_part), tp.n_splits,
-                                  Pi_v, out, n_vec));
+                                  Pi_v, out, n_vec, reinterpret_cast<int*>(ws)));
     return LEANKV_OK;
 }
 

@@ -317,169 +317,244 @@ __global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const Pre
     }
 }
 
-// Rotation of many vectors by one 128 x 128 matrix on the tensor cores: the matrix is split into fp16 high
-// and low halves held in shared memory (B operands, via ldmatrix), the vectors likewise (A operands), and
-// out = a_h.M_h + a_h.M_l (+ a_l.M_h when the input is not exactly fp16) with fp32 accumulation: the dropped
-// low x low term is below 2^-22 of |a||M|. A CTA takes 64 vectors at a time, 16 per warp.
+// Rotation of many vectors by one 128 x 128 matrix on the fifth-generation tensor cores (tcgen05): the matrix
+// is split into fp16 high and low halves (B operands), the vectors likewise (A operands), both in shared memory
+// in the blocked K-major layout the MMA's shared-memory descriptors address, and
+//   out = a_h.M_h + a_h.M_l (+ a_l.M_h when the input is not exactly fp16)
+// is accumulated in fp32 in tensor memory: the dropped low x low term is below 2^-22 of |a||M|. A CTA takes 128
+// vectors (M = 128), N = 128, and issues 8 k-steps x 2 or 3 products of tcgen05.mma (128 x 128 x 16) from one
+// elected thread; completion comes back through an mbarrier (tcgen05.commit), the four warps then read
+// their 32 accumulator lanes with tcgen05.ld and store the result.
 //   kForward:  out[v][j] = sum_k M[j][k] * in[v][k]     (query rotation, M = Pi_K; in fp16 (exact), out fp32)
 //   !kForward: out[v][j] = sum_i in[v][i] * M[i][j]     (inverse value rotation, M = Pi_V; in = the page ranges'
 //              partial results of the prefill kernel, merged and normalised here; out fp16)
-constexpr int kRotRows = 64;
+//
+// Blocked K-major layout (no swizzle): element (row, k) of an operand lives at
+//   (row / 8) * kUmmaSbo + (k / 8) * kUmmaLbo + (row % 8) * 16 + (k % 8) * 2   bytes,
+// i.e. 8 x 8 core matrices of 128 contiguous bytes, the 16 core matrices of a row group side by side.
+constexpr int kRotRows = 128;
+constexpr int kRotThreads = 256;
 constexpr int kRotMaxSplits = 8;
-constexpr size_t kRotSmemBytes = (size_t)2 * kDim * kPfStride * 2 + (size_t)2 * kRotRows * kPfStride * 2 +
-                                 (size_t)kRotRows * kRotMaxSplits * sizeof(float);
+constexpr uint32_t kUmmaLbo = 128;                       // next core matrix along K
+constexpr uint32_t kUmmaSbo = (kDim / 8) * 128;          // next group of 8 rows: 2048 bytes
+constexpr uint32_t kUmmaTileBytes = kRotRows * kDim * 2; // one 128 x 128 fp16 operand: 32 KB
+constexpr uint32_t kRotTmemCols = 128;                   // fp32 accumulator: 128 lanes x 128 columns
+// instruction descriptor: D fp32 (bits 4-5 = 1), A and B fp16 (0), both K-major (bits 15, 16 = 0), N / 8 at bit 17,
+// M / 16 at bit 24
+constexpr uint32_t kUmmaIdesc = (1u << 4) | ((uint32_t)(kDim / 8) << 17) | ((uint32_t)(kRotRows / 16) << 24);
+constexpr size_t kRotSmemBytes = 4 * (size_t)kUmmaTileBytes + (size_t)kRotRows * kRotMaxSplits * sizeof(float) + 16;
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    // start address >> 4 (14 bits), leading byte offset >> 4 at bit 16, stride byte offset >> 4 at bit 32,
+    // descriptor version 1 at bit 46, no swizzle (layout type 0 at bit 61)
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(kUmmaLbo >> 4) << 16) |
+           ((uint64_t)(kUmmaSbo >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ uint32_t umma_offset(int row, int k8) {     // byte offset of the 16-byte piece (row, 8 k8 ..)
+    return (uint32_t)(row >> 3) * kUmmaSbo + (uint32_t)k8 * kUmmaLbo + (uint32_t)(row & 7) * 16;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n"
+        :
+        : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kUmmaIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
 
 template <bool kForward>
-__global__ void __launch_bounds__(128) tq_rot_rows_kernel(const void* in, const float* ml_part, int n_splits,
-                                                         const float* M, void* out, int n_vec) {
-    extern __shared__ __align__(128) uint8_t rot_smem[];
-    __half* s_bh = reinterpret_cast<__half*>(rot_smem);          // [n = out coord][k]: high halves of B
-    __half* s_bl = s_bh + kDim * kPfStride;
-    __half* s_ah = s_bl + kDim * kPfStride;                      // [row][k]: high halves of the input rows
-    __half* s_al = s_ah + kRotRows * kPfStride;
-    float* s_w = reinterpret_cast<float*>(s_al + kRotRows * kPfStride);   // [row][range]: merge weights
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
+__global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in, const float* ml_part, int n_splits,
+                                                         const float* M, void* out, int n_vec, int* status) {
+    extern __shared__ __align__(1024) uint8_t rot_smem[];
+    uint8_t* s_bh = rot_smem;                                   // B high halves: [n = out coord][k], blocked
+    uint8_t* s_bl = s_bh + kUmmaTileBytes;
+    uint8_t* s_ah = s_bl + kUmmaTileBytes;                      // A high halves: [row][k], blocked
+    uint8_t* s_al = s_ah + kUmmaTileBytes;
+    float* s_w = reinterpret_cast<float*>(s_al + kUmmaTileBytes);         // [row][range]: merge weights
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_w + kRotRows * kRotMaxSplits);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 1);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int v0 = blockIdx.x * kRotRows;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                     "r"(kRotTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        mbar_init(smem_u32(s_bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     // The matrix is a constant of the cache: stage it before the dependency wait. B[k][n] is M[n][k] for the
     // forward rotation (rows of M as they are) and M[k][n] for the inverse one (transposed copy).
     if (kForward) {
-        for (int i = tid; i < kDim * (kDim / 4); i += 128) {
-            const int r = i / (kDim / 4), c4 = i % (kDim / 4);
-            const float4 w = __ldg(reinterpret_cast<const float4*>(M + (size_t)r * kDim) + c4);
-            const float x[4] = {w.x, w.y, w.z, w.w};
-            __half hi[4], lo[4];
+#pragma unroll 4
+        for (int i = tid; i < kDim * (kDim / 8); i += kRotThreads) {
+            const int n = i / (kDim / 8), k8 = i % (kDim / 8);
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(M + (size_t)n * kDim + 8 * k8));
+            const float4 w1 = __ldg(reinterpret_cast<const float4*>(M + (size_t)n * kDim + 8 * k8) + 1);
+            const float x[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            __half hi[8], lo[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 8; ++e) {
                 hi[e] = __float2half_rn(x[e]);
                 lo[e] = __float2half_rn(x[e] - __half2float(hi[e]));
             }
-            *reinterpret_cast<uint2*>(s_bh + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(hi);
-            *reinterpret_cast<uint2*>(s_bl + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(lo);
+            *reinterpret_cast<uint4*>(s_bh + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(s_bl + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(lo);
         }
     } else {
-        // thread n builds row n of the copy from column n of M (coalesced reads, two k per 32-bit store)
-#pragma unroll 8
-        for (int k2 = 0; k2 < kDim / 2; ++k2) {
-            const float w0 = __ldg(M + (size_t)(2 * k2) * kDim + tid), w1 = __ldg(M + (size_t)(2 * k2 + 1) * kDim + tid);
-            const __half h0 = __float2half_rn(w0), h1 = __float2half_rn(w1);
-            *reinterpret_cast<__half2*>(s_bh + tid * kPfStride + 2 * k2) = __halves2half2(h0, h1);
-            *reinterpret_cast<__half2*>(s_bl + tid * kPfStride + 2 * k2) =
-                __floats2half2_rn(w0 - __half2float(h0), w1 - __half2float(h1));
+        // thread (n, half) builds half of row n of the copy from column n of M (coalesced reads)
+        const int n = tid & (kDim - 1);
+#pragma unroll 2
+        for (int k8 = (tid >> 7) * (kDim / 16); k8 < ((tid >> 7) + 1) * (kDim / 16); ++k8) {
+            __half hi[8], lo[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float w = __ldg(M + (size_t)(8 * k8 + e) * kDim + n);
+                hi[e] = __float2half_rn(w);
+                lo[e] = __float2half_rn(w - __half2float(hi[e]));
+            }
+            *reinterpret_cast<uint4*>(s_bh + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(s_bl + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(lo);
         }
     }
     pdl_begin();
-    const uint32_t b_frag = (uint32_t)((8 * (lane >> 4) + (lane & 7)) * kPfStride + 8 * ((lane >> 3) & 1)) * 2;
-    for (int v0 = blockIdx.x * kRotRows; v0 < n_vec; v0 += gridDim.x * kRotRows) {
-        __syncthreads();                           // the matrix is staged / the previous tile has been consumed
-        // ---- the tile's input rows as fp16 high and low halves ----
-        if (!kForward) {
-            // weights that merge the page ranges' partial results of a row: scale to the common maximum and
-            // divide by the merged denominator (the value norms already carry 1 / alpha); one thread per row
-            if (tid < kRotRows) {
-                const int v = v0 + tid;
-                float mz[kRotMaxSplits], lz[kRotMaxSplits];
-                float m = kNoRef;
+    // ---- the tile's input rows as fp16 high and low halves ----
+    if (!kForward) {
+        // weights that merge the page ranges' partial results of a row: scale to the common maximum and
+        // divide by the merged denominator (the value norms already carry 1 / alpha); one thread per row
+        if (tid < kRotRows) {
+        const int v = v0 + tid;
+        float mz[kRotMaxSplits], lz[kRotMaxSplits];
+        float m = kNoRef;
 #pragma unroll
-                for (int z = 0; z < kRotMaxSplits; ++z) {
-                    mz[z] = kNoRef;
-                    lz[z] = 0.f;
-                    if (z < n_splits && v < n_vec) {
-                        const float2 ml = *reinterpret_cast<const float2*>(ml_part + ((size_t)z * n_vec + v) * 2);
-                        mz[z] = ml.x;
-                        lz[z] = ml.y;
-                    }
-                    m = fmaxf(m, mz[z]);
-                }
-                float l = 0.f;
-#pragma unroll
-                for (int z = 0; z < kRotMaxSplits; ++z) {
-                    mz[z] = ex2_approx(mz[z] - m);
-                    l = fmaf(mz[z], lz[z], l);
-                }
-                const float inv = l > 0.f ? 1.0f / l : 0.f;
-#pragma unroll
-                for (int z = 0; z < kRotMaxSplits; ++z) s_w[tid * kRotMaxSplits + z] = mz[z] * inv;
+        for (int z = 0; z < kRotMaxSplits; ++z) {
+            mz[z] = kNoRef;
+            lz[z] = 0.f;
+            if (z < n_splits && v < n_vec) {
+                const float2 ml = *reinterpret_cast<const float2*>(ml_part + ((size_t)z * n_vec + v) * 2);
+                mz[z] = ml.x;
+                lz[z] = ml.y;
             }
-            __syncthreads();
+            m = fmaxf(m, mz[z]);
         }
-#pragma unroll 4
-        for (int i = tid; i < kRotRows * (kDim / 4); i += 128) {
-            const int r = i / (kDim / 4), c4 = i % (kDim / 4);
-            const int v = v0 + r;
-            float x[4] = {0.f, 0.f, 0.f, 0.f};
+        float l = 0.f;
+#pragma unroll
+        for (int z = 0; z < kRotMaxSplits; ++z) {
+            mz[z] = ex2_approx(mz[z] - m);
+            l = fmaf(mz[z], lz[z], l);
+        }
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+        for (int z = 0; z < kRotMaxSplits; ++z) s_w[tid * kRotMaxSplits + z] = mz[z] * inv;
+        }
+        __syncthreads();
+    }
+#pragma unroll 2
+    for (int i = tid; i < kRotRows * (kDim / 8); i += kRotThreads) {
+        const int r = i / (kDim / 8), k8 = i % (kDim / 8);
+        const int v = v0 + r;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        __half hi[8], lo[8];
+        if (kForward) {
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (v < n_vec) raw = *reinterpret_cast<const uint4*>(static_cast<const __half*>(in) + (size_t)v * kDim + 8 * k8);
+            *reinterpret_cast<uint4*>(s_ah + umma_offset(r, k8)) = raw;          // exact fp16 input: no low half
+        } else {
             if (v < n_vec) {
-                if (kForward) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(in) + (size_t)v * kDim + 4 * c4);
-                    const float2 p0 = h2_to_f2(raw.x), p1 = h2_to_f2(raw.y);
-                    x[0] = p0.x; x[1] = p0.y; x[2] = p1.x; x[3] = p1.y;
-                } else {
-                    const float* o_part = static_cast<const float*>(in);
-                    for (int z = 0; z < n_splits; ++z) {
-                        const float f = s_w[r * kRotMaxSplits + z];
-                        const float4 o = *reinterpret_cast<const float4*>(o_part + ((size_t)z * n_vec + v) * kDim + 4 * c4);
-                        x[0] = fmaf(f, o.x, x[0]); x[1] = fmaf(f, o.y, x[1]);
-                        x[2] = fmaf(f, o.z, x[2]); x[3] = fmaf(f, o.w, x[3]);
-                    }
+                const float* o_part = static_cast<const float*>(in);
+                for (int z = 0; z < n_splits; ++z) {
+                    const float f = s_w[r * kRotMaxSplits + z];
+                    const float4* src = reinterpret_cast<const float4*>(o_part + ((size_t)z * n_vec + v) * kDim + 8 * k8);
+                    const float4 o0 = src[0], o1 = src[1];
+                    x[0] = fmaf(f, o0.x, x[0]); x[1] = fmaf(f, o0.y, x[1]); x[2] = fmaf(f, o0.z, x[2]); x[3] = fmaf(f, o0.w, x[3]);
+                    x[4] = fmaf(f, o1.x, x[4]); x[5] = fmaf(f, o1.y, x[5]); x[6] = fmaf(f, o1.z, x[6]); x[7] = fmaf(f, o1.w, x[7]);
                 }
             }
-            __half hi[4], lo[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 8; ++e) {
                 hi[e] = __float2half_rn(x[e]);
                 lo[e] = __float2half_rn(x[e] - __half2float(hi[e]));
             }
-            *reinterpret_cast<uint2*>(s_ah + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(hi);
-            if (!kForward) *reinterpret_cast<uint2*>(s_al + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(lo);
+            *reinterpret_cast<uint4*>(s_ah + umma_offset(r, k8)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(s_al + umma_offset(r, k8)) = *reinterpret_cast<const uint4*>(lo);
         }
-        __syncthreads();
-        float acc[16][4];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-        const __half* ah_row = s_ah + (16 * warp + g) * kPfStride + 2 * t;
-        const __half* al_row = s_al + (16 * warp + g) * kPfStride + 2 * t;
+    }
+    // make the operands (written through the generic proxy) visible to the tensor core's async proxy
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_tmem);
+
+    if (tid == 0) {
+        const uint32_t ah = smem_u32(s_ah), al = smem_u32(s_al), bh = smem_u32(s_bh), bl = smem_u32(s_bl);
 #pragma unroll
         for (int ks = 0; ks < kDim / 16; ++ks) {
-            uint32_t ah[4], al[4] = {0u, 0u, 0u, 0u};
-            ah[0] = *reinterpret_cast<const uint32_t*>(ah_row + 16 * ks);
-            ah[1] = *reinterpret_cast<const uint32_t*>(ah_row + 8 * kPfStride + 16 * ks);
-            ah[2] = *reinterpret_cast<const uint32_t*>(ah_row + 16 * ks + 8);
-            ah[3] = *reinterpret_cast<const uint32_t*>(ah_row + 8 * kPfStride + 16 * ks + 8);
-            if (!kForward) {
-                al[0] = *reinterpret_cast<const uint32_t*>(al_row + 16 * ks);
-                al[1] = *reinterpret_cast<const uint32_t*>(al_row + 8 * kPfStride + 16 * ks);
-                al[2] = *reinterpret_cast<const uint32_t*>(al_row + 16 * ks + 8);
-                al[3] = *reinterpret_cast<const uint32_t*>(al_row + 8 * kPfStride + 16 * ks + 8);
-            }
+            const uint32_t off = (uint32_t)ks * 2 * kUmmaLbo;          // 16 k = two core matrices along K
+            umma_f16(tmem_base, umma_desc(ah + off), umma_desc(bh + off), ks == 0 ? 0u : 1u);
+            umma_f16(tmem_base, umma_desc(ah + off), umma_desc(bl + off), 1u);
+            if (!kForward) umma_f16(tmem_base, umma_desc(al + off), umma_desc(bh + off), 1u);
+        }
+        // the barrier is arrived on when every MMA issued above has completed
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(s_bar))
+                     : "memory");
+    }
+    const bool done = mbar_wait_bounded(smem_u32(s_bar), 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (done) {
+        // warp w reads accumulator lanes 32 (w % 4) .. + 31 = rows of the tile (the lanes a warp may touch follow
+        // from its index modulo 4); warps 0-3 take columns 0-63, warps 4-7 columns 64-127; 32 columns per load
+        const int lane0 = 32 * (warp & 3);
+        const int v = v0 + lane0 + (tid & 31);
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-                // matrices (n tile j, k low), (j, k high), (j + 1, k low), (j + 1, k high)
-                uint32_t bh[4], bl[4];
-                const uint32_t off = b_frag + (uint32_t)(8 * j * kPfStride + 16 * ks) * 2;
-                ldmatrix_x4(bh, smem_u32(s_bh) + off);
-                ldmatrix_x4(bl, smem_u32(s_bl) + off);
-                mma_16816(acc[j], ah[0], ah[1], ah[2], ah[3], bh[0], bh[1]);
-                mma_16816(acc[j], ah[0], ah[1], ah[2], ah[3], bl[0], bl[1]);
-                mma_16816(acc[j + 1], ah[0], ah[1], ah[2], ah[3], bh[2], bh[3]);
-                mma_16816(acc[j + 1], ah[0], ah[1], ah[2], ah[3], bl[2], bl[3]);
-                if (!kForward) {
-                    mma_16816(acc[j], al[0], al[1], al[2], al[3], bh[0], bh[1]);
-                    mma_16816(acc[j + 1], al[0], al[1], al[2], al[3], bh[2], bh[3]);
+        for (int c0 = (warp >> 2) * (kDim / 2); c0 < ((warp >> 2) + 1) * (kDim / 2); c0 += 32) {
+            uint32_t r[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)lane0 << 16) + (uint32_t)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (v < n_vec) {
+                if (kForward) {
+                    float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + (size_t)v * kDim + c0);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        o[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                } else {
+                    uint4* o = reinterpret_cast<uint4*>(static_cast<__half*>(out) + (size_t)v * kDim + c0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(r[8 * q + 2 * e]), __uint_as_float(r[8 * q + 2 * e + 1]));
+                            pk[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        o[q] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
                 }
             }
         }
-        // rows g and g + 8 of the warp's 16; columns 8 j + 2 t, + 1
-        const int vA = v0 + 16 * warp + g, vB = vA + 8;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            if (kForward) {
-                float* o = static_cast<float*>(out);
-                if (vA < n_vec) *reinterpret_cast<float2*>(o + (size_t)vA * kDim + 8 * j + 2 * t) = make_float2(acc[j][0], acc[j][1]);
-                if (vB < n_vec) *reinterpret_cast<float2*>(o + (size_t)vB * kDim + 8 * j + 2 * t) = make_float2(acc[j][2], acc[j][3]);
-            } else {
-                __half* o = static_cast<__half*>(out);
-                if (vA < n_vec) *reinterpret_cast<__half2*>(o + (size_t)vA * kDim + 8 * j + 2 * t) = __floats2half2_rn(acc[j][0], acc[j][1]);
-                if (vB < n_vec) *reinterpret_cast<__half2*>(o + (size_t)vB * kDim + 8 * j + 2 * t) = __floats2half2_rn(acc[j][2], acc[j][3]);
-            }
-        }
+    } else if (tid == 0) {
+        atomicOr(status, kStatusWaitTimeout);
     }
+    // tensor memory goes back before the CTA exits, whatever happened above
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kRotTmemCols) : "memory");
 }
