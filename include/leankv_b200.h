@@ -181,6 +181,9 @@ int leankv_tq_pool_append(const void* k, const void* v, int B, int n_kv_heads, i
  * stats[0] = coordinates re-derived, stats[1] = coordinates quantized on the current device since
  * the last reset (synchronous copy; reset != 0 clears the counters). */
 int leankv_tq_band_stats(unsigned long long* stats /* host, 2 */, int reset);
+/* *status = 0 unless a bounded wait for the tensor cores inside a multi-token append has ever run out on the
+ * current device (the pages written by that launch are then incomplete). Synchronous copy. */
+int leankv_tq_append_status(int* status /* host */);
 
 /* Pool -> reference format for pages of one sequence: codes as nibble-packed uint8
  * [n_kv_heads][n_tokens][64] and norms fp32 [n_kv_heads][n_tokens] (the fp16 pool

@@ -101,6 +101,7 @@ SIGNATURES = {
     "leankv_decode_end": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "leankv_decode_end_sharded": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                           c_int, c_void_p]),
+    "leankv_tq_append_status": (c_int, [POINTER(c_int)]),
     "leankv_xchg_recv_bytes": (c_size_t, [c_int, c_int, c_int]),
     "leankv_xchg_advance": (c_int, [c_void_p, c_void_p]),
     "leankv_sparse_gemv_allreduce_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,

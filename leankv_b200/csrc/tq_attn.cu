@@ -41,6 +41,7 @@
 
 #include "common.cuh"
 #include "tq_layout.cuh"
+#include "umma.cuh"
 
 namespace leankv {
 namespace {

@@ -329,66 +329,28 @@ __global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const Pre
 //   !kForward: out[v][j] = sum_i in[v][i] * M[i][j]     (inverse value rotation, M = Pi_V; in = the page ranges'
 //              partial results of the prefill kernel, merged and normalised here; out fp16)
 //
-// Blocked K-major layout (no swizzle): element (row, k) of an operand lives at
-//   (row / 8) * kUmmaSbo + (k / 8) * kUmmaLbo + (row % 8) * 16 + (k % 8) * 2   bytes,
-// i.e. 8 x 8 core matrices of 128 contiguous bytes, the 16 core matrices of a row group side by side.
-constexpr int kRotRows = 128;
+// (operand layout and descriptors: umma.cuh)
+constexpr int kRotRows = umma::kRows;
 constexpr int kRotThreads = 256;
 constexpr int kRotMaxSplits = 8;
-constexpr uint32_t kUmmaLbo = 128;                       // next core matrix along K
-constexpr uint32_t kUmmaSbo = (kDim / 8) * 128;          // next group of 8 rows: 2048 bytes
-constexpr uint32_t kUmmaTileBytes = kRotRows * kDim * 2; // one 128 x 128 fp16 operand: 32 KB
-constexpr uint32_t kRotTmemCols = 128;                   // fp32 accumulator: 128 lanes x 128 columns
-// instruction descriptor: D fp32 (bits 4-5 = 1), A and B fp16 (0), both K-major (bits 15, 16 = 0), N / 8 at bit 17,
-// M / 16 at bit 24
-constexpr uint32_t kUmmaIdesc = (1u << 4) | ((uint32_t)(kDim / 8) << 17) | ((uint32_t)(kRotRows / 16) << 24);
-constexpr size_t kRotSmemBytes = 4 * (size_t)kUmmaTileBytes + (size_t)kRotRows * kRotMaxSplits * sizeof(float) + 16;
-
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    // start address >> 4 (14 bits), leading byte offset >> 4 at bit 16, stride byte offset >> 4 at bit 32,
-    // descriptor version 1 at bit 46, no swizzle (layout type 0 at bit 61)
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(kUmmaLbo >> 4) << 16) |
-           ((uint64_t)(kUmmaSbo >> 4) << 32) | (1ull << 46);
-}
-__device__ __forceinline__ uint32_t umma_offset(int row, int k8) {     // byte offset of the 16-byte piece (row, 8 k8 ..)
-    return (uint32_t)(row >> 3) * kUmmaSbo + (uint32_t)k8 * kUmmaLbo + (uint32_t)(row & 7) * 16;
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
-        "}\n"
-        :
-        : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kUmmaIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-        : "memory");
-}
+constexpr size_t kRotSmemBytes = 4 * (size_t)umma::kTileBytes + (size_t)kRotRows * kRotMaxSplits * sizeof(float) + 16;
 
 template <bool kForward>
 __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in, const float* ml_part, int n_splits,
                                                          const float* M, void* out, int n_vec, int* status) {
     extern __shared__ __align__(1024) uint8_t rot_smem[];
     uint8_t* s_bh = rot_smem;                                   // B high halves: [n = out coord][k], blocked
-    uint8_t* s_bl = s_bh + kUmmaTileBytes;
-    uint8_t* s_ah = s_bl + kUmmaTileBytes;                      // A high halves: [row][k], blocked
-    uint8_t* s_al = s_ah + kUmmaTileBytes;
-    float* s_w = reinterpret_cast<float*>(s_al + kUmmaTileBytes);         // [row][range]: merge weights
+    uint8_t* s_bl = s_bh + umma::kTileBytes;
+    uint8_t* s_ah = s_bl + umma::kTileBytes;                      // A high halves: [row][k], blocked
+    uint8_t* s_al = s_ah + umma::kTileBytes;
+    float* s_w = reinterpret_cast<float*>(s_al + umma::kTileBytes);         // [row][range]: merge weights
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_w + kRotRows * kRotMaxSplits);
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 1);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int v0 = blockIdx.x * kRotRows;
 
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
-                     "r"(kRotTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    if (tid == 0) {
-        mbar_init(smem_u32(s_bar), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
+    if (warp == 0) umma::tmem_alloc(smem_u32(s_tmem));
+    if (tid == 0) umma::bar_init(smem_u32(s_bar));
     // The matrix is a constant of the cache: stage it before the dependency wait. B[k][n] is M[n][k] for the
     // forward rotation (rows of M as they are) and M[k][n] for the inverse one (transposed copy).
     if (kForward) {
@@ -404,8 +366,8 @@ __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in
                 hi[e] = __float2half_rn(x[e]);
                 lo[e] = __float2half_rn(x[e] - __half2float(hi[e]));
             }
-            *reinterpret_cast<uint4*>(s_bh + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(hi);
-            *reinterpret_cast<uint4*>(s_bl + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(lo);
+            *reinterpret_cast<uint4*>(s_bh + umma::offset(n, k8)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(s_bl + umma::offset(n, k8)) = *reinterpret_cast<const uint4*>(lo);
         }
     } else {
         // thread (n, half) builds half of row n of the copy from column n of M (coalesced reads)
@@ -419,8 +381,8 @@ __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in
                 hi[e] = __float2half_rn(w);
                 lo[e] = __float2half_rn(w - __half2float(hi[e]));
             }
-            *reinterpret_cast<uint4*>(s_bh + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(hi);
-            *reinterpret_cast<uint4*>(s_bl + umma_offset(n, k8)) = *reinterpret_cast<const uint4*>(lo);
+            *reinterpret_cast<uint4*>(s_bh + umma::offset(n, k8)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(s_bl + umma::offset(n, k8)) = *reinterpret_cast<const uint4*>(lo);
         }
     }
     pdl_begin();
@@ -464,7 +426,7 @@ __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in
         if (kForward) {
             uint4 raw = make_uint4(0u, 0u, 0u, 0u);
             if (v < n_vec) raw = *reinterpret_cast<const uint4*>(static_cast<const __half*>(in) + (size_t)v * kDim + 8 * k8);
-            *reinterpret_cast<uint4*>(s_ah + umma_offset(r, k8)) = raw;          // exact fp16 input: no low half
+            *reinterpret_cast<uint4*>(s_ah + umma::offset(r, k8)) = raw;          // exact fp16 input: no low half
         } else {
             if (v < n_vec) {
                 const float* o_part = static_cast<const float*>(in);
@@ -481,32 +443,31 @@ __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in
                 hi[e] = __float2half_rn(x[e]);
                 lo[e] = __float2half_rn(x[e] - __half2float(hi[e]));
             }
-            *reinterpret_cast<uint4*>(s_ah + umma_offset(r, k8)) = *reinterpret_cast<const uint4*>(hi);
-            *reinterpret_cast<uint4*>(s_al + umma_offset(r, k8)) = *reinterpret_cast<const uint4*>(lo);
+            *reinterpret_cast<uint4*>(s_ah + umma::offset(r, k8)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(s_al + umma::offset(r, k8)) = *reinterpret_cast<const uint4*>(lo);
         }
     }
     // make the operands (written through the generic proxy) visible to the tensor core's async proxy
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    umma::fence_operands();
+    umma::fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    umma::fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_tmem);
 
     if (tid == 0) {
         const uint32_t ah = smem_u32(s_ah), al = smem_u32(s_al), bh = smem_u32(s_bh), bl = smem_u32(s_bl);
 #pragma unroll
         for (int ks = 0; ks < kDim / 16; ++ks) {
-            const uint32_t off = (uint32_t)ks * 2 * kUmmaLbo;          // 16 k = two core matrices along K
-            umma_f16(tmem_base, umma_desc(ah + off), umma_desc(bh + off), ks == 0 ? 0u : 1u);
-            umma_f16(tmem_base, umma_desc(ah + off), umma_desc(bl + off), 1u);
-            if (!kForward) umma_f16(tmem_base, umma_desc(al + off), umma_desc(bh + off), 1u);
+            const uint32_t off = (uint32_t)ks * 2 * umma::kLbo;          // 16 k = two core matrices along K
+            umma::mma_f16(tmem_base, umma::desc(ah + off), umma::desc(bh + off), ks == 0 ? 0u : 1u);
+            umma::mma_f16(tmem_base, umma::desc(ah + off), umma::desc(bl + off), 1u);
+            if (!kForward) umma::mma_f16(tmem_base, umma::desc(al + off), umma::desc(bh + off), 1u);
         }
         // the barrier is arrived on when every MMA issued above has completed
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(s_bar))
-                     : "memory");
+        umma::commit(smem_u32(s_bar));
     }
-    const bool done = mbar_wait_bounded(smem_u32(s_bar), 0);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool done = umma::bar_wait(smem_u32(s_bar), 0);
+    umma::fence_after_sync();
     if (done) {
         // warp w reads accumulator lanes 32 (w % 4) .. + 31 = rows of the tile (the lanes a warp may touch follow
         // from its index modulo 4); warps 0-3 take columns 0-63, warps 4-7 columns 64-127; 32 columns per load
@@ -515,18 +476,7 @@ __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in
 #pragma unroll
         for (int c0 = (warp >> 2) * (kDim / 2); c0 < ((warp >> 2) + 1) * (kDim / 2); c0 += 32) {
             uint32_t r[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)lane0 << 16) + (uint32_t)c0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                : "r"(taddr)
-                : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            umma::ld32(r, tmem_base, lane0, c0);
             if (v < n_vec) {
                 if (kForward) {
                     float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + (size_t)v * kDim + c0);
@@ -553,8 +503,7 @@ __global__ void __launch_bounds__(kRotThreads) tq_rot_rows_kernel(const void* in
         atomicOr(status, kStatusWaitTimeout);
     }
     // tensor memory goes back before the CTA exits, whatever happened above
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    umma::fence_before_sync();
     __syncthreads();
-    if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kRotTmemCols) : "memory");
+    if (warp == 0) umma::tmem_free(tmem_base);
 }

@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "tq_layout.cuh"
+#include "umma.cuh"
 
 namespace leankv {
 namespace {
@@ -355,10 +356,14 @@ __global__ void __launch_bounds__(128) tq_pool_append_kernel(const AppendParams 
 }
 
 #include "tq_append_tc.cuh"
+#include "tq_append_t5.cuh"
 
 // Coordinates decided by the exact chain / coordinates quantized by the tensor-core append, per device,
 // since the last reset (read by leankv_tq_band_stats).
 __device__ unsigned long long g_band_stats[2];
+// Non-zero once a bounded wait for the tensor cores inside the tcgen05 append has run out (per device, sticky;
+// read by leankv_tq_append_status).
+__device__ int g_append_status;
 
 struct UnpackParams {
     const uint8_t* pool;
@@ -394,16 +399,20 @@ __global__ void tq_pool_unpack_kernel(const UnpackParams p) {
     }
 }
 
-// LEANKV_TQ_APPEND=fp32 keeps multi-token appends on the fp32 kernel (the definition the tensor-core
-// path is tested against).
-bool tc_append_enabled() {
+// LEANKV_TQ_APPEND selects the kernel of multi-token appends: "fp32" = the fp32 kernel (the definition the
+// tensor-core paths are tested against), default / "mma" = fast rotation on mma.sync (64-token tiles, two CTAs
+// per SM), "t5" = fast rotation on tcgen05 (128-token tiles, one CTA per SM: measured slower, 1.49 ms against
+// 1.09 ms for a million vectors, because its norm / code / pack phases have no second CTA to overlap with).
+// All three write the same bits.
+int tc_append_mode() {
     static int state = -1;
     if (state < 0) {
         const char* e = std::getenv("LEANKV_TQ_APPEND");
-        state = (e != nullptr && e[0] == 'f') ? 0 : 1;
+        state = e == nullptr ? 1 : (e[0] == 'f' ? 0 : (e[0] == 't' && e[1] == '5' ? 2 : 1));
     }
-    return state == 1;
+    return state;
 }
+bool tc_append_enabled() { return tc_append_mode() != 0; }
 
 int check_tq_common(long long n_vec, int dim, int bits) {
     if (n_vec < 0) return LEANKV_EINVAL;
@@ -525,7 +534,9 @@ extern "C" int leankv_tq_pool_append(const void* k, const void* v, int B, int n_
         // prompt-sized appends: rotation on tensor cores, codes identical to the fp32 kernels
         AppendTcParams tp{};
         tp.a = p;
-        tp.groups = (groups + 3) / 4;
+        const bool t5 = tc_append_mode() == 2;
+        const int pages_per_tile = t5 ? kT5Pages : 4;
+        tp.groups = (groups + pages_per_tile - 1) / pages_per_tile;
         tp.n_tiles = 2LL * B * n_kv_heads * tp.groups;
         void* stats = nullptr;
         LEANKV_CUDA_TRY(cudaGetSymbolAddress(&stats, g_band_stats));
@@ -537,7 +548,18 @@ extern "C" int leankv_tq_pool_append(const void* k, const void* v, int B, int n_
         if (dev < 0 || dev >= kMaxDevices || !attr_done[dev]) {
             LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_pool_append_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)kTcSmemBytes));
+            LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_pool_append_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)kT5SmemBytes));
             if (dev >= 0 && dev < kMaxDevices) attr_done[dev] = true;
+        }
+        if (t5) {
+            void* st_word = nullptr;
+            LEANKV_CUDA_TRY(cudaGetSymbolAddress(&st_word, g_append_status));
+            const long long slots1 = sm_count();            // 148 KB of shared memory: one CTA per SM
+            const int grid_t5 = (int)(tp.n_tiles < slots1 ? tp.n_tiles : slots1);
+            LEANKV_CUDA_TRY(launch_kernel(tq_pool_append_t5_kernel, dim3(grid_t5), dim3(kT5Threads), kT5SmemBytes,
+                                          static_cast<cudaStream_t>(stream), tp, static_cast<int*>(st_word)));
+            return LEANKV_OK;
         }
         const long long slots = 2LL * sm_count();
         const int grid_tc = (int)(tp.n_tiles < slots ? tp.n_tiles : slots);
@@ -575,6 +597,12 @@ extern "C" int leankv_tq_pool_unpack(const void* pool, int n_pages, int n_kv_hea
     if (blocks > sm_count() * 16LL) blocks = sm_count() * 16LL;
     tq_pool_unpack_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     LEANKV_CUDA_TRY(cudaGetLastError());
+    return LEANKV_OK;
+}
+
+extern "C" int leankv_tq_append_status(int* status /* host */) {
+    if (!status) return LEANKV_EINVAL;
+    LEANKV_CUDA_TRY(cudaMemcpyFromSymbol(status, g_append_status, sizeof(int)));
     return LEANKV_OK;
 }
 

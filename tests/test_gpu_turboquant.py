@@ -467,14 +467,16 @@ for t0, t1 in ((0, 1000), (1000, T)):
 torch.cuda.synchronize()
 stats = (ctypes.c_ulonglong * 2)()
 lib.leankv_tq_band_stats(stats, 0)
-print("POOL", hashlib.sha256(pool.cpu().numpy().tobytes()).hexdigest(), stats[0], stats[1])
+st = ctypes.c_int(0)
+lib.leankv_tq_append_status(ctypes.byref(st))
+print("POOL", hashlib.sha256(pool.cpu().numpy().tobytes()).hexdigest(), stats[0], stats[1], st.value)
 """
 
 
 def test_tensor_core_append_writes_the_same_pool_as_the_fp32_kernel_on_all_of_config3():
     """All 16 sequences x 8 heads x 4096 tokens, K and V (134 M coordinates), appended in two launches:
-    the pool written with the rotation on tensor cores must equal, byte for byte, the pool written by the
-    sequential-fma fp32 kernel that defines the codes. Each path runs in a process of its own (the path is
+    the pools written with the rotation on tensor cores (tcgen05 and mma.sync variants) must equal, byte for
+    byte, the pool written by the sequential-fma fp32 kernel that defines the codes. Each path runs in a process of its own (the path is
     chosen once per process by LEANKV_TQ_APPEND)."""
     import os
     import subprocess
@@ -483,17 +485,20 @@ def test_tensor_core_append_writes_the_same_pool_as_the_fp32_kernel_on_all_of_co
     from conftest import ROOT
 
     out = {}
-    for mode in ("tc", "fp32"):
+    for mode in ("t5", "mma", "fp32"):
         env = dict(os.environ, LEANKV_TQ_APPEND=mode)
         r = subprocess.run([sys.executable, "-c", _POOL_HASH_SNIPPET % {"root": ROOT}], env=env,
                            capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         line = [ln for ln in r.stdout.splitlines() if ln.startswith("POOL")][-1].split()
-        out[mode] = (line[1], int(line[2]), int(line[3]))
-    print("tensor-core append: coordinates re-derived exactly / quantized:", out["tc"][1], "/", out["tc"][2])
-    assert out["tc"][0] == out["fp32"][0]
-    assert out["tc"][2] == 2 * 16 * 8 * 4096 * 128 and out["fp32"][2] == 0
-    assert 0 < out["tc"][1] < 0.02 * out["tc"][2]
+        out[mode] = (line[1], int(line[2]), int(line[3]), int(line[4]))
+    for mode in ("t5", "mma"):          # rotation on tcgen05 (128-token tiles) / on mma.sync (64-token tiles)
+        print(mode, "append: coordinates re-derived exactly / quantized:", out[mode][1], "/", out[mode][2])
+        assert out[mode][0] == out["fp32"][0], mode
+        assert out[mode][2] == 2 * 16 * 8 * 4096 * 128
+        assert 0 < out[mode][1] < 0.02 * out[mode][2]
+        assert out[mode][3] == 0                       # no bounded wait ran out
+    assert out["fp32"][2] == 0
 
 
 def test_paged_cache_page_table_on_device_follows_the_reference_allocator():
