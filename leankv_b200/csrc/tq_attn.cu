@@ -458,7 +458,7 @@ struct TilePlan {
 static TilePlan make_tile_plan(int T, int start_pos, int Hq, int Hkv) {
     TilePlan tp;
     tp.n_tiles = (T + kPfTokens - 1) / kPfTokens;
-    const long long ctas = (long long)tp.n_tiles * Hkv, slots = (long long)sm_count() * 3;
+    const long long ctas = (long long)tp.n_tiles * Hkv, slots = (long long)sm_count() * 2;
     long long s = ((long long)start_pos + T + kPage - 1) / kPage / 16;
     if (ctas >= 4 * slots) s = 1;
     if (s > 8) s = 8;

@@ -1,14 +1,15 @@
 // Causal attention of a chunk of prompt tokens over the packed pages, one query tile per CTA
 // (included by tq_attn.cu, inside namespace leankv::{anonymous}).
 //
-// A CTA takes 16 consecutive query tokens of one kv head: 64 rows (token, GQA head), 16 per warp.
+// A CTA takes 32 consecutive query tokens of one kv head: 128 rows (token, GQA head), two 16-row MMA tiles per
+// warp, which share every K / V operand fragment.
 // It walks the sequence's pages up to the tile's last token; each page is fetched once (bulk copy,
 // ring of 3), de-quantized once into shared memory as fp16 operands by the 128 threads (one 32-code
 // unit each, the same byte-permute look-ups as the decode kernel) and then used by all four warps:
-//   scores  S[16 rows][16 tokens] = Q''[16][128] . Khat^T    (mma.m16n8k16, Q'' = hi + lo fp16 halves
+//   scores  S[32 rows][16 tokens] = Q''[32][128] . Khat^T    (mma.m16n8k16, Q'' = hi + lo fp16 halves
 //                                                             of the rotated, pre-scaled query)
-//   output  O[16 rows][128]      += P[16][16] . Vhat[16][128] (probabilities times value norms in fp16)
-// with the usual online softmax per row in registers. So a page costs one de-quantization per 16
+//   output  O[32 rows][128]      += P[32][16] . Vhat[16][128] (probabilities times value norms in fp16)
+// with the usual online softmax per row in registers. So a page costs one de-quantization per 32
 // query tokens instead of one per token, which is what the decode kernel run on prompt rows pays.
 // When a tile has many pages they are cut into ranges handled by separate CTAs (grid z). Each CTA leaves its
 // partial result in the rotated space (fp32 sums, maximum, denominator); tq_rot_rows_kernel<false> merges the
@@ -29,8 +30,9 @@ struct PrefillParams {
     int* status;
 };
 
-constexpr int kPfTokens = 16;                  // query tokens per CTA
-constexpr int kPfRows = kPfTokens * kGroup;    // 64 rows
+constexpr int kPfMt = 2;                       // 16-row MMA tiles per warp
+constexpr int kPfTokens = 4 * 4 * kPfMt;       // query tokens per CTA: 4 warps x 4 tokens per tile x tiles
+constexpr int kPfRows = kPfTokens * kGroup;    // 128 rows (token, GQA head)
 constexpr int kPfStride = kDim + 8;            // halfs per row of the Q / K tiles (bank-conflict-free fragments)
 constexpr int kPfVtStride = 24;                // halfs per row of the transposed V tile (16 tokens + padding)
 constexpr int kPfStages = 3;
@@ -47,7 +49,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
                  : "r"(addr));
 }
 
-__global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_attn_kernel(const PrefillParams p) {
     extern __shared__ __align__(128) uint8_t pf_smem[];
     uint8_t* s_raw = pf_smem;                                                   // [stages][K chunk | V chunk]
     __half* s_qh = reinterpret_cast<__half*>(s_raw + kPfStages * 2 * kChunkBytes);
@@ -118,31 +120,25 @@ __global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const Pre
         *reinterpret_cast<uint2*>(s_ql + r * kPfStride + 4 * c4) = *reinterpret_cast<const uint2*>(lo);
     }
 
-    // this lane's two rows of the warp's 16: (token, head) of rows g and g + 8
-    const int qpos0 = p.start_pos + tok0 + 4 * warp + (g >> 2);          // position of row g's token
-    const int qpos1 = qpos0 + 2;                                         // row g + 8: two tokens further
-    float m0 = kNoRef, m1 = kNoRef, l0 = 0.f, l1 = 0.f;
-    float acc[16][4];
+    // The warp's rows: kPfMt tiles of 16 (token, head) rows, 4 tokens each; this lane holds rows g and g + 8 of
+    // every tile. Tile mt covers tokens tok0 + 4 * (kPfMt * warp + mt) .. + 3.
+    int qpos[kPfMt][2];
+    float m_run[kPfMt][2], l_run[kPfMt][2];
+    float acc[kPfMt][16][4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    __syncthreads();                                                     // the query tile is in shared memory
-    // the warp's query rows as A operands, held in registers for the whole page loop
-    uint32_t qa_h[kDim / 16][4], qa_l[kDim / 16][4];
-    {
-        const __half* qh_row0 = s_qh + (16 * warp + g) * kPfStride + 2 * t;
-        const __half* ql_row0 = s_ql + (16 * warp + g) * kPfStride + 2 * t;
+    for (int mt = 0; mt < kPfMt; ++mt) {
+        qpos[mt][0] = p.start_pos + tok0 + 4 * (kPfMt * warp + mt) + (g >> 2);   // position of row g's token
+        qpos[mt][1] = qpos[mt][0] + 2;                                           // row g + 8: two tokens further
+        m_run[mt][0] = m_run[mt][1] = kNoRef;
+        l_run[mt][0] = l_run[mt][1] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < kDim / 16; ++ks) {
-            qa_h[ks][0] = *reinterpret_cast<const uint32_t*>(qh_row0 + 16 * ks);
-            qa_h[ks][1] = *reinterpret_cast<const uint32_t*>(qh_row0 + 8 * kPfStride + 16 * ks);
-            qa_h[ks][2] = *reinterpret_cast<const uint32_t*>(qh_row0 + 16 * ks + 8);
-            qa_h[ks][3] = *reinterpret_cast<const uint32_t*>(qh_row0 + 8 * kPfStride + 16 * ks + 8);
-            qa_l[ks][0] = *reinterpret_cast<const uint32_t*>(ql_row0 + 16 * ks);
-            qa_l[ks][1] = *reinterpret_cast<const uint32_t*>(ql_row0 + 8 * kPfStride + 16 * ks);
-            qa_l[ks][2] = *reinterpret_cast<const uint32_t*>(ql_row0 + 16 * ks + 8);
-            qa_l[ks][3] = *reinterpret_cast<const uint32_t*>(ql_row0 + 8 * kPfStride + 16 * ks + 8);
-        }
+        for (int j = 0; j < 16; ++j) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
     }
+    __syncthreads();                                                     // the query tile is in shared memory
+    // A fragments come from shared memory every page (ldmatrix.x4: rows 0-7 / 8-15 x k low / high of a tile)
+    const uint32_t q_frag_off =
+        (uint32_t)(((16 * kPfMt * warp + 8 * ((lane >> 3) & 1) + (lane & 7)) * kPfStride + 8 * (lane >> 4)) * 2);
+    const uint32_t qh_frag = smem_u32(s_qh) + q_frag_off, ql_frag = smem_u32(s_ql) + q_frag_off;
     // ldmatrix row addresses of this lane (bytes, shared window): matrix L >> 3, row L & 7
     const uint32_t k_frag_addr =
         smem_u32(s_k + (8 * (lane >> 4) + (lane & 7)) * kPfStride + 8 * ((lane >> 3) & 1));
@@ -207,81 +203,97 @@ __global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const Pre
         const uint32_t k_frag = k_frag_addr + (uint32_t)(buf * kKTile * 2);
         const uint32_t v_frag = v_frag_addr + (uint32_t)(buf * kVTile * 2);
 
-        // ---- scores of this warp's 16 rows against the page's 16 tokens ----
-        float sc[2][4];
+        // ---- scores of this warp's rows against the page's 16 tokens ----
+        float sc[kPfMt][2][4];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+        for (int mt = 0; mt < kPfMt; ++mt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) sc[mt][j][0] = sc[mt][j][1] = sc[mt][j][2] = sc[mt][j][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < kDim / 16; ++ks) {
             // one ldmatrix brings the B fragments of both token tiles: matrices (tile 0, k low), (tile 0, k high),
-            // (tile 1, k low), (tile 1, k high); lane L supplies row L & 7 of matrix L >> 3
+            // (tile 1, k low), (tile 1, k high); lane L supplies row L & 7 of matrix L >> 3. They serve every
+            // row tile of the warp.
             uint32_t kb[4];
             ldmatrix_x4(kb, k_frag + 2 * 16 * ks);
-            mma_16816(sc[0], qa_h[ks][0], qa_h[ks][1], qa_h[ks][2], qa_h[ks][3], kb[0], kb[1]);
-            mma_16816(sc[0], qa_l[ks][0], qa_l[ks][1], qa_l[ks][2], qa_l[ks][3], kb[0], kb[1]);
-            mma_16816(sc[1], qa_h[ks][0], qa_h[ks][1], qa_h[ks][2], qa_h[ks][3], kb[2], kb[3]);
-            mma_16816(sc[1], qa_l[ks][0], qa_l[ks][1], qa_l[ks][2], qa_l[ks][3], kb[2], kb[3]);
+#pragma unroll
+            for (int mt = 0; mt < kPfMt; ++mt) {
+                uint32_t ah[4], al[4];
+                ldmatrix_x4(ah, qh_frag + (uint32_t)((16 * mt * kPfStride + 16 * ks) * 2));
+                ldmatrix_x4(al, ql_frag + (uint32_t)((16 * mt * kPfStride + 16 * ks) * 2));
+                mma_16816(sc[mt][0], ah[0], ah[1], ah[2], ah[3], kb[0], kb[1]);
+                mma_16816(sc[mt][0], al[0], al[1], al[2], al[3], kb[0], kb[1]);
+                mma_16816(sc[mt][1], ah[0], ah[1], ah[2], ah[3], kb[2], kb[3]);
+                mma_16816(sc[mt][1], al[0], al[1], al[2], al[3], kb[2], kb[3]);
+            }
         }
-        // key norm, causal mask (key position <= query position; every such position holds a token)
         const int kbase = (pg_lo + pg) * kPage;
-        float rmax0 = kNoRef, rmax1 = kNoRef;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int tok = 8 * j + 2 * t + c;
-                const float knt = kn[tok];
-                const float v0 = kbase + tok <= qpos0 ? sc[j][c] * knt : kNoRef;
-                const float v1 = kbase + tok <= qpos1 ? sc[j][2 + c] * knt : kNoRef;
-                sc[j][c] = v0;
-                sc[j][2 + c] = v1;
-                rmax0 = fmaxf(rmax0, v0);
-                rmax1 = fmaxf(rmax1, v1);
-            }
-        }
-        rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 1));
-        rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 2));
-        rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 1));
-        rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 2));
-        const float mn0 = fmaxf(m0, rmax0), mn1 = fmaxf(m1, rmax1);
-        const float f0 = ex2_approx(m0 - mn0), f1 = ex2_approx(m1 - mn1);
-        m0 = mn0;
-        m1 = mn1;
-        // probabilities; a masked entry is exactly 0 (kNoRef - m underflows), also while a row has seen nothing
-        float pr[2][4];
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                pr[j][c] = sc[j][c] > 0.5f * kNoRef ? ex2_approx(sc[j][c] - m0) : 0.f;
-                pr[j][2 + c] = sc[j][2 + c] > 0.5f * kNoRef ? ex2_approx(sc[j][2 + c] - m1) : 0.f;
-                sum0 += pr[j][c];
-                sum1 += pr[j][2 + c];
-            }
-        }
-        l0 = l0 * f0 + sum0;                     // per-lane partial sums; the quad is added up at the end
-        l1 = l1 * f1 + sum1;
-        if (__any_sync(0xffffffffu, f0 != 1.0f || f1 != 1.0f)) {          // a row's maximum moved: rescale its sums
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                acc[j][0] *= f0; acc[j][1] *= f0;
-                acc[j][2] *= f1; acc[j][3] *= f1;
-            }
-        }
-        // P (times value norm / alpha) as the A operand: tokens 2t, 2t+1 (tile 0) and 2t+8, 2t+9 (tile 1)
         const float vn0 = vn[2 * t], vn1 = vn[2 * t + 1], vn8 = vn[2 * t + 8], vn9 = vn[2 * t + 9];
-        const uint32_t a0 = pack_h2(pr[0][0] * vn0, pr[0][1] * vn1);
-        const uint32_t a1 = pack_h2(pr[0][2] * vn0, pr[0][3] * vn1);
-        const uint32_t a2 = pack_h2(pr[1][0] * vn8, pr[1][1] * vn9);
-        const uint32_t a3 = pack_h2(pr[1][2] * vn8, pr[1][3] * vn9);
+        uint32_t pa[kPfMt][4];                  // P (times value norm / alpha) as A operands
+#pragma unroll
+        for (int mt = 0; mt < kPfMt; ++mt) {
+            // key norm, causal mask (key position <= query position; every such position holds a token)
+            float rmax0 = kNoRef, rmax1 = kNoRef;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int tok = 8 * j + 2 * t + c;
+                    const float knt = kn[tok];
+                    const float v0 = kbase + tok <= qpos[mt][0] ? sc[mt][j][c] * knt : kNoRef;
+                    const float v1 = kbase + tok <= qpos[mt][1] ? sc[mt][j][2 + c] * knt : kNoRef;
+                    sc[mt][j][c] = v0;
+                    sc[mt][j][2 + c] = v1;
+                    rmax0 = fmaxf(rmax0, v0);
+                    rmax1 = fmaxf(rmax1, v1);
+                }
+            }
+            rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 1));
+            rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 2));
+            rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 1));
+            rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 2));
+            const float mn0 = fmaxf(m_run[mt][0], rmax0), mn1 = fmaxf(m_run[mt][1], rmax1);
+            const float f0 = ex2_approx(m_run[mt][0] - mn0), f1 = ex2_approx(m_run[mt][1] - mn1);
+            m_run[mt][0] = mn0;
+            m_run[mt][1] = mn1;
+            // probabilities; a masked entry is exactly 0, also while a row has seen nothing
+            float pr[2][4];
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    pr[j][c] = sc[mt][j][c] > 0.5f * kNoRef ? ex2_approx(sc[mt][j][c] - mn0) : 0.f;
+                    pr[j][2 + c] = sc[mt][j][2 + c] > 0.5f * kNoRef ? ex2_approx(sc[mt][j][2 + c] - mn1) : 0.f;
+                    sum0 += pr[j][c];
+                    sum1 += pr[j][2 + c];
+                }
+            }
+            l_run[mt][0] = l_run[mt][0] * f0 + sum0;   // per-lane partial sums; the quad is added up at the end
+            l_run[mt][1] = l_run[mt][1] * f1 + sum1;
+            if (__any_sync(0xffffffffu, f0 != 1.0f || f1 != 1.0f)) {      // a row's maximum moved: rescale its sums
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    acc[mt][j][0] *= f0; acc[mt][j][1] *= f0;
+                    acc[mt][j][2] *= f1; acc[mt][j][3] *= f1;
+                }
+            }
+            // tokens 2t, 2t+1 (tile 0) and 2t+8, 2t+9 (tile 1)
+            pa[mt][0] = pack_h2(pr[0][0] * vn0, pr[0][1] * vn1);
+            pa[mt][1] = pack_h2(pr[0][2] * vn0, pr[0][3] * vn1);
+            pa[mt][2] = pack_h2(pr[1][0] * vn8, pr[1][1] * vn9);
+            pa[mt][3] = pack_h2(pr[1][2] * vn8, pr[1][3] * vn9);
+        }
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
             // matrices (coords 8j.., tokens 0-7), (8j.., tokens 8-15), (8(j+1).., 0-7), (8(j+1).., 8-15)
             uint32_t vb[4];
             ldmatrix_x4(vb, v_frag + 2 * 8 * j * kPfVtStride);
-            mma_16816(acc[j], a0, a1, a2, a3, vb[0], vb[1]);
-            mma_16816(acc[j + 1], a0, a1, a2, a3, vb[2], vb[3]);
+#pragma unroll
+            for (int mt = 0; mt < kPfMt; ++mt) {
+                mma_16816(acc[mt][j], pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], vb[0], vb[1]);
+                mma_16816(acc[mt][j + 1], pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], vb[2], vb[3]);
+            }
         }
         if (pg + 1 < n_pg) got = dequant(pg + 1);        // into the other buffer, while slower warps finish page pg
     }
@@ -297,23 +309,30 @@ __global__ void __launch_bounds__(kAttnThreads) tq_prefill_attn_kernel(const Pre
     }
 
     // ---- this range's partial result, in the rotated space: sums, running maximum, denominator ----
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const int tokA = tok0 + 4 * warp + (g >> 2), tokB = tokA + 2, head = g & 3;
     const size_t n_vec = (size_t)p.T * Hq;
-    const size_t vA = (size_t)tokA * Hq + (size_t)kvh * kGroup + head, vB = (size_t)tokB * Hq + (size_t)kvh * kGroup + head;
-    float* oA = p.o_part + ((size_t)blockIdx.z * n_vec + vA) * kDim + 2 * t;
-    float* oB = p.o_part + ((size_t)blockIdx.z * n_vec + vB) * kDim + 2 * t;
+    const int head = g & 3;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        if (tokA < p.T) *reinterpret_cast<float2*>(oA + 8 * j) = make_float2(acc[j][0], acc[j][1]);
-        if (tokB < p.T) *reinterpret_cast<float2*>(oB + 8 * j) = make_float2(acc[j][2], acc[j][3]);
-    }
-    if (t == 0) {
-        if (tokA < p.T) *reinterpret_cast<float2*>(p.ml_part + ((size_t)blockIdx.z * n_vec + vA) * 2) = make_float2(m0, l0);
-        if (tokB < p.T) *reinterpret_cast<float2*>(p.ml_part + ((size_t)blockIdx.z * n_vec + vB) * 2) = make_float2(m1, l1);
+    for (int mt = 0; mt < kPfMt; ++mt) {
+        float l0 = l_run[mt][0], l1 = l_run[mt][1];
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const int tokA = tok0 + 4 * (kPfMt * warp + mt) + (g >> 2), tokB = tokA + 2;
+        const size_t vA = (size_t)tokA * Hq + (size_t)kvh * kGroup + head, vB = (size_t)tokB * Hq + (size_t)kvh * kGroup + head;
+        float* oA = p.o_part + ((size_t)blockIdx.z * n_vec + vA) * kDim + 2 * t;
+        float* oB = p.o_part + ((size_t)blockIdx.z * n_vec + vB) * kDim + 2 * t;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (tokA < p.T) *reinterpret_cast<float2*>(oA + 8 * j) = make_float2(acc[mt][j][0], acc[mt][j][1]);
+            if (tokB < p.T) *reinterpret_cast<float2*>(oB + 8 * j) = make_float2(acc[mt][j][2], acc[mt][j][3]);
+        }
+        if (t == 0) {
+            if (tokA < p.T)
+                *reinterpret_cast<float2*>(p.ml_part + ((size_t)blockIdx.z * n_vec + vA) * 2) = make_float2(m_run[mt][0], l0);
+            if (tokB < p.T)
+                *reinterpret_cast<float2*>(p.ml_part + ((size_t)blockIdx.z * n_vec + vB) * 2) = make_float2(m_run[mt][1], l1);
+        }
     }
 }
 
