@@ -250,13 +250,16 @@ int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
  * keys and values only, and never to an fp16 copy. Replaces, for prompt chunks, cache.update +
  * eager attention (leankv/turboquant/cache.py:136-142, transformers modeling_mistral.py:96-117).
  * q, out: [T][n_q_heads][128] fp16. seq_pages (device): the sequence's page ids in order, at least
- * (start_pos + T + 15) / 16 of them. Three launches: the query rotation (tensor cores, fp16 high/low split
- * of Pi_K), the attention kernel (one CTA per 16 query tokens, kv head and page range: a page is
- * de-quantized once per 16 tokens into fp16 operand tiles; scores and the value sum on tensor cores with the
- * query as fp16 high + low halves and fp32 accumulation), and the merge of the page ranges with the inverse
- * value rotation. The result agrees with decode steps at the same positions to fp16 rounding (rel-L2 < 5e-4
- * in the tests). The workspace's first word is the status word and must be zero before the first use; the
- * rest needs no preparation and one workspace may serve chunks of any length. */
+ * (start_pos + T + 15) / 16 of them. Three launches: the query rotation (tcgen05 tensor cores, fp16
+ * high/low split of Pi_K), the attention kernel (one CTA per 32 query tokens, kv head and page range: a
+ * page is de-quantized once per 32 tokens into fp16 operand tiles; scores and the value sum on tensor cores
+ * with the query as fp16 high + low halves and fp32 accumulation: tcgen05.mma with the accumulators in
+ * tensor memory by default, mma.sync when the environment has LEANKV_PREFILL_MMA=sync), and the merge of
+ * the page ranges with the inverse value rotation. The result agrees with decode steps at the same
+ * positions to fp16 rounding (rel-L2 < 5e-4 in the tests). The workspace's first word is the status word
+ * and must be zero before the first use (bit 0: a bounded wait ran out, bit 1: a page id out of range;
+ * with bit 0, bits 4..6 say which wait: page copy, score MMAs, value MMAs); the rest needs no preparation
+ * and one workspace may serve chunks of any length. */
 size_t leankv_tq_prefill_attn_workspace_bytes(int T, int start_pos, int n_q_heads, int n_kv_heads);
 int leankv_tq_prefill_attn(const void* q, void* out, int T, int start_pos, int n_q_heads, int n_kv_heads,
                            const void* pool, int n_pages, const int32_t* seq_pages, const float* Pi_k,

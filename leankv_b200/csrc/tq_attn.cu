@@ -448,6 +448,16 @@ static long long prefill_rows_pages(long long first_pos, long long n) {
     return upto(first_pos + n) - upto(first_pos);
 }
 
+// LEANKV_PREFILL_MMA=sync keeps the prefill attention's two products on mma.sync; default: tcgen05.
+static bool prefill_on_tcgen05() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("LEANKV_PREFILL_MMA");
+        v = (e != nullptr && e[0] == 's') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 struct TilePlan {
     int n_tiles, n_splits;
     size_t off_qprime, off_opart, off_ml, total;
@@ -510,6 +520,8 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     if (((attr_done.load(std::memory_order_acquire) >> dev) & 1ull) == 0) {
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kPfSmemBytes));
+        LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_prefill_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kT5SmemBytes));
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_rot_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kRotSmemBytes));
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_rot_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -536,8 +548,12 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     p.tl0 = lut.tl0; p.tl1 = lut.tl1; p.th0 = lut.th0; p.th1 = lut.th1;
     p.inv_alpha = 1.0f / lut.alpha;
     p.status = reinterpret_cast<int*>(ws);
-    LEANKV_CUDA_TRY(launch_kernel(tq_prefill_attn_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
-                                  dim3(kAttnThreads), kPfSmemBytes, st, p));
+    if (prefill_on_tcgen05())
+        LEANKV_CUDA_TRY(launch_kernel(tq_prefill_t5_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
+                                      dim3(kAttnThreads), kT5SmemBytes, st, p));
+    else
+        LEANKV_CUDA_TRY(launch_kernel(tq_prefill_attn_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
+                                      dim3(kAttnThreads), kPfSmemBytes, st, p));
     LEANKV_CUDA_TRY(launch_kernel(tq_rot_rows_kernel<false>, dim3(rot_grid), dim3(kRotThreads), kRotSmemBytes, st,
                                   static_cast<const void*>(o_part), static_cast<const float*>(ml_part), tp.n_splits,
                                   Pi_v, out, n_vec, reinterpret_cast<int*>(ws)));

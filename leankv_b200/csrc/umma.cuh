@@ -81,6 +81,54 @@ __device__ __forceinline__ void ld32(uint32_t (&r)[32], uint32_t tmem_base, int 
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- the same with explicit tile geometry (operands whose K extent is not 128, N other than 128) ----
+// K-major blocked operand with `k_chunks` 16-byte pieces per row: core matrices of a row group side by side
+// (leading byte offset 128), row groups k_chunks * 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_k(uint32_t addr, int k_chunks) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(kLbo >> 4) << 16) |
+           ((uint64_t)(((uint32_t)k_chunks * 128u) >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ uint32_t offset_k(int row, int k8, int k_chunks) {
+    return (uint32_t)(row >> 3) * (uint32_t)k_chunks * 128u + (uint32_t)k8 * kLbo + (uint32_t)(row & 7) * 16;
+}
+// instruction descriptor for D fp32 = A fp16 . B fp16, both K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t idesc_n(int n) { return (1u << 4) | ((uint32_t)(n / 8) << 17) | ((uint32_t)(kRows / 16) << 24); }
+__device__ __forceinline__ void mma_f16_n(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n"
+        :
+        : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_n(uint32_t slot_addr, uint32_t n_cols) {      // n_cols: power of two >= 32
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(n_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free_n(uint32_t tmem_base, uint32_t n_cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(n_cols) : "memory");
+}
+// 32 consecutive accumulator columns of this thread's lane, written back
+__device__ __forceinline__ void st32(const uint32_t (&r)[32], uint32_t tmem_base, int lane0, int col0) {
+    const uint32_t taddr = tmem_base + ((uint32_t)lane0 << 16) + (uint32_t)col0;
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void bar_init(uint32_t bar) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
