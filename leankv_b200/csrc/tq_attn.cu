@@ -550,7 +550,7 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     p.status = reinterpret_cast<int*>(ws);
     if (prefill_on_tcgen05())
         LEANKV_CUDA_TRY(launch_kernel(tq_prefill_t5_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
-                                      dim3(kAttnThreads), kT5SmemBytes, st, p));
+                                      dim3(kT5Threads), kT5SmemBytes, st, p));
     else
         LEANKV_CUDA_TRY(launch_kernel(tq_prefill_attn_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
                                       dim3(kAttnThreads), kPfSmemBytes, st, p));

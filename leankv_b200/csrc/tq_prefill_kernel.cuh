@@ -339,11 +339,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_attn_kernel(const 
 // ---- the same attention with both products on the fifth-generation tensor cores ----------------------------
 // One CTA = 32 query tokens x 4 GQA heads = 128 rows = the M of tcgen05.mma; thread t owns row t, which is also
 // accumulator lane t in tensor memory, so the online softmax needs no shuffles. Pages are taken two at a time
-// (32 tokens): they are de-quantized into K-major blocked operand tiles (umma.cuh), one thread issues
-//   S[128 x 32]  = Q''_h . K^T + Q''_l . K^T      16 MMAs (N = 32, K = 16) into tensor-memory columns 0..31
+// (a block of 32 tokens): they are de-quantized into K-major blocked operand tiles (umma.cuh), one thread issues
+//   S[128 x 32]  = Q''_h . K^T + Q''_l . K^T      16 MMAs (N = 32, K = 16) into one of two score buffers in tensor memory
 // every thread reads its row of S (tcgen05.ld), applies key norm, causal mask and the running maximum, writes
 // its 32 probabilities (times value norm, fp16) as a row of the P operand tile, and one thread issues
-//   O[128 x 128] += P[128 x 32] . V[32 x 128]      2 MMAs (N = 128) into columns 32..159.
+//   O[128 x 128] += P[128 x 32] . V[32 x 128]      2 MMAs (N = 128) into columns 64..191.
+// The loop is software-pipelined: the keys of block b+1 are de-quantized (second K tile) and their score MMAs
+// issued (second score buffer) before the softmax of block b, and the value MMAs of block b run under the key
+// de-quantization of block b+2, so neither MMA group's latency is waited for in the open.
 // The running maximum only moves when a block exceeds it by more than kT5Slack (log2 units); then the rows of O
 // are rescaled in tensor memory (tcgen05.ld / st), which is rare after the first blocks. Completion of each MMA
 // group comes back through an mbarrier (tcgen05.commit) with a bounded wait. Output: the same partial results
@@ -352,29 +355,32 @@ constexpr int kT5Blk = 2;                          // pages per block
 constexpr int kT5N = kT5Blk * kPage;               // 32 tokens per block
 constexpr int kT5KChunksTok = kT5N / 8;            // 16-byte pieces along K for operands whose K is the token axis
 constexpr float kT5Slack = 8.0f;
-constexpr uint32_t kT5TmemCols = 256;              // S: 0..31, O: 32..159
-constexpr int kT5Stages = 2;
+constexpr uint32_t kT5TmemCols = 256;              // S: 0..31 and 32..63, O: 64..191
+constexpr int kT5Threads = 160;                    // four row warps + one warp whose first thread issues copies and MMAs
+constexpr int kT5Issuer = 128;
+constexpr int kT5Stages = 4;                      // raw page blocks in flight (three blocks of lead over their use)
+constexpr int kT5KTileBytes = kT5N * kDim * 2;
 // diagnostic status bits beside the time-out bit: the wait that ran out was for a page copy, the score MMAs, the value MMAs
 constexpr int kT5WherePages = 0x10, kT5WhereScores = 0x20, kT5WhereValues = 0x40;
 constexpr size_t kT5SmemBytes = 2 * (size_t)umma::kTileBytes             // Q'' high and low halves
-                                + (size_t)kT5N * kDim * 2                  // K tile  [token][coord]
+                                + 2 * (size_t)kT5KTileBytes                // K tiles [token][coord], blocks b and b+1
                                 + (size_t)kDim * kT5N * 2                  // V tile  [coord][token]
                                 + (size_t)umma::kRows * kT5N * 2           // P tile  [row][token]
                                 + (size_t)kT5Stages * kT5Blk * 2 * kChunkBytes   // raw chunks
-                                + 2 * kT5N * sizeof(float) + 64;
+                                + 3 * kT5N * sizeof(float) + 64;
 
-__global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_t5_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t t5_smem[];
     uint8_t* s_qh = t5_smem;
     uint8_t* s_ql = s_qh + umma::kTileBytes;
-    uint8_t* s_k = s_ql + umma::kTileBytes;                     // B of S:  rows = tokens, K = coordinates
-    uint8_t* s_v = s_k + (size_t)kT5N * kDim * 2;               // B of O:  rows = coordinates, K = tokens
+    uint8_t* s_k = s_ql + umma::kTileBytes;                     // B of S:  rows = tokens, K = coordinates (x 2)
+    uint8_t* s_v = s_k + 2 * (size_t)kT5KTileBytes;             // B of O:  rows = coordinates, K = tokens
     uint8_t* s_p = s_v + (size_t)kDim * kT5N * 2;               // A of O:  rows = (token, head), K = tokens
     uint8_t* s_raw = s_p + (size_t)umma::kRows * kT5N * 2;      // [stages][page of the block][K chunk | V chunk]
-    float* s_kn = reinterpret_cast<float*>(s_raw + (size_t)kT5Stages * kT5Blk * 2 * kChunkBytes);
-    float* s_vn = s_kn + kT5N;
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_vn + kT5N);   // [0..1] raw stages, [2] S done, [3] O done
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 4);
+    float* s_kn = reinterpret_cast<float*>(s_raw + (size_t)kT5Stages * kT5Blk * 2 * kChunkBytes);   // [2][32]
+    float* s_vn = s_kn + 2 * kT5N;
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_vn + kT5N);   // [0..3] raw stages, [4..5] S buffers, [6] O
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + kT5Stages + 3);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int H = p.H, Hq = H * kGroup;
@@ -389,12 +395,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_t5_kernel(const Pr
     const int n_blk = (n_pg + kT5Blk - 1) / kT5Blk;
 
     const uint32_t bar0 = smem_u32(s_bar);
+    const uint32_t bar_o = bar0 + 8 * (kT5Stages + 2);
+    auto bar_raw = [&](int b) { return bar0 + 8u * (uint32_t)(b % kT5Stages); };
+    auto bar_s = [&](int b) { return bar0 + 8u * (uint32_t)(kT5Stages + (b & 1)); };
+    // block b is use number b / 4 of its raw stage and b / 2 of its score buffer: those uses' phase parities
+    auto par_raw = [](int b) { return (uint32_t)((b / kT5Stages) & 1); };
+    auto par2 = [](int b) { return (uint32_t)((b >> 1) & 1); };
     int where = 0;                                            // which bounded wait gave up (kT5Where* status bits)
-    auto wait_short = [&](uint32_t bar, uint32_t parity) -> bool { return umma::bar_wait(bar, parity); };
+
     if (warp == 0) umma::tmem_alloc_n(smem_u32(s_tmem), kT5TmemCols);
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8 * i, 1);
+        for (int i = 0; i < kT5Stages + 3; ++i) mbar_init(bar0 + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     pdl_begin();
@@ -402,17 +414,26 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_t5_kernel(const Pr
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_tmem);
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kT5N;
+    const uint32_t tmem_o = tmem_base + 2 * kT5N;
 
     const size_t page_stride = (size_t)2 * H * kChunkBytes, kv_stride = (size_t)H * kChunkBytes;
     const uint8_t* pool_kvh = p.pool + (size_t)kvh * kChunkBytes;
     bool bad_page = false;
-    auto issue = [&](int blk) {                              // thread 0: the block's (up to two) pages into stage blk & 1
-        const int st = blk & 1;
+    int n_issued = 0, n_landed = 0;                          // thread 0: page blocks requested / seen to arrive
+    int next_id[kT5Blk] = {0, 0};                            // thread 0: page ids of the block issue() takes next
+    auto load_ids = [&](int blk) {
+#pragma unroll
+        for (int i = 0; i < kT5Blk; ++i)
+            next_id[i] = blk * kT5Blk + i < n_pg ? p.seq_pages[pg_lo + blk * kT5Blk + i] : 0;
+    };
+    auto issue = [&](int blk) {                              // thread 0: the block's (up to two) pages into stage blk % 4
+        const int st = blk % kT5Stages;
         const int n_here = min(kT5Blk, n_pg - blk * kT5Blk);
         mbar_expect_tx(bar0 + 8 * st, (uint32_t)n_here * 2 * kChunkBytes);
-        for (int i = 0; i < n_here; ++i) {
-            int id = p.seq_pages[pg_lo + blk * kT5Blk + i];
+#pragma unroll
+        for (int i = 0; i < kT5Blk; ++i) {
+            if (i >= n_here) break;
+            int id = next_id[i];
             if (id < 0 || id >= p.n_pages) {
                 id = 0;
                 bad_page = true;
@@ -422,12 +443,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_t5_kernel(const Pr
             bulk_g2s(dst, src, kChunkBytes, bar0 + 8 * st);
             bulk_g2s(dst + kChunkBytes, src + kv_stride, kChunkBytes, bar0 + 8 * st);
         }
+        n_issued = blk + 1;
+        load_ids(blk + 1);                                   // calls come in block order: the ids are there by the next one
     };
-    if (tid == 0)
+    if (tid == kT5Issuer) {
+        load_ids(0);
         for (int blk = 0; blk < min(kT5Stages, n_blk); ++blk) issue(blk);
+    }
 
     // ---- the tile's queries: rotated, scaled, fp16 high and low halves, in the blocked operand layout ----
-    for (int i = tid; i < umma::kRows * (kDim / 8); i += kAttnThreads) {
+    for (int i = tid; i < umma::kRows * (kDim / 8); i += kT5Threads) {
         const int r = i / (kDim / 8), k8 = i % (kDim / 8);
         const int tok = tok0 + (r >> 2), head = r & 3;
         float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -447,152 +472,181 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_t5_kernel(const Pr
         *reinterpret_cast<uint4*>(s_ql + umma::offset(r, k8)) = *reinterpret_cast<const uint4*>(lo);
     }
 
+    // thread = one unit (32 codes) of page tid / 64 of the block: 32 fp16 values alpha * c[code], two per register
+    const int pgi = tid >> 6, ui = tid & 63;
+    auto unit_values = [&](const uint8_t* chunk, uint32_t (&h2)[16]) {
+        const Unit u = load_unit(reinterpret_cast<const uint32_t*>(chunk), ui);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t sa = u.s[w], sb = sa >> 16;
+            const uint32_t la = __byte_perm(p.tl0, p.tl1, sa), ha = __byte_perm(p.th0, p.th1, sa);
+            const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb), hb = __byte_perm(p.th0, p.th1, sb);
+            h2[4 * w + 0] = __byte_perm(la, ha, 0x5140);
+            h2[4 * w + 1] = __byte_perm(la, ha, 0x7362);
+            h2[4 * w + 2] = __byte_perm(lb, hb, 0x5140);
+            h2[4 * w + 3] = __byte_perm(lb, hb, 0x7362);
+        }
+    };
+    // norm of token j of block b (K or V chunk), times 1 / alpha; 0 for pages beyond the range
+    auto norm_of = [&](int b, int j, bool is_v) -> float {
+        const int pj = j >> 4;
+        if (b * kT5Blk + pj >= n_pg) return 0.f;
+        const uint8_t* rw = s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pj) * 2 * kChunkBytes + (is_v ? kChunkBytes : 0);
+        return __half2float(reinterpret_cast<const __half*>(rw + kNormOffsetBytes)[j & 15]) * p.inv_alpha;
+    };
+    auto dequant_keys = [&](int b) {                         // block b's keys -> K tile b & 1
+        if (warp >= 4) return;
+        uint32_t h2[16];
+        unit_values(s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pgi) * 2 * kChunkBytes, h2);
+        // K unit ui = 4 * token + quarter: coordinates 32 * quarter .. + 31 of the token = 4 pieces of row token
+        uint8_t* kt = s_k + (size_t)(b & 1) * kT5KTileBytes;
+        const int trow = 16 * pgi + (ui >> 2), k8 = 4 * (ui & 3);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(kt + umma::offset(trow, k8 + q)) = make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
+        if (tid < kT5N) s_kn[(b & 1) * kT5N + tid] = norm_of(b, tid, false);
+    };
+    auto dequant_values = [&](int b) {                       // block b's values -> the V tile
+        if (warp >= 4) return;
+        uint32_t h2[16];
+        unit_values(s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pgi) * 2 * kChunkBytes + kChunkBytes, h2);
+        // V unit: coordinates 16 * grp .. + 15 of tokens 2 * pair, 2 * pair + 1: register i holds the pair's two
+        // tokens of coordinate 16 * grp + i = 4 bytes of row (coordinate) along K (tokens)
+        const int grp = (ui & 31) >> 2, pair = (ui & 3) + ((ui >> 5) << 2);
+        const int tokb = 16 * pgi + 2 * pair;                // token index in the block
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            *reinterpret_cast<uint32_t*>(s_v + umma::offset_k(16 * grp + i, tokb >> 3, kT5KChunksTok) + (tokb & 7) * 2) = h2[i];
+        if (tid < kT5N) s_vn[tid] = norm_of(b, tid, true);
+    };
+    auto issue_scores = [&](int b) {                         // thread 0: S(b) into score buffer b & 1
+        const uint32_t qh = smem_u32(s_qh), ql = smem_u32(s_ql);
+        const uint32_t kb = smem_u32(s_k) + (uint32_t)(b & 1) * kT5KTileBytes;
+        const uint32_t ts = tmem_base + (uint32_t)(b & 1) * kT5N;
+#pragma unroll
+        for (int ks = 0; ks < kDim / 16; ++ks) {
+            const uint32_t off = (uint32_t)ks * 2 * umma::kLbo;
+            umma::mma_f16_n(ts, umma::desc(qh + off), umma::desc(kb + off), umma::idesc_n(kT5N), ks == 0 ? 0u : 1u);
+            umma::mma_f16_n(ts, umma::desc(ql + off), umma::desc(kb + off), umma::idesc_n(kT5N), 1u);
+        }
+        umma::commit(bar_s(b));
+    };
+
     const int row = tid;                                      // = accumulator lane
     const int lane0 = 32 * warp;
     const int qpos = p.start_pos + tok0 + (row >> 2);
     float m_ref = kNoRef, l_run = 0.f;
-    uint32_t ph_raw = 0, ph_s = 0, ph_o = 0;                  // phase parities (ph_raw: bit per stage)
-    bool failed = false, o_pending = false;                   // o_pending: a PV group has been committed and not waited for
+    bool failed = false;
+    int n_pv = 0;                                             // value MMA groups committed
 
-    for (int blk = 0; blk < n_blk; ++blk) {
-        const int st = blk & 1;
-        // the previous block's PV MMAs read the V and P tiles: they must be done before the tiles are rewritten
-        if (o_pending) {
-            const bool ok = wait_short(bar0 + 8 * 3, ph_o);
-            ph_o ^= 1u;
-            o_pending = false;
-            if (!ok) { failed = true; where |= kT5WhereValues; }
+    // ---- prologue: keys of block 0, their score MMAs ----
+    if (n_blk > 0) {
+        if (!umma::bar_wait(bar_raw(0), 0)) {
+            failed = true;
+            where |= kT5WherePages;
+        } else if (tid == kT5Issuer) {
+            n_landed = 1;
         }
-        const bool got = wait_short(bar0 + 8 * st, (ph_raw >> st) & 1u);
-        if (!got) where |= kT5WherePages;
-        ph_raw ^= 1u << st;
-        umma::fence_after_sync();
-        if (__syncthreads_or(!got || failed)) {
+        dequant_keys(0);
+    }
+    umma::fence_operands();
+    umma::fence_before_sync();
+    failed = __syncthreads_or(failed);                        // also publishes the query tiles
+    umma::fence_after_sync();
+    if (!failed && n_blk > 0 && tid == kT5Issuer) issue_scores(0);
+
+    for (int blk = 0; blk < n_blk && !failed; ++blk) {
+        // (1) keys of the next block while S(blk) is on the tensor cores
+        if (blk + 1 < n_blk) {
+            if (!umma::bar_wait(bar_raw(blk + 1), par_raw(blk + 1))) {
+                failed = true;
+                where |= kT5WherePages;
+            } else if (tid == kT5Issuer) {
+                n_landed = blk + 2;
+            }
+            dequant_keys(blk + 1);
+        }
+        // (2) values of this block: the previous block's value MMAs read the V and P tiles and must be done
+        if (blk > 0) {
+            if (!umma::bar_wait(bar_o, (uint32_t)((blk - 1) & 1))) {
+                failed = true;
+                where |= kT5WhereValues;
+            }
+            umma::fence_after_sync();
+        }
+        dequant_values(blk);
+        umma::fence_operands();
+        umma::fence_before_sync();
+        if (__syncthreads_or(failed)) {
             failed = true;
             break;
         }
-        // ---- de-quantize the block: thread = one K unit and one V unit of page tid / 64 ----
-        {
-            const int pgi = tid >> 6, ui = tid & 63;
-            const uint8_t* raw = s_raw + ((size_t)st * kT5Blk + pgi) * 2 * kChunkBytes;
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                const Unit u = load_unit(reinterpret_cast<const uint32_t*>(raw + (which ? kChunkBytes : 0)), ui);
-                uint32_t h2[16];                 // 32 fp16 values alpha * c[code], two per register, code order
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const uint32_t sa = u.s[w], sb = sa >> 16;
-                    const uint32_t la = __byte_perm(p.tl0, p.tl1, sa), ha = __byte_perm(p.th0, p.th1, sa);
-                    const uint32_t lb = __byte_perm(p.tl0, p.tl1, sb), hb = __byte_perm(p.th0, p.th1, sb);
-                    h2[4 * w + 0] = __byte_perm(la, ha, 0x5140);
-                    h2[4 * w + 1] = __byte_perm(la, ha, 0x7362);
-                    h2[4 * w + 2] = __byte_perm(lb, hb, 0x5140);
-                    h2[4 * w + 3] = __byte_perm(lb, hb, 0x7362);
-                }
-                if (which == 0) {
-                    // K unit ui = 4 * token + quarter: coordinates 32 * quarter .. + 31 of the token = 4 pieces of row token
-                    const int trow = 16 * pgi + (ui >> 2), k8 = 4 * (ui & 3);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        *reinterpret_cast<uint4*>(s_k + umma::offset(trow, k8 + q)) =
-                            make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
-                } else {
-                    // V unit: coordinates 16 * grp .. + 15 of tokens 2 * pair, 2 * pair + 1: register i holds the
-                    // pair's two tokens of coordinate 16 * grp + i = 4 bytes of row (coordinate) along K (tokens)
-                    const int grp = (ui & 31) >> 2, pair = (ui & 3) + ((ui >> 5) << 2);
-                    const int tokb = 16 * pgi + 2 * pair;                       // token index in the block
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        *reinterpret_cast<uint32_t*>(s_v + umma::offset_k(16 * grp + i, tokb >> 3, kT5KChunksTok) +
-                                                     (tokb & 7) * 2) = h2[i];
-                }
-            }
-            if (tid < 2 * kT5N) {
-                const int which = tid >= kT5N, j = tid & (kT5N - 1);             // token j of the block
-                const int pj = j >> 4;
-                float v = 0.f;                                                   // pages beyond the range: norm 0
-                if (blk * kT5Blk + pj < n_pg) {
-                    const uint8_t* rw = s_raw + ((size_t)st * kT5Blk + pj) * 2 * kChunkBytes + (which ? kChunkBytes : 0);
-                    v = __half2float(reinterpret_cast<const __half*>(rw + kNormOffsetBytes)[j & 15]) * p.inv_alpha;
-                }
-                (which ? s_vn : s_kn)[j] = v;
-            }
-        }
-        umma::fence_operands();
-        umma::fence_before_sync();
-        __syncthreads();
         umma::fence_after_sync();
-        if (tid == 0) {
-            if (blk + kT5Stages < n_blk) issue(blk + kT5Stages);       // the raw stage has been consumed
-            const uint32_t qh = smem_u32(s_qh), ql = smem_u32(s_ql), kb = smem_u32(s_k);
-#pragma unroll
-            for (int ks = 0; ks < kDim / 16; ++ks) {
-                const uint32_t off = (uint32_t)ks * 2 * umma::kLbo;
-                umma::mma_f16_n(tmem_s, umma::desc(qh + off), umma::desc(kb + off), umma::idesc_n(kT5N), ks == 0 ? 0u : 1u);
-                umma::mma_f16_n(tmem_s, umma::desc(ql + off), umma::desc(kb + off), umma::idesc_n(kT5N), 1u);
-            }
-            umma::commit(bar0 + 8 * 2);
+        if (tid == kT5Issuer) {
+            if (blk + kT5Stages < n_blk) issue(blk + kT5Stages);       // both halves of the raw stage have been consumed
+            if (blk + 1 < n_blk) issue_scores(blk + 1);
         }
-        {
-            const bool ok = wait_short(bar0 + 8 * 2, ph_s);
-            if (!ok) where |= kT5WhereScores;
-            ph_s ^= 1u;
-            umma::fence_after_sync();
-            if (__syncthreads_or(!ok)) {
-                failed = true;
-                break;
-            }
+        // (3) this thread's row of S(blk): key norm, causal mask, running maximum
+        if (!umma::bar_wait(bar_s(blk), par2(blk))) {
+            failed = true;
+            where |= kT5WhereScores;
         }
-        // ---- this thread's row of scores: key norm, causal mask, running maximum ----
-        uint32_t sv[32];
-        umma::ld32(sv, tmem_s, lane0, 0);
-        const int kbase = (pg_lo + blk * kT5Blk) * kPage;
-        const int n_tok_here = min(kT5Blk, n_pg - blk * kT5Blk) * kPage;     // tokens of this block that lie in the range
-        float sc[32];
-        float bmax = kNoRef;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const bool vis = j < n_tok_here && kbase + j <= qpos;
-            sc[j] = vis ? __uint_as_float(sv[j]) * s_kn[j] : kNoRef;
-            bmax = fmaxf(bmax, sc[j]);
-        }
-        // the reference only moves when the block exceeds it by more than the slack; the rows of O are then
-        // rescaled in tensor memory (all lanes of a warp take part; lanes that do not move use factor 1)
-        const bool move = bmax > m_ref + kT5Slack;
-        const float m_new = move ? bmax : m_ref;
-        const float f = move ? ex2_approx(m_ref - m_new) : 1.0f;
-        if (__any_sync(0xffffffffu, move) && blk > 0) {
-#pragma unroll
-            for (int c0 = 0; c0 < kDim; c0 += 32) {
-                uint32_t ov[32];
-                umma::ld32(ov, tmem_o, lane0, c0);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-                umma::st32(ov, tmem_o, lane0, c0);
-            }
-        }
-        m_ref = m_new;
-        l_run *= f;
-        // probabilities (at most 2^slack) times value norm, fp16, as this row of the P operand
-        {
-            float sum = 0.f;
-            __half ph[32];
+        umma::fence_after_sync();
+        if (warp < 4) {
+            uint32_t sv[32];
+            umma::ld32(sv, tmem_base + (uint32_t)(blk & 1) * kT5N, lane0, 0);
+            const float* kn = s_kn + (blk & 1) * kT5N;
+            const int kbase = (pg_lo + blk * kT5Blk) * kPage;
+            const int n_tok_here = min(kT5Blk, n_pg - blk * kT5Blk) * kPage;     // tokens of this block that lie in the range
+            float sc[32];
+            float bmax = kNoRef;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float pr = sc[j] > 0.5f * kNoRef ? ex2_approx(sc[j] - m_ref) : 0.f;
-                sum += pr;
-                ph[j] = __float2half_rn(pr * s_vn[j]);
+                const bool vis = j < n_tok_here && kbase + j <= qpos;
+                sc[j] = vis ? __uint_as_float(sv[j]) * kn[j] : kNoRef;
+                bmax = fmaxf(bmax, sc[j]);
             }
-            l_run += sum;
+            // the reference only moves when the block exceeds it by more than the slack; the rows of O are then
+            // rescaled in tensor memory (all lanes of a warp take part; lanes that do not move use factor 1)
+            const bool move = bmax > m_ref + kT5Slack;
+            const float m_new = move ? bmax : m_ref;
+            const float f = move ? ex2_approx(m_ref - m_new) : 1.0f;
+            if (__any_sync(0xffffffffu, move) && blk > 0) {
 #pragma unroll
-            for (int c = 0; c < kT5KChunksTok; ++c)
-                *reinterpret_cast<uint4*>(s_p + umma::offset_k(row, c, kT5KChunksTok)) = *reinterpret_cast<const uint4*>(ph + 8 * c);
+                for (int c0 = 0; c0 < kDim; c0 += 32) {
+                    uint32_t ov[32];
+                    umma::ld32(ov, tmem_o, lane0, c0);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+                    umma::st32(ov, tmem_o, lane0, c0);
+                }
+            }
+            m_ref = m_new;
+            l_run *= f;
+            // probabilities (at most 2^slack) times value norm, fp16, as this row of the P operand
+            {
+                float sum = 0.f;
+                __half ph[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float pr = sc[j] > 0.5f * kNoRef ? ex2_approx(sc[j] - m_ref) : 0.f;
+                    sum += pr;
+                    ph[j] = __float2half_rn(pr * s_vn[j]);
+                }
+                l_run += sum;
+#pragma unroll
+                for (int c = 0; c < kT5KChunksTok; ++c)
+                    *reinterpret_cast<uint4*>(s_p + umma::offset_k(row, c, kT5KChunksTok)) = *reinterpret_cast<const uint4*>(ph + 8 * c);
+            }
         }
         umma::fence_operands();
         umma::fence_before_sync();
-        __syncthreads();
+        if (__syncthreads_or(failed)) {
+            failed = true;
+            break;
+        }
         umma::fence_after_sync();
-        if (tid == 0) {
+        if (tid == kT5Issuer) {
             const uint32_t pb = smem_u32(s_p), vb = smem_u32(s_v);
 #pragma unroll
             for (int kt = 0; kt < kT5N / 16; ++kt) {
@@ -600,32 +654,33 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_t5_kernel(const Pr
                 umma::mma_f16_n(tmem_o, umma::desc_k(pb + off, kT5KChunksTok), umma::desc_k(vb + off, kT5KChunksTok),
                                 umma::idesc_n(kDim), (blk == 0 && kt == 0) ? 0u : 1u);
             }
-            umma::commit(bar0 + 8 * 3);
+            umma::commit(bar_o);
         }
-        o_pending = true;
+        n_pv = blk + 1;
     }
-    if (o_pending) {
-        const bool ok = wait_short(bar0 + 8 * 3, ph_o);
+    if (!failed && n_pv > 0) {
+        if (!umma::bar_wait(bar_o, (uint32_t)((n_pv - 1) & 1))) {
+            failed = true;
+            where |= kT5WhereValues;
+        }
         umma::fence_after_sync();
-        if (!ok) { failed = true; where |= kT5WhereValues; }
     }
     failed = __syncthreads_or(failed);
     if (where != 0) atomicOr(p.status, where);
-    if ((failed || bad_page) && tid == 0) atomicOr(p.status, failed ? kStatusWaitTimeout : kStatusBadPage);
-    if (failed && tid == 0) {
+    if ((failed || bad_page) && tid == kT5Issuer) atomicOr(p.status, failed ? kStatusWaitTimeout : kStatusBadPage);
+    if (failed && tid == kT5Issuer) {
         // give page copies that may still be in flight a bounded chance to land in this CTA's shared memory
-#pragma unroll
-        for (int st = 0; st < kT5Stages; ++st) wait_short(bar0 + 8 * st, (ph_raw >> st) & 1u);
+        for (int b = n_landed; b < n_issued; ++b) umma::bar_wait(bar_raw(b), par_raw(b));
     }
 
     // ---- this range's partial result for this thread's row ----
     // (tcgen05.ld is a warp-wide instruction: every lane takes part, rows beyond the chunk only skip the stores)
     const int tok = tok0 + (row >> 2), head = row & 3;
-    const bool store = !failed && tok < p.T;
+    const bool store = !failed && tok < p.T && warp < 4;
     const size_t n_vec = (size_t)p.T * Hq;
     const size_t v = (size_t)min(tok, p.T - 1) * Hq + (size_t)kvh * kGroup + head;
     float* dst = p.o_part + ((size_t)blockIdx.z * n_vec + v) * kDim;
-    if (!failed && n_blk > 0) {                     // CTA-uniform
+    if (!failed && n_blk > 0 && warp < 4) {         // warp-uniform
 #pragma unroll
         for (int c0 = 0; c0 < kDim; c0 += 32) {
             uint32_t ov[32];
