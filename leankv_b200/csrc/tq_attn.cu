@@ -38,6 +38,8 @@
 
 #include <algorithm>
 #include <atomic>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "tq_layout.cuh"
@@ -462,6 +464,71 @@ struct TilePlan {
     int n_tiles, n_splits;
     size_t off_qprime, off_opart, off_ml, total;
 };
+
+// Where the page ranges of a tile begin (cumulative fractions in 1/65536). CTAs are handed to the SMs in grid
+// order (tiles of one range first, longest tile first, then the next range), and with more CTAs than the
+// 2 x SM-count that run at once equal ranges leave the last round of CTAs part-empty. Ranges that shrink
+// geometrically put the short ones last, so the tail evens out. The ratio is picked by playing the schedule
+// through on the host (every CTA goes to the slot that frees first; cost = pages + a fixed start-up) for
+// equal ranges and three ratios; the last plan is remembered, since a model asks for it once per layer.
+struct SplitPlan {
+    uint32_t cum[9];
+};
+static SplitPlan plan_splits(const TilePlan& tp, int T, int start_pos, int Hkv) {
+    static std::mutex mu;
+    static long long last_key[4] = {-1, -1, -1, -1};
+    static SplitPlan last_plan;
+    std::lock_guard<std::mutex> lock(mu);
+    const long long key[4] = {T, start_pos, Hkv, tp.n_splits};
+    if (std::memcmp(key, last_key, sizeof(key)) == 0) return last_plan;
+    const int s = tp.n_splits;
+    const int slots = sm_count() * 2;
+    auto fill = [&](double r, SplitPlan& sp) {
+        double w[8], tot = 0.0, acc = 0.0;
+        for (int z = 0; z < s; ++z) tot += (w[z] = std::pow(r, z));
+        sp.cum[0] = 0;
+        for (int z = 0; z < s; ++z) {
+            acc += w[z];
+            sp.cum[z + 1] = (uint32_t)std::llround(65536.0 * acc / tot);
+        }
+        sp.cum[s] = 65536;
+        for (int z = s + 1; z <= 8; ++z) sp.cum[z] = 65536;
+    };
+    SplitPlan best;
+    fill(1.0, best);
+    const long long ctas = (long long)tp.n_tiles * Hkv * s;
+    if (s > 1 && ctas > slots && ctas <= 16384) {
+        const double ratios[4] = {1.0, 0.8, 0.7, 0.6};
+        double best_t = 0.0;
+        std::vector<double> heap;
+        for (int c = 0; c < 4; ++c) {
+            SplitPlan sp;
+            fill(ratios[c], sp);
+            heap.assign(slots, 0.0);                                  // min-heap of the times the slots free up
+            auto cmp = [](double a, double b) { return a > b; };
+            double t_end = 0.0;
+            for (int z = 0; z < s; ++z)
+                for (int y = 0; y < Hkv; ++y)
+                    for (int x = 0; x < tp.n_tiles; ++x) {
+                        const int tile = tp.n_tiles - 1 - x;
+                        const long long last_tok = std::min<long long>((long long)tile * kPfTokens + kPfTokens, T) - 1;
+                        const long long n_all = (start_pos + last_tok) / kPage + 1;
+                        const long long n_pg = ((n_all * sp.cum[z + 1]) >> 16) - ((n_all * sp.cum[z]) >> 16);
+                        std::pop_heap(heap.begin(), heap.end(), cmp);
+                        heap.back() += 4.0 + (double)n_pg;
+                        t_end = std::max(t_end, heap.back());
+                        std::push_heap(heap.begin(), heap.end(), cmp);
+                    }
+            if (c == 0 || t_end < 0.98 * best_t) {                    // equal ranges unless a ratio clearly wins
+                best_t = t_end;
+                best = sp;
+            }
+        }
+    }
+    std::memcpy(last_key, key, sizeof(key));
+    last_plan = best;
+    return best;
+}
 // The pages of a query tile are cut into up to 8 ranges of at least ~16 pages, handled by separate CTAs, unless
 // the (tile, kv head) pairs alone already make several waves: many short CTAs fill the SMs evenly although
 // causal tiles differ in length (measured at 512 tokens after 3584: 2 ranges 366 us, 8 ranges 312 us).
@@ -539,6 +606,10 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     p.o_part = o_part;
     p.ml_part = ml_part;
     p.n_splits = tp.n_splits;
+    {
+        const SplitPlan sp = plan_splits(tp, T, start_pos, n_kv_heads);
+        std::memcpy(p.split_cum, sp.cum, sizeof(p.split_cum));
+    }
     p.pool = static_cast<const uint8_t*>(pool);
     p.n_pages = n_pages;
     p.H = n_kv_heads;

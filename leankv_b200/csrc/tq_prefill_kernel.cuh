@@ -21,6 +21,7 @@ struct PrefillParams {
     float* o_part;             // [n_splits][T][Hq][128] un-normalised partial results in the rotated space
     float* ml_part;            // [n_splits][T][Hq][2]: running maximum (log2 units) and denominator of each partial
     int n_splits;              // the pages of a query tile are cut into this many ranges (grid z)
+    uint32_t split_cum[9];     // range z of a tile with n pages = pages [n * cum[z] >> 16, n * cum[z+1] >> 16)
     const uint8_t* pool;
     int n_pages, H;
     const int32_t* seq_pages;  // the sequence's page ids in order
@@ -29,6 +30,11 @@ struct PrefillParams {
     float inv_alpha;
     int* status;
 };
+
+// first page of range z of a tile with n_all pages (z = n_splits gives n_all)
+__device__ __forceinline__ int split_begin(const PrefillParams& p, int n_all, int z) {
+    return (int)(((unsigned long long)n_all * p.split_cum[z]) >> 16);
+}
 
 constexpr int kPfMt = 2;                       // 16-row MMA tiles per warp
 constexpr int kPfTokens = 4 * 4 * kPfMt;       // query tokens per CTA: 4 warps x 4 tokens per tile x tiles
@@ -71,8 +77,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_attn_kernel(const 
     const int tok0 = tile * kPfTokens;                       // first query token of the tile (chunk-relative)
     const int last_tok = min(tok0 + kPfTokens, p.T) - 1;
     const int n_all = (p.start_pos + last_tok) / kPage + 1;  // pages the tile's last token sees
-    const int pg_lo = (int)((long long)n_all * blockIdx.z / p.n_splits);
-    const int n_pg = (int)((long long)n_all * (blockIdx.z + 1) / p.n_splits) - pg_lo;   // this CTA's share of them
+    const int pg_lo = split_begin(p, n_all, blockIdx.z);
+    const int n_pg = split_begin(p, n_all, blockIdx.z + 1) - pg_lo;                     // this CTA's share of them
 
     const uint32_t bar0 = smem_u32(s_bar);
     if (tid == 0) {
@@ -390,8 +396,8 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     const int tok0 = tile * 32;
     const int last_tok = min(tok0 + 32, p.T) - 1;
     const int n_all = (p.start_pos + last_tok) / kPage + 1;
-    const int pg_lo = (int)((long long)n_all * blockIdx.z / p.n_splits);
-    const int n_pg = (int)((long long)n_all * (blockIdx.z + 1) / p.n_splits) - pg_lo;
+    const int pg_lo = split_begin(p, n_all, blockIdx.z);
+    const int n_pg = split_begin(p, n_all, blockIdx.z + 1) - pg_lo;
     const int n_blk = (n_pg + kT5Blk - 1) / kT5Blk;
 
     const uint32_t bar0 = smem_u32(s_bar);
@@ -595,16 +601,29 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
         if (warp < 4) {
             uint32_t sv[32];
             umma::ld32(sv, tmem_base + (uint32_t)(blk & 1) * kT5N, lane0, 0);
-            const float* kn = s_kn + (blk & 1) * kT5N;
             const int kbase = (pg_lo + blk * kT5Blk) * kPage;
             const int n_tok_here = min(kT5Blk, n_pg - blk * kT5Blk) * kPage;     // tokens of this block that lie in the range
+            // a whole block at or below the tile's first query position needs no mask (CTA-uniform)
+            const bool full = n_tok_here == kT5N && kbase + kT5N - 1 <= p.start_pos + tok0;
             float sc[32];
             float bmax = kNoRef;
+            {
+                const float4* kn4 = reinterpret_cast<const float4*>(s_kn + (blk & 1) * kT5N);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const bool vis = j < n_tok_here && kbase + j <= qpos;
-                sc[j] = vis ? __uint_as_float(sv[j]) * kn[j] : kNoRef;
-                bmax = fmaxf(bmax, sc[j]);
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 n = kn4[j4];
+                    sc[4 * j4 + 0] = __uint_as_float(sv[4 * j4 + 0]) * n.x;
+                    sc[4 * j4 + 1] = __uint_as_float(sv[4 * j4 + 1]) * n.y;
+                    sc[4 * j4 + 2] = __uint_as_float(sv[4 * j4 + 2]) * n.z;
+                    sc[4 * j4 + 3] = __uint_as_float(sv[4 * j4 + 3]) * n.w;
+                }
+                if (!full) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (!(j < n_tok_here && kbase + j <= qpos)) sc[j] = kNoRef;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) bmax = fmaxf(bmax, sc[j]);
             }
             // the reference only moves when the block exceeds it by more than the slack; the rows of O are then
             // rescaled in tensor memory (all lanes of a warp take part; lanes that do not move use factor 1)
@@ -626,17 +645,26 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
             // probabilities (at most 2^slack) times value norm, fp16, as this row of the P operand
             {
                 float sum = 0.f;
-                __half ph[32];
+                __half2 ph[16];
+                const float4* vn4 = reinterpret_cast<const float4*>(s_vn);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float pr = sc[j] > 0.5f * kNoRef ? ex2_approx(sc[j] - m_ref) : 0.f;
-                    sum += pr;
-                    ph[j] = __float2half_rn(pr * s_vn[j]);
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 n = vn4[j4];
+                    float pr[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float x = sc[4 * j4 + e];
+                        // a masked entry gives 0 (with no reference yet x - m_ref would be 0, hence the test)
+                        pr[e] = (full || x > 0.5f * kNoRef) ? ex2_approx(x - m_ref) : 0.f;
+                    }
+                    sum += (pr[0] + pr[1]) + (pr[2] + pr[3]);
+                    ph[2 * j4] = __floats2half2_rn(pr[0] * n.x, pr[1] * n.y);
+                    ph[2 * j4 + 1] = __floats2half2_rn(pr[2] * n.z, pr[3] * n.w);
                 }
                 l_run += sum;
 #pragma unroll
                 for (int c = 0; c < kT5KChunksTok; ++c)
-                    *reinterpret_cast<uint4*>(s_p + umma::offset_k(row, c, kT5KChunksTok)) = *reinterpret_cast<const uint4*>(ph + 8 * c);
+                    *reinterpret_cast<uint4*>(s_p + umma::offset_k(row, c, kT5KChunksTok)) = *reinterpret_cast<const uint4*>(ph + 4 * c);
             }
         }
         umma::fence_operands();
