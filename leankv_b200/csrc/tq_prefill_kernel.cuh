@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
 
     // ---- the tile's queries: rotated, scaled, fp16 high and low halves, in the blocked operand layout ----
     for (int i = tid; i < umma::kRows * (kDim / 8); i += kT5Threads) {
-        const int r = i / (kDim / 8), k8 = i % (kDim / 8);
+        const int r = i % umma::kRows, k8 = i / umma::kRows;     // 8 lanes = 8 rows of one 128-byte core matrix
         const int tok = tok0 + (r >> 2), head = r & 3;
         float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (tok < p.T) {
@@ -480,8 +480,8 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
 
     // thread = one unit (32 codes) of page tid / 64 of the block: 32 fp16 values alpha * c[code], two per register
     const int pgi = tid >> 6, ui = tid & 63;
-    auto unit_values = [&](const uint8_t* chunk, uint32_t (&h2)[16]) {
-        const Unit u = load_unit(reinterpret_cast<const uint32_t*>(chunk), ui);
+    auto unit_values = [&](const uint8_t* chunk, int unit, uint32_t (&h2)[16]) {
+        const Unit u = load_unit(reinterpret_cast<const uint32_t*>(chunk), unit);
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const uint32_t sa = u.s[w], sb = sa >> 16;
@@ -503,10 +503,12 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     auto dequant_keys = [&](int b) {                         // block b's keys -> K tile b & 1
         if (warp >= 4) return;
         uint32_t h2[16];
-        unit_values(s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pgi) * 2 * kChunkBytes, h2);
-        // K unit ui = 4 * token + quarter: coordinates 32 * quarter .. + 31 of the token = 4 pieces of row token
+        // K unit 4 * token + quarter: coordinates 32 * quarter .. + 31 of the token = 4 pieces of row token;
+        // 8 consecutive lanes take 8 consecutive tokens of one quarter, so a 16-byte store fills one core matrix
+        const int ktok = ui & 15, kq = ui >> 4;
+        unit_values(s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pgi) * 2 * kChunkBytes, 4 * ktok + kq, h2);
         uint8_t* kt = s_k + (size_t)(b & 1) * kT5KTileBytes;
-        const int trow = 16 * pgi + (ui >> 2), k8 = 4 * (ui & 3);
+        const int trow = 16 * pgi + ktok, k8 = 4 * kq;
 #pragma unroll
         for (int q = 0; q < 4; ++q)
             *reinterpret_cast<uint4*>(kt + umma::offset(trow, k8 + q)) = make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
@@ -515,14 +517,30 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     auto dequant_values = [&](int b) {                       // block b's values -> the V tile
         if (warp >= 4) return;
         uint32_t h2[16];
-        unit_values(s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pgi) * 2 * kChunkBytes + kChunkBytes, h2);
+        unit_values(s_raw + ((size_t)(b % kT5Stages) * kT5Blk + pgi) * 2 * kChunkBytes + kChunkBytes, ui, h2);
         // V unit: coordinates 16 * grp .. + 15 of tokens 2 * pair, 2 * pair + 1: register i holds the pair's two
-        // tokens of coordinate 16 * grp + i = 4 bytes of row (coordinate) along K (tokens)
-        const int grp = (ui & 31) >> 2, pair = (ui & 3) + ((ui >> 5) << 2);
-        const int tokb = 16 * pgi + 2 * pair;                // token index in the block
+        // tokens of coordinate 16 * grp + i = 4 bytes of row (coordinate) along K (tokens). Lanes 4n .. 4n+3 hold
+        // pairs 0..3 (or 4..7) of one group = the 8 tokens of a 16-byte piece: a 4 x 4 transpose between them
+        // (per 4 registers) leaves lane p with the whole piece of coordinates 4j + p, stored with one instruction.
+        const int grp = (ui & 31) >> 2, pl = ui & 3, half = ui >> 5;
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-            *reinterpret_cast<uint32_t*>(s_v + umma::offset_k(16 * grp + i, tokb >> 3, kT5KChunksTok) + (tokb & 7) * 2) = h2[i];
+        for (int j = 0; j < 4; ++j) {
+            uint32_t* a = h2 + 4 * j;
+#pragma unroll
+            for (int c = 0; c < 4; c += 2) {                 // 2 x 2 blocks between lanes p, p ^ 1
+                const uint32_t send = (pl & 1) ? a[c] : a[c + 1];
+                const uint32_t got = __shfl_xor_sync(0xffffffffu, send, 1);
+                if (pl & 1) a[c] = got; else a[c + 1] = got;
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {                    // then between lanes p, p ^ 2
+                const uint32_t send = (pl & 2) ? a[c] : a[c + 2];
+                const uint32_t got = __shfl_xor_sync(0xffffffffu, send, 2);
+                if (pl & 2) a[c] = got; else a[c + 2] = got;
+            }
+            *reinterpret_cast<uint4*>(s_v + umma::offset_k(16 * grp + 4 * j + pl, 2 * pgi + half, kT5KChunksTok)) =
+                make_uint4(a[0], a[1], a[2], a[3]);
+        }
         if (tid < kT5N) s_vn[tid] = norm_of(b, tid, true);
     };
     auto issue_scores = [&](int b) {                         // thread 0: S(b) into score buffer b & 1
