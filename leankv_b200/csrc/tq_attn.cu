@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(128) tq_qrot_kernel(const __half* q, const flo
 // ---- main kernel -----------------------------------------------------------
 #include "tq_attn_kernel.cuh"
 #include "tq_prefill_kernel.cuh"
+#include "tq_prefill_ws.cuh"
 
 // ---- host side ---------------------------------------------------------------
 struct AttnPlan {
@@ -450,14 +451,16 @@ static long long prefill_rows_pages(long long first_pos, long long n) {
     return upto(first_pos + n) - upto(first_pos);
 }
 
-// LEANKV_PREFILL_MMA=sync keeps the prefill attention's two products on mma.sync; default: tcgen05.
-static bool prefill_on_tcgen05() {
+// The prefill attention's two products: tcgen05 with operands in shared memory (default), mma.sync
+// (LEANKV_PREFILL_MMA=sync), or the warp-specialised tcgen05 form with query and probabilities in tensor memory
+// (LEANKV_PREFILL_MMA=ws).
+static int prefill_mode() {
     static int v = -1;
     if (v < 0) {
         const char* e = std::getenv("LEANKV_PREFILL_MMA");
-        v = (e != nullptr && e[0] == 's') ? 0 : 1;
+        v = (e != nullptr && e[0] == 's') ? 0 : (e != nullptr && e[0] == 'w') ? 2 : 1;
     }
-    return v == 1;
+    return v;
 }
 
 struct TilePlan {
@@ -482,7 +485,7 @@ static SplitPlan plan_splits(const TilePlan& tp, int T, int start_pos, int Hkv) 
     const long long key[4] = {T, start_pos, Hkv, tp.n_splits};
     if (std::memcmp(key, last_key, sizeof(key)) == 0) return last_plan;
     const int s = tp.n_splits;
-    const int slots = sm_count() * 2;
+    const int slots = sm_count() * (prefill_mode() == 2 ? 1 : 2);
     auto fill = [&](double r, SplitPlan& sp) {
         double w[8], tot = 0.0, acc = 0.0;
         for (int z = 0; z < s; ++z) tot += (w[z] = std::pow(r, z));
@@ -589,6 +592,8 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
                                              (int)kPfSmemBytes));
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_prefill_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kT5SmemBytes));
+        LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_prefill_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kWsSmemBytes));
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_rot_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kRotSmemBytes));
         LEANKV_CUDA_TRY(cudaFuncSetAttribute(tq_rot_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -619,7 +624,10 @@ extern "C" int leankv_tq_prefill_attn(const void* q, void* out, int T, int start
     p.tl0 = lut.tl0; p.tl1 = lut.tl1; p.th0 = lut.th0; p.th1 = lut.th1;
     p.inv_alpha = 1.0f / lut.alpha;
     p.status = reinterpret_cast<int*>(ws);
-    if (prefill_on_tcgen05())
+    if (prefill_mode() == 2)
+        LEANKV_CUDA_TRY(launch_kernel(tq_prefill_ws_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
+                                      dim3(kWsThreads), kWsSmemBytes, st, p));
+    else if (prefill_mode() == 1)
         LEANKV_CUDA_TRY(launch_kernel(tq_prefill_t5_kernel, dim3(tp.n_tiles, n_kv_heads, tp.n_splits),
                                       dim3(kT5Threads), kT5SmemBytes, st, p));
     else

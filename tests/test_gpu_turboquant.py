@@ -386,23 +386,26 @@ def test_prefill_attention_of_a_late_chunk_splits_the_page_range_over_ctas():
         assert rel_l2(got[t].cpu(), want[t]) < ATTN_TOL, t
 
 
-def test_prefill_attention_mma_sync_form_passes_the_same_checks():
-    """The prefill attention runs its two products on tcgen05 by default; LEANKV_PREFILL_MMA=sync (read once
-    per process) selects the mma.sync kernel, which must pass the same oracle / decode-step checks."""
+def test_prefill_attention_other_forms_pass_the_same_checks():
+    """The prefill attention runs its two products on tcgen05 with operands in shared memory by default;
+    LEANKV_PREFILL_MMA (read once per process) selects the mma.sync kernel (sync) or the warp-specialised tcgen05
+    kernel with query and probabilities in tensor memory (ws). Both must pass the same oracle / decode-step
+    checks."""
     import os
     import subprocess
     import sys
 
     from conftest import ROOT
 
-    if os.environ.get("LEANKV_PREFILL_MMA", "").startswith("s"):
-        pytest.skip("already inside the mma.sync run")
-    env = dict(os.environ, LEANKV_PREFILL_MMA="sync")
-    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_turboquant.py"), "-m", "gpu",
-                        "-x", "-q", "-k", "prefill_attention_on_packed or prefill_attention_of_a_late"],
-                       env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
-    assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-1000:])
-    assert "2 passed" in r.stdout
+    if os.environ.get("LEANKV_PREFILL_MMA"):
+        pytest.skip("already inside a run with the form chosen")
+    for mode in ("sync", "ws"):
+        env = dict(os.environ, LEANKV_PREFILL_MMA=mode)
+        r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_turboquant.py"), "-m", "gpu",
+                            "-x", "-q", "-k", "prefill_attention_on_packed or prefill_attention_of_a_late"],
+                           env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+        assert r.returncode == 0, (mode, r.stdout[-2000:], r.stderr[-1000:])
+        assert "2 passed" in r.stdout, mode
 
 
 def test_rotated_attention_plain_call_directly_after_a_multi_page_append():
