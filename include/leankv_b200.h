@@ -254,7 +254,8 @@ int leankv_tq_decode_attn_status(const void* workspace, int* status /* host */);
  * high/low split of Pi_K), the attention kernel (one CTA per 32 query tokens, kv head and page range: a
  * page is de-quantized once per 32 tokens into fp16 operand tiles; scores and the value sum on tensor cores
  * with the query as fp16 high + low halves and fp32 accumulation: tcgen05.mma with the accumulators in
- * tensor memory by default, mma.sync when the environment has LEANKV_PREFILL_MMA=sync), and the merge of
+ * tensor memory by default; LEANKV_PREFILL_MMA=sync in the environment selects an mma.sync form, =ws a
+ * warp-specialised tcgen05 form with query and probabilities as tensor-memory operands), and the merge of
  * the page ranges with the inverse value rotation. The result agrees with decode steps at the same
  * positions to fp16 rounding (rel-L2 < 5e-4 in the tests). The workspace's first word is the status word
  * and must be zero before the first use (bit 0: a bounded wait ran out, bit 1: a page id out of range;
