@@ -353,6 +353,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) tq_prefill_attn_kernel(const 
 // The loop is software-pipelined: the keys of block b+1 are de-quantized (second K tile) and their score MMAs
 // issued (second score buffer) before the softmax of block b, and the value MMAs of block b run under the key
 // de-quantization of block b+2, so neither MMA group's latency is waited for in the open.
+// The issuing thread runs on its own: the row warps tell it through two mbarriers (128 arrivals each) that a
+// block's K / V tiles, or its P tile, are written, and hear back only through the MMA groups' commit barriers;
+// among themselves the row warps meet once per block at a named barrier. So the ~2 000 cycles the single thread
+// spends issuing 18 MMAs and 4 copies per block overlap the row warps' work instead of standing in their way.
 // The running maximum only moves when a block exceeds it by more than kT5Slack (log2 units); then the rows of O
 // are rescaled in tensor memory (tcgen05.ld / st), which is rare after the first blocks. Completion of each MMA
 // group comes back through an mbarrier (tcgen05.commit) with a bounded wait. Output: the same partial results
@@ -373,7 +377,7 @@ constexpr size_t kT5SmemBytes = 2 * (size_t)umma::kTileBytes             // Q'' 
                                 + (size_t)kDim * kT5N * 2                  // V tile  [coord][token]
                                 + (size_t)umma::kRows * kT5N * 2           // P tile  [row][token]
                                 + (size_t)kT5Stages * kT5Blk * 2 * kChunkBytes   // raw chunks
-                                + 3 * kT5N * sizeof(float) + 64;
+                                + 2 * 4 * kT5N * sizeof(float) + 128;     // norms of four blocks; barriers
 
 __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t t5_smem[];
@@ -383,10 +387,11 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     uint8_t* s_v = s_k + 2 * (size_t)kT5KTileBytes;             // B of O:  rows = coordinates, K = tokens
     uint8_t* s_p = s_v + (size_t)kDim * kT5N * 2;               // A of O:  rows = (token, head), K = tokens
     uint8_t* s_raw = s_p + (size_t)umma::kRows * kT5N * 2;      // [stages][page of the block][K chunk | V chunk]
-    float* s_kn = reinterpret_cast<float*>(s_raw + (size_t)kT5Stages * kT5Blk * 2 * kChunkBytes);   // [2][32]
-    float* s_vn = s_kn + 2 * kT5N;
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_vn + kT5N);   // [0..3] raw stages, [4..5] S buffers, [6] O
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + kT5Stages + 3);
+    float* s_kn = reinterpret_cast<float*>(s_raw + (size_t)kT5Stages * kT5Blk * 2 * kChunkBytes);   // [block & 3][32]
+    float* s_vn = s_kn + 4 * kT5N;
+    // [0..3] raw stages, [4..5] S buffers, [6] O, [7] K / V tiles of a block written, [8] P tile written
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_vn + 4 * kT5N);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + kT5Stages + 5);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int H = p.H, Hq = H * kGroup;
@@ -402,6 +407,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
 
     const uint32_t bar0 = smem_u32(s_bar);
     const uint32_t bar_o = bar0 + 8 * (kT5Stages + 2);
+    const uint32_t bar_tiles = bar0 + 8 * (kT5Stages + 3), bar_probs = bar0 + 8 * (kT5Stages + 4);
     auto bar_raw = [&](int b) { return bar0 + 8u * (uint32_t)(b % kT5Stages); };
     auto bar_s = [&](int b) { return bar0 + 8u * (uint32_t)(kT5Stages + (b & 1)); };
     // block b is use number b / 4 of its raw stage and b / 2 of its score buffer: those uses' phase parities
@@ -413,6 +419,8 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < kT5Stages + 3; ++i) mbar_init(bar0 + 8 * i, 1);
+        mbar_init(bar_tiles, 128);
+        mbar_init(bar_probs, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     pdl_begin();
@@ -425,7 +433,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     const size_t page_stride = (size_t)2 * H * kChunkBytes, kv_stride = (size_t)H * kChunkBytes;
     const uint8_t* pool_kvh = p.pool + (size_t)kvh * kChunkBytes;
     bool bad_page = false;
-    int n_issued = 0, n_landed = 0;                          // thread 0: page blocks requested / seen to arrive
+    int n_issued = 0;                                        // issuing thread: page blocks requested
     int next_id[kT5Blk] = {0, 0};                            // thread 0: page ids of the block issue() takes next
     auto load_ids = [&](int blk) {
 #pragma unroll
@@ -512,7 +520,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
 #pragma unroll
         for (int q = 0; q < 4; ++q)
             *reinterpret_cast<uint4*>(kt + umma::offset(trow, k8 + q)) = make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
-        if (tid < kT5N) s_kn[(b & 1) * kT5N + tid] = norm_of(b, tid, false);
+        if (tid < kT5N) s_kn[(b & 3) * kT5N + tid] = norm_of(b, tid, false);
     };
     auto dequant_values = [&](int b) {                       // block b's values -> the V tile
         if (warp >= 4) return;
@@ -541,7 +549,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
             *reinterpret_cast<uint4*>(s_v + umma::offset_k(16 * grp + 4 * j + pl, 2 * pgi + half, kT5KChunksTok)) =
                 make_uint4(a[0], a[1], a[2], a[3]);
         }
-        if (tid < kT5N) s_vn[tid] = norm_of(b, tid, true);
+        if (tid < kT5N) s_vn[(b & 3) * kT5N + tid] = norm_of(b, tid, true);
     };
     auto issue_scores = [&](int b) {                         // thread 0: S(b) into score buffer b & 1
         const uint32_t qh = smem_u32(s_qh), ql = smem_u32(s_ql);
@@ -564,12 +572,10 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     int n_pv = 0;                                             // value MMA groups committed
 
     // ---- prologue: keys of block 0, their score MMAs ----
-    if (n_blk > 0) {
+    if (n_blk > 0 && warp < 4) {
         if (!umma::bar_wait(bar_raw(0), 0)) {
             failed = true;
             where |= kT5WherePages;
-        } else if (tid == kT5Issuer) {
-            n_landed = 1;
         }
         dequant_keys(0);
     }
@@ -577,134 +583,146 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     umma::fence_before_sync();
     failed = __syncthreads_or(failed);                        // also publishes the query tiles
     umma::fence_after_sync();
-    if (!failed && n_blk > 0 && tid == kT5Issuer) issue_scores(0);
 
-    for (int blk = 0; blk < n_blk && !failed; ++blk) {
-        // (1) keys of the next block while S(blk) is on the tensor cores
-        if (blk + 1 < n_blk) {
-            if (!umma::bar_wait(bar_raw(blk + 1), par_raw(blk + 1))) {
-                failed = true;
-                where |= kT5WherePages;
-            } else if (tid == kT5Issuer) {
-                n_landed = blk + 2;
+    if (warp == 4) {
+        // ------------------------------------------------------------------ the issuing thread
+        if (tid == kT5Issuer && !failed && n_blk > 0) {
+            issue_scores(0);
+            for (int blk = 0; blk < n_blk; ++blk) {
+                // K(blk + 1) and V(blk) are written, both halves of the raw stage of block blk consumed
+                if (!umma::bar_wait(bar_tiles, (uint32_t)(blk & 1))) {
+                    failed = true;
+                    where |= kT5WherePages;
+                    break;
+                }
+                umma::fence_after_sync();
+                if (blk + 1 < n_blk) issue_scores(blk + 1);
+                if (blk + kT5Stages < n_blk) issue(blk + kT5Stages);
+                // P(blk) is written (and O rescaled where the reference moved)
+                if (!umma::bar_wait(bar_probs, (uint32_t)(blk & 1))) {
+                    failed = true;
+                    where |= kT5WhereScores;
+                    break;
+                }
+                umma::fence_after_sync();
+                const uint32_t pb = smem_u32(s_p), vb = smem_u32(s_v);
+#pragma unroll
+                for (int kt = 0; kt < kT5N / 16; ++kt) {
+                    const uint32_t off = (uint32_t)kt * 2 * umma::kLbo;
+                    umma::mma_f16_n(tmem_o, umma::desc_k(pb + off, kT5KChunksTok), umma::desc_k(vb + off, kT5KChunksTok),
+                                    umma::idesc_n(kDim), (blk == 0 && kt == 0) ? 0u : 1u);
+                }
+                umma::commit(bar_o);
             }
-            dequant_keys(blk + 1);
         }
-        // (2) values of this block: the previous block's value MMAs read the V and P tiles and must be done
-        if (blk > 0) {
-            if (!umma::bar_wait(bar_o, (uint32_t)((blk - 1) & 1))) {
+    } else if (!failed) {
+        // ------------------------------------------------------------------ the row warps
+        // A wait that runs out makes the thread skip every later wait but not the barriers: all 128 threads
+        // walk all blocks, so that nobody is left standing at the named barrier.
+        for (int blk = 0; blk < n_blk; ++blk) {
+            // (1) keys of the next block while S(blk) is on the tensor cores
+            if (blk + 1 < n_blk) {
+                if (!failed && !umma::bar_wait(bar_raw(blk + 1), par_raw(blk + 1))) {
+                    failed = true;
+                    where |= kT5WherePages;
+                }
+                dequant_keys(blk + 1);
+            }
+            // (2) values of this block: the previous block's value MMAs read the V and P tiles and must be done
+            if (blk > 0) {
+                if (!failed && !umma::bar_wait(bar_o, (uint32_t)((blk - 1) & 1))) {
+                    failed = true;
+                    where |= kT5WhereValues;
+                }
+                umma::fence_after_sync();
+            }
+            dequant_values(blk);
+            umma::fence_operands();
+            umma::fence_before_sync();
+            umma::bar_arrive(bar_tiles);                                  // for the issuing thread
+            asm volatile("bar.sync 1, 128;" ::: "memory");                // the block's value norms, for the other rows
+            // (3) this thread's row of S(blk): key norm, causal mask, running maximum
+            if (!failed && !umma::bar_wait(bar_s(blk), par2(blk))) {
                 failed = true;
-                where |= kT5WhereValues;
+                where |= kT5WhereScores;
             }
             umma::fence_after_sync();
-        }
-        dequant_values(blk);
-        umma::fence_operands();
-        umma::fence_before_sync();
-        if (__syncthreads_or(failed)) {
-            failed = true;
-            break;
-        }
-        umma::fence_after_sync();
-        if (tid == kT5Issuer) {
-            if (blk + kT5Stages < n_blk) issue(blk + kT5Stages);       // both halves of the raw stage have been consumed
-            if (blk + 1 < n_blk) issue_scores(blk + 1);
-        }
-        // (3) this thread's row of S(blk): key norm, causal mask, running maximum
-        if (!umma::bar_wait(bar_s(blk), par2(blk))) {
-            failed = true;
-            where |= kT5WhereScores;
-        }
-        umma::fence_after_sync();
-        if (warp < 4) {
-            uint32_t sv[32];
-            umma::ld32(sv, tmem_base + (uint32_t)(blk & 1) * kT5N, lane0, 0);
-            const int kbase = (pg_lo + blk * kT5Blk) * kPage;
-            const int n_tok_here = min(kT5Blk, n_pg - blk * kT5Blk) * kPage;     // tokens of this block that lie in the range
-            // a whole block at or below the tile's first query position needs no mask (CTA-uniform)
-            const bool full = n_tok_here == kT5N && kbase + kT5N - 1 <= p.start_pos + tok0;
-            float sc[32];
-            float bmax = kNoRef;
             {
-                const float4* kn4 = reinterpret_cast<const float4*>(s_kn + (blk & 1) * kT5N);
+                uint32_t sv[32];
+                umma::ld32(sv, tmem_base + (uint32_t)(blk & 1) * kT5N, lane0, 0);
+                const int kbase = (pg_lo + blk * kT5Blk) * kPage;
+                const int n_tok_here = min(kT5Blk, n_pg - blk * kT5Blk) * kPage;     // tokens of this block that lie in the range
+                // a whole block at or below the tile's first query position needs no mask (CTA-uniform)
+                const bool full = n_tok_here == kT5N && kbase + kT5N - 1 <= p.start_pos + tok0;
+                float sc[32];
+                float bmax = kNoRef;
+                {
+                    const float4* kn4 = reinterpret_cast<const float4*>(s_kn + (blk & 3) * kT5N);
 #pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4) {
-                    const float4 n = kn4[j4];
-                    sc[4 * j4 + 0] = __uint_as_float(sv[4 * j4 + 0]) * n.x;
-                    sc[4 * j4 + 1] = __uint_as_float(sv[4 * j4 + 1]) * n.y;
-                    sc[4 * j4 + 2] = __uint_as_float(sv[4 * j4 + 2]) * n.z;
-                    sc[4 * j4 + 3] = __uint_as_float(sv[4 * j4 + 3]) * n.w;
-                }
-                if (!full) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (!(j < n_tok_here && kbase + j <= qpos)) sc[j] = kNoRef;
-                }
-#pragma unroll
-                for (int j = 0; j < 32; ++j) bmax = fmaxf(bmax, sc[j]);
-            }
-            // the reference only moves when the block exceeds it by more than the slack; the rows of O are then
-            // rescaled in tensor memory (all lanes of a warp take part; lanes that do not move use factor 1)
-            const bool move = bmax > m_ref + kT5Slack;
-            const float m_new = move ? bmax : m_ref;
-            const float f = move ? ex2_approx(m_ref - m_new) : 1.0f;
-            if (__any_sync(0xffffffffu, move) && blk > 0) {
-#pragma unroll
-                for (int c0 = 0; c0 < kDim; c0 += 32) {
-                    uint32_t ov[32];
-                    umma::ld32(ov, tmem_o, lane0, c0);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-                    umma::st32(ov, tmem_o, lane0, c0);
-                }
-            }
-            m_ref = m_new;
-            l_run *= f;
-            // probabilities (at most 2^slack) times value norm, fp16, as this row of the P operand
-            {
-                float sum = 0.f;
-                __half2 ph[16];
-                const float4* vn4 = reinterpret_cast<const float4*>(s_vn);
-#pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4) {
-                    const float4 n = vn4[j4];
-                    float pr[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float x = sc[4 * j4 + e];
-                        // a masked entry gives 0 (with no reference yet x - m_ref would be 0, hence the test)
-                        pr[e] = (full || x > 0.5f * kNoRef) ? ex2_approx(x - m_ref) : 0.f;
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 n = kn4[j4];
+                        sc[4 * j4 + 0] = __uint_as_float(sv[4 * j4 + 0]) * n.x;
+                        sc[4 * j4 + 1] = __uint_as_float(sv[4 * j4 + 1]) * n.y;
+                        sc[4 * j4 + 2] = __uint_as_float(sv[4 * j4 + 2]) * n.z;
+                        sc[4 * j4 + 3] = __uint_as_float(sv[4 * j4 + 3]) * n.w;
                     }
-                    sum += (pr[0] + pr[1]) + (pr[2] + pr[3]);
-                    ph[2 * j4] = __floats2half2_rn(pr[0] * n.x, pr[1] * n.y);
-                    ph[2 * j4 + 1] = __floats2half2_rn(pr[2] * n.z, pr[3] * n.w);
+                    if (!full) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (!(j < n_tok_here && kbase + j <= qpos)) sc[j] = kNoRef;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) bmax = fmaxf(bmax, sc[j]);
                 }
-                l_run += sum;
+                // the reference only moves when the block exceeds it by more than the slack; the rows of O are then
+                // rescaled in tensor memory (all lanes of a warp take part; lanes that do not move use factor 1)
+                const bool move = bmax > m_ref + kT5Slack;
+                const float m_new = move ? bmax : m_ref;
+                const float f = move ? ex2_approx(m_ref - m_new) : 1.0f;
+                if (__any_sync(0xffffffffu, move) && blk > 0) {
 #pragma unroll
-                for (int c = 0; c < kT5KChunksTok; ++c)
-                    *reinterpret_cast<uint4*>(s_p + umma::offset_k(row, c, kT5KChunksTok)) = *reinterpret_cast<const uint4*>(ph + 4 * c);
-            }
-        }
-        umma::fence_operands();
-        umma::fence_before_sync();
-        if (__syncthreads_or(failed)) {
-            failed = true;
-            break;
-        }
-        umma::fence_after_sync();
-        if (tid == kT5Issuer) {
-            const uint32_t pb = smem_u32(s_p), vb = smem_u32(s_v);
+                    for (int c0 = 0; c0 < kDim; c0 += 32) {
+                        uint32_t ov[32];
+                        umma::ld32(ov, tmem_o, lane0, c0);
 #pragma unroll
-            for (int kt = 0; kt < kT5N / 16; ++kt) {
-                const uint32_t off = (uint32_t)kt * 2 * umma::kLbo;
-                umma::mma_f16_n(tmem_o, umma::desc_k(pb + off, kT5KChunksTok), umma::desc_k(vb + off, kT5KChunksTok),
-                                umma::idesc_n(kDim), (blk == 0 && kt == 0) ? 0u : 1u);
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+                        umma::st32(ov, tmem_o, lane0, c0);
+                    }
+                }
+                m_ref = m_new;
+                l_run *= f;
+                // probabilities (at most 2^slack) times value norm, fp16, as this row of the P operand
+                {
+                    float sum = 0.f;
+                    __half2 ph[16];
+                    const float4* vn4 = reinterpret_cast<const float4*>(s_vn + (blk & 3) * kT5N);
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 n = vn4[j4];
+                        float pr[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float x = sc[4 * j4 + e];
+                            // a masked entry gives 0 (with no reference yet x - m_ref would be 0, hence the test)
+                            pr[e] = (full || x > 0.5f * kNoRef) ? ex2_approx(x - m_ref) : 0.f;
+                        }
+                        sum += (pr[0] + pr[1]) + (pr[2] + pr[3]);
+                        ph[2 * j4] = __floats2half2_rn(pr[0] * n.x, pr[1] * n.y);
+                        ph[2 * j4 + 1] = __floats2half2_rn(pr[2] * n.z, pr[3] * n.w);
+                    }
+                    l_run += sum;
+#pragma unroll
+                    for (int c = 0; c < kT5KChunksTok; ++c)
+                        *reinterpret_cast<uint4*>(s_p + umma::offset_k(row, c, kT5KChunksTok)) = *reinterpret_cast<const uint4*>(ph + 4 * c);
+                }
             }
-            umma::commit(bar_o);
+            umma::fence_operands();
+            umma::fence_before_sync();
+            umma::bar_arrive(bar_probs);
+            n_pv = blk + 1;
         }
-        n_pv = blk + 1;
     }
-    if (!failed && n_pv > 0) {
+    if (!failed && n_pv > 0) {                                // row warps: the last value MMAs
         if (!umma::bar_wait(bar_o, (uint32_t)((n_pv - 1) & 1))) {
             failed = true;
             where |= kT5WhereValues;
@@ -716,7 +734,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tq_prefill_t5_kernel(const Pref
     if ((failed || bad_page) && tid == kT5Issuer) atomicOr(p.status, failed ? kStatusWaitTimeout : kStatusBadPage);
     if (failed && tid == kT5Issuer) {
         // give page copies that may still be in flight a bounded chance to land in this CTA's shared memory
-        for (int b = n_landed; b < n_issued; ++b) umma::bar_wait(bar_raw(b), par_raw(b));
+        for (int b = max(0, n_issued - kT5Stages); b < n_issued; ++b) umma::bar_wait(bar_raw(b), par_raw(b));
     }
 
     // ---- this range's partial result for this thread's row ----
