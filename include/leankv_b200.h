@@ -70,7 +70,9 @@ size_t leankv_sparse_gemv_workspace_bytes(int N, int Z);
  * fp16 [N] and are added in fp16 after y has been rounded (bias first, as
  * patching.py:174-175 does, then residual + y as the decoder block does).
  * active_elems (may be NULL) is a uint64 counter that receives += the number of weight
- * elements streamed (channels that passed the threshold x columns); 2 bytes each. */
+ * elements streamed (channels that passed the threshold x columns); 2 bytes each.
+ * Besides those, every CTA asks up to 32 KB of its weight rows into L2 before the previous kernel in the
+ * stream has finished (LEANKV_GEMV_PREFETCH_KB; Wt must therefore not be written by that kernel). */
 int leankv_sparse_gemv_f16(const void* Wt, const void* x, void* y, int N, int Z,
                            float threshold, const void* bias, const void* residual,
                            void* workspace, size_t workspace_bytes,

@@ -46,6 +46,7 @@ struct GemvParams {
     unsigned long long* active_elems;
     int N, Z;
     int n_slices, k_splits, rows_per_split;
+    int prefetch_rows;   // weight rows of its range a CTA asks into L2 before it waits for the previous kernel
     int n_segments;
     int seg_end[LEANKV_MAX_SEGMENTS];
     float thr[LEANKV_MAX_SEGMENTS];
@@ -76,6 +77,22 @@ struct GemvPlan {
     int n_slices, k_splits, rows_per_split;
     size_t counter_bytes, partial_bytes;
 };
+
+// How many weight rows of its range a CTA asks into L2 ahead of the dependency wait: LEANKV_GEMV_PREFETCH_KB
+// kilobytes per CTA (default 32; 0 = off), at most LEANKV_GEMV_PREFETCH_PCT per cent of the range (default 25).
+// Measured on the Mistral-7B-shape decode step: off 427.2 tok/s, 16 KB 435.5, 32 KB 437.6 (25 %: 438.1), 48 KB 434.0.
+static int prefetch_rows(int rows_per_split, int arrays) {
+    static int kb = -1, pct = -1;
+    if (kb < 0) {
+        const char* e = std::getenv("LEANKV_GEMV_PREFETCH_KB");
+        kb = e != nullptr ? std::max(0, std::min(512, std::atoi(e))) : 32;
+        const char* f = std::getenv("LEANKV_GEMV_PREFETCH_PCT");
+        pct = f != nullptr ? std::max(0, std::min(100, std::atoi(f))) : 25;
+    }
+    const int by_bytes = kb * 1024 / (kColsPerCta * 2 * arrays);
+    const int by_share = (int)((long long)rows_per_split * pct / 100);
+    return std::min(std::min(by_bytes, by_share), kThreads / arrays);
+}
 
 GemvPlan make_plan(int N, int Z, int arrays) {
     GemvPlan pl;
@@ -128,6 +145,23 @@ __global__ void __launch_bounds__(kThreads, kSwiglu ? 3 : 4) sparse_gemv_kernel(
     __shared__ int s_wcount[kWarps];
     __shared__ int s_last;
 
+    // The weights are constants, not an output of the previous kernel: the first rows of this CTA's range are
+    // asked into L2 before the dependency wait, so that they arrive while the previous kernel drains and while
+    // this CTA tests and compacts its input channels. Which rows are active is not known yet, so about
+    // (sparsity) of these bytes are not used; the count is kept small.
+    if (p.prefetch_rows > 0) {
+        const int z0p = blockIdx.y * p.rows_per_split;
+        const int nr = min(p.prefetch_rows, min(p.rows_per_split, p.Z - z0p));
+        const int colb = blockIdx.x * kColsPerCta;
+        const int bytes = min(kColsPerCta, p.N - colb) * 2;           // N % 8 == 0: a multiple of 16
+        const int t = threadIdx.x;
+        if (t < nr * kArrays && bytes > 0) {
+            const int r = kSwiglu ? t >> 1 : t;
+            const __half* base = (kSwiglu && (t & 1)) ? p.Wt2 : p.Wt;
+            const __half* a = base + (size_t)(z0p + r) * p.N + colb;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a), "r"(bytes) : "memory");
+        }
+    }
     pdl_begin();
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -494,6 +528,7 @@ int launch_gemv(const void* Wt, const void* x, void* y, int N, int Z, const lean
     p.n_slices = pl.n_slices;
     p.k_splits = pl.k_splits;
     p.rows_per_split = pl.rows_per_split;
+    p.prefetch_rows = prefetch_rows(pl.rows_per_split, 1);
     p.n_segments = segs->n_segments;
     for (int s = 0; s < LEANKV_MAX_SEGMENTS; ++s) {
         p.seg_end[s] = s < segs->n_segments ? segs->seg_end[s] : N;
@@ -620,6 +655,7 @@ static int launch_swiglu(const void* Wt_gate, const void* Wt_up, const void* x, 
     p.n_slices = pl.n_slices;
     p.k_splits = pl.k_splits;
     p.rows_per_split = pl.rows_per_split;
+    p.prefetch_rows = prefetch_rows(pl.rows_per_split, 2);
     p.n_segments = 1;
     for (int s = 0; s < LEANKV_MAX_SEGMENTS; ++s) {
         p.seg_end[s] = N;
