@@ -72,7 +72,9 @@ size_t leankv_sparse_gemv_workspace_bytes(int N, int Z);
  * active_elems (may be NULL) is a uint64 counter that receives += the number of weight
  * elements streamed (channels that passed the threshold x columns); 2 bytes each.
  * Besides those, every CTA asks up to 32 KB of its weight rows into L2 before the previous kernel in the
- * stream has finished (LEANKV_GEMV_PREFETCH_KB; Wt must therefore not be written by that kernel). */
+ * stream has finished (LEANKV_GEMV_PREFETCH_KB, 0 = off): a hint that changes DRAM traffic (about the masked
+ * share of those bytes is read for nothing) and timing, never results — L2 is the point of coherence, so
+ * even a Wt written by that previous kernel is read correctly afterwards. */
 int leankv_sparse_gemv_f16(const void* Wt, const void* x, void* y, int N, int Z,
                            float threshold, const void* bias, const void* residual,
                            void* workspace, size_t workspace_bytes,
