@@ -309,3 +309,41 @@ def test_one_workspace_serves_projections_of_different_widths():
                                                    xs[512].data_ptr(), g.data_ptr(), 14336, 512, 0.25, 0.25,
                                                    ws.data_ptr(), ws.numel(), None, st), "swiglu")
         assert torch.isfinite(g).all()
+
+
+_PREFETCH_SNIPPET = r"""
+import hashlib, sys, torch
+sys.path.insert(0, %(root)r)
+from leankv_b200 import workloads
+from leankv_b200.teal.kernels.sparse_gemv import prepare_weight_for_sparse_gemv, sparse_gemv, sparse_swiglu
+dev = torch.device("cuda:0")
+c = workloads.sparse_gemv_case(device=dev)
+y1 = sparse_gemv(c.x.reshape(1, 1, -1), prepare_weight_for_sparse_gemv(c.weight), c.threshold)
+s = workloads.swiglu_case(device=dev)
+y2 = sparse_swiglu(s.x.reshape(1, 1, -1), prepare_weight_for_sparse_gemv(s.w_gate), prepare_weight_for_sparse_gemv(s.w_up),
+                   s.threshold, s.threshold)
+torch.cuda.synchronize()
+print("OUT", hashlib.sha256(y1.cpu().numpy().tobytes() + y2.cpu().numpy().tobytes()).hexdigest())
+"""
+
+
+def test_weight_prefetch_budget_never_changes_a_result():
+    """The kernels ask some of their weight rows into L2 ahead of the previous kernel's completion
+    (LEANKV_GEMV_PREFETCH_KB, read once per process): a hint, so configs 1 and 2 must come out bit for bit the
+    same with the prefetch off, at its default and with every row of a CTA's range asked for."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    out = {}
+    for name, env in (("off", {"LEANKV_GEMV_PREFETCH_KB": "0"}), ("default", {}),
+                      ("all", {"LEANKV_GEMV_PREFETCH_KB": "512", "LEANKV_GEMV_PREFETCH_PCT": "100"})):
+        full = {k: v for k, v in os.environ.items() if not k.startswith("LEANKV_GEMV_PREFETCH")}
+        full.update(env)
+        r = subprocess.run([sys.executable, "-c", _PREFETCH_SNIPPET % {"root": ROOT}], env=full, capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        out[name] = [ln for ln in r.stdout.splitlines() if ln.startswith("OUT")][-1].split()[1]
+    assert out["off"] == out["default"] == out["all"]
